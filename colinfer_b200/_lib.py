@@ -1,0 +1,74 @@
+"""ctypes binding of libcolinfer_b200.so (the C ABI declared in include/colinfer_b200.h).
+
+There is no CPU path: if the library is missing this module raises, and every op needs CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcolinfer_b200.so")
+
+F32, BF16 = 0, 1
+FORCE_DISTRIBUTION = 1
+ROW_DEGENERATE, ROW_TIMEOUT, ROW_HIST_SLOW = 1, 2, 4
+
+
+class SamplerParamsC(C.Structure):
+    _fields_ = [("temperature", C.c_void_p), ("top_k", C.c_void_p), ("top_p", C.c_void_p), ("log_min_p", C.c_void_p),
+                ("seed", C.c_void_p), ("repetition_penalty", C.c_void_p), ("presence_penalty", C.c_void_p),
+                ("frequency_penalty", C.c_void_p), ("history", C.c_void_p), ("hist_len", C.c_void_p),
+                ("hist_stride", C.c_int32)]
+
+
+class Geometry(C.Structure):
+    _fields_ = [("cluster", C.c_int32), ("slice_elems", C.c_int32), ("smem_bytes", C.c_int32), ("bulk_copy", C.c_int32)]
+
+
+ROW_STATS_BYTES = 32  # sizeof(colinfer_row_stats): 3 x f32, i32, i64, u64
+
+# name -> (restype, argtypes); every symbol include/colinfer_b200.h declares
+SIGNATURES = {
+    "colinfer_philox_uniform": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_apply_mask": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_sample": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.POINTER(SamplerParamsC),
+                                  C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_processed_probs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_inverse_cdf": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_spec_accept": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_spec_verify": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.POINTER(SamplerParamsC),
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_spec_verify_stats_bytes": (C.c_int64, [C.c_int, C.c_int]),
+    "colinfer_spec_verify_ids_bytes": (C.c_int64, [C.c_int, C.c_int]),
+    "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.POINTER(Geometry)]),
+    "colinfer_set_cluster_override": (C.c_int, [C.c_int]),
+    "colinfer_version": (C.c_int, []),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises (never falls back) when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m colinfer_b200.build` "
+                               "(there is no CPU or eager fallback for this path)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    """cudaError_t -> RuntimeError, the exception type the reference's bindings raise (TORCH_CHECK)."""
+    if code != 0:
+        raise RuntimeError(f"{what} failed: CUDA error {code}" + (" (invalid value / shape)" if code == 1 else ""))

@@ -1,0 +1,378 @@
+// ops.cu -- the small kernels of the logits -> token path (sm_100a): Philox uniforms, the stand-alone grammar mask, the
+// full-probability writer behind processed_probs, inverse_cdf, and the speculative accept / verify steps.
+#include "common.cuh"
+#include "../../include/colinfer_b200.h"
+
+// ------------------------------------------------------------------------------------------------ philox_uniform
+// Replaces k_philox_uniform (csrc/sampling.cu:25-35 of the reference).  One thread per output; the grid covers B * n.
+__global__ void k_philox_uniform(const int64_t* __restrict__ seed, const int64_t* __restrict__ offset,
+                                 float* __restrict__ out, int B, int n) {
+    const long long total = (long long)B * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int b = (int)(i / n), j = (int)(i % n);
+        out[i] = u32_to_uniform(philox_word(philox_key(seed[b]), (u64)offset[b] + (u64)j));
+    }
+}
+
+extern "C" int colinfer_philox_uniform(const int64_t* seed, const int64_t* offset, float* out, int B, int n, void* stream) {
+    if (!seed || !offset || !out || B < 0 || n < 0) return (int)cudaErrorInvalidValue;
+    const long long total = (long long)B * n;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads : 148 * 8);
+    k_philox_uniform<<<blocks, threads, 0, (cudaStream_t)stream>>>(seed, offset, out, B, n);
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ apply_mask
+// Replaces apply_mask (engine/runtime/sampler.py:50-56): pure streaming, 4 tokens per thread share one mask nibble.
+__global__ void k_apply_mask(const float* __restrict__ logits, const int32_t* __restrict__ mask, float* __restrict__ out,
+                             long long rows, int V, int W, int vec) {
+    const long long row = blockIdx.y;
+    const float* src = logits + row * V;
+    float* dst = out + row * V;
+    const int32_t* m = mask + row * W;
+    if (vec) {
+        const int n4 = V >> 2;
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+            float4 v = __ldg(reinterpret_cast<const float4*>(src) + i);
+            const int g = i << 2;
+            const uint32_t bits = ((uint32_t)__ldg(m + (g >> 5)) >> (g & 31)) & 0xFu;
+            if (!(bits & 1u)) v.x = CI_NEG_INF;
+            if (!(bits & 2u)) v.y = CI_NEG_INF;
+            if (!(bits & 4u)) v.z = CI_NEG_INF;
+            if (!(bits & 8u)) v.w = CI_NEG_INF;
+            reinterpret_cast<float4*>(dst)[i] = v;
+        }
+    } else {
+        for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < V; g += gridDim.x * blockDim.x) {
+            const float v = __ldg(src + g);
+            dst[g] = (((uint32_t)__ldg(m + (g >> 5)) >> (g & 31)) & 1u) ? v : CI_NEG_INF;
+        }
+    }
+}
+
+extern "C" int colinfer_apply_mask(const float* logits, const int32_t* mask, float* out, int64_t rows, int V, int W, void* stream) {
+    if (!logits || !mask || !out || rows < 0 || V <= 0 || W < (V + 31) / 32) return (int)cudaErrorInvalidValue;
+    if (rows == 0) return 0;
+    if (rows > 65535) {
+        // the row index rides in gridDim.y; split very tall inputs
+        for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+            const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
+            const int e = colinfer_apply_mask(logits + r0 * V, mask + r0 * W, out + r0 * V, nr, V, W, stream);
+            if (e) return e;
+        }
+        return 0;
+    }
+    const int vec = ((V & 3) == 0 && ((((uintptr_t)logits) | ((uintptr_t)out)) & 15) == 0) ? 1 : 0;
+    const int threads = 256;
+    const int work = vec ? V / 4 : V;
+    int bx = (work + threads - 1) / threads;
+    if (bx > 1024) bx = 1024;
+    k_apply_mask<<<dim3(bx, (unsigned)rows), threads, 0, (cudaStream_t)stream>>>(logits, mask, out, rows, V, W, vec);
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ processed_probs
+// P(t) = exp(z_t - m) / S on the kept set of the row (described by the row statistics of the fused kernel), else 0.
+__global__ void k_write_probs(const float* __restrict__ logits, const colinfer_row_stats* __restrict__ stats,
+                              float* __restrict__ out, int V) {
+    const int row = blockIdx.y;
+    const colinfer_row_stats st = stats[row];
+    const float* src = logits + (size_t)row * V;
+    float* dst = out + (size_t)row * V;
+    const bool bad = (st.status & (COLINFER_ROW_DEGENERATE | COLINFER_ROW_TIMEOUT)) != 0 || st.mass_q == 0;
+    const float m = scale_logit(st.lmax, st.tc);
+    const float S = (float)((double)st.mass_q * (1.0 / 1099511627776.0));
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < V; g += gridDim.x * blockDim.x) {
+        const float l = __ldg(src + g);
+        float p;
+        if (bad) p = __int_as_float(0x7fc00000);               // NaN, as a softmax without a finite maximum gives
+        else if (l >= st.lcut && l > CI_NEG_INF) p = __fdiv_rn(expf(scale_logit(l, st.tc) - m), S);
+        else p = 0.0f;
+        dst[g] = p;
+    }
+}
+
+extern "C" int colinfer_processed_probs(const float* logits, const float* temperature, const int32_t* top_k,
+                                        const float* top_p, const float* log_min_p, float* out,
+                                        colinfer_row_stats* scratch, int R, int V, void* stream) {
+    if (!logits || !temperature || !top_k || !top_p || !log_min_p || !out || !scratch || R < 0 || V <= 0)
+        return (int)cudaErrorInvalidValue;
+    if (R == 0) return 0;
+    colinfer_sampler_params p = {};
+    p.temperature = temperature; p.top_k = top_k; p.top_p = top_p; p.log_min_p = log_min_p;
+    int e = colinfer_sample(logits, COLINFER_F32, nullptr, 0, 0, &p, nullptr, 0, nullptr, nullptr, scratch, nullptr,
+                            1, R, V, COLINFER_FORCE_DISTRIBUTION, stream);
+    if (e) return e;
+    const int threads = 256;
+    int bx = (V + threads - 1) / threads;
+    if (bx > 296) bx = 296;
+    for (int r0 = 0; r0 < R; r0 += 65535) {
+        const int nr = R - r0 < 65535 ? R - r0 : 65535;
+        k_write_probs<<<dim3(bx, nr), threads, 0, (cudaStream_t)stream>>>(logits + (size_t)r0 * V, scratch + r0,
+                                                                           out + (size_t)r0 * V, V);
+    }
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ inverse_cdf
+// One CTA per row.  Sums are float64 (the reference's fp32 scan order is device dependent; float64 is what its CPU
+// cumsum accumulates in).  Warp w owns a contiguous region, lanes interleave, so the index order is (warp, step, lane).
+#define ICDF_THREADS 1024
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_incl_scan_f64(double v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(ICDF_THREADS) k_inverse_cdf(const float* __restrict__ P, const float* __restrict__ u,
+                                                              int64_t* __restrict__ out, int V) {
+    __shared__ double wtot[ICDF_THREADS / 32];
+    __shared__ long long result;
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* src = P + (size_t)row * V;
+    const int nwarps = ICDF_THREADS / 32;
+    const int reg = (((V + 31) / 32 + nwarps - 1) / nwarps) * 32;
+    const int lo = min(warp * reg, V), hi = min(lo + reg, V);
+    double acc = 0.0;
+    for (int i = lo + lane; i < hi; i += 32) acc += (double)__ldg(src + i);
+    const double wt = warp_sum_f64(acc);
+    if (lane == 0) wtot[warp] = wt;
+    if (threadIdx.x == 0) result = V - 1;
+    __syncthreads();
+    double total = 0.0, woff = 0.0;
+    for (int w = 0; w < nwarps; ++w) { if (w < warp) woff += wtot[w]; total += wtot[w]; }
+    const double t = (double)u[row] * total;
+    // first index whose inclusive prefix reaches t; the owning warp is the first whose inclusive total reaches it
+    if (woff < t && woff + wt >= t) {
+        double run = woff;
+        for (int i0 = lo; i0 < hi; i0 += 32) {
+            const int i = i0 + lane;
+            const double v = i < hi ? (double)__ldg(src + i) : 0.0;
+            const double incl = warp_incl_scan_f64(v, lane);
+            const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= t);
+            if (hit) {
+                if (lane == __ffs(hit) - 1) result = i;
+                break;
+            }
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out[row] = result;
+}
+
+extern "C" int colinfer_inverse_cdf(const float* P, const float* u, int64_t* out, int R, int V, void* stream) {
+    if (!P || !u || !out || R < 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    if (R == 0) return 0;
+    k_inverse_cdf<<<R, ICDF_THREADS, 0, (cudaStream_t)stream>>>(P, u, out, V);
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ spec_accept
+// The accept / bonus / stop-cut lines of the reference's speculative cycle (engine/spec/mtp.py:406-415, 422-423),
+// one thread per slot instead of ~20 tiny launches.
+__global__ void k_spec_accept(const int64_t* __restrict__ pred, const int64_t* __restrict__ tok,
+                              const int64_t* __restrict__ stop_ids, const int32_t* __restrict__ active,
+                              int64_t* __restrict__ out_tok, int32_t* __restrict__ n_out, int B, int k1, int S) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const int k = k1 - 1;
+    const int64_t* pr = pred + (size_t)b * k1;
+    const int64_t* d = tok + (size_t)b * k1 + 1;
+    int n = 1;
+    while (n - 1 < k && pr[n - 1] == d[n - 1]) ++n;
+    int64_t bonus = pr[n - 1];
+    if (stop_ids != nullptr) {
+        const int64_t* st = stop_ids + (size_t)b * S;
+        bool cut = false;
+        for (int i = 0; i < n - 1 && i < k && !cut; ++i) {
+            for (int s = 0; s < S; ++s) {
+                if (d[i] == st[s]) { n = i + 1; bonus = d[i]; cut = true; break; }
+            }
+        }
+    }
+    if (active != nullptr) n *= active[b];
+    int64_t* o = out_tok + (size_t)b * k1;
+    for (int i = 0; i < k; ++i) o[i] = d[i];
+    o[k] = bonus;
+    if (n >= 1) o[n - 1] = bonus;
+    n_out[b] = n;
+}
+
+extern "C" int colinfer_spec_accept(const int64_t* pred, const int64_t* tok, const int64_t* stop_ids,
+                                    const int32_t* active, int64_t* out_tok, int32_t* n, int B, int k1, int S, void* stream) {
+    if (!pred || !tok || !out_tok || !n || B < 0 || k1 < 1 || S < 0) return (int)cudaErrorInvalidValue;
+    if (B == 0) return 0;
+    k_spec_accept<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(pred, tok, S > 0 ? stop_ids : nullptr, active, out_tok, n, B, k1, S);
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ spec_verify (rejection)
+// Finish step: per slot, decide the accepted prefix from the row statistics of the target and draft rows, then, at a
+// rejection, stream the two rows of that position once to draw from the residual max(p - q, 0).
+#define VF_THREADS 1024
+struct VerifyArgs {
+    const void* tl; const void* dl; int dtype;
+    const int32_t* mask; int W;
+    const float* temperature;
+    const int64_t* draft_ids; const float* ua; const float* us;
+    const colinfer_row_stats* st_t; const colinfer_row_stats* st_d; const int64_t* samp_t;
+    int64_t* out_tok; int32_t* n;
+    int B, k, V;
+};
+
+__device__ __forceinline__ float load_logit(const void* base, int dtype, size_t idx) {
+    return dtype == COLINFER_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx])
+                                  : __ldg(reinterpret_cast<const float*>(base) + idx);
+}
+__device__ __forceinline__ bool mask_allows(const int32_t* mrow, int t) {
+    return mrow == nullptr || (((uint32_t)__ldg(mrow + (t >> 5)) >> (t & 31)) & 1u);
+}
+// probability of one token under a row's processed distribution, in float64
+__device__ double token_prob(const colinfer_row_stats& st, float l, long long tok) {
+    if (st.status & COLINFER_ROW_DEGENERATE) return tok == st.argmax ? 1.0 : 0.0;
+    if (!(l >= st.lcut) || !(l > CI_NEG_INF) || st.mass_q == 0) return 0.0;
+    const float d = scale_logit(l, st.tc) - scale_logit(st.lmax, st.tc);
+    return exp((double)d) / ((double)st.mass_q * (1.0 / 1099511627776.0));
+}
+// residual mass of one token in units of 2^-40 (fp32 arithmetic, integer result)
+__device__ __forceinline__ u64 residual_q(float lt, float ld, const colinfer_row_stats& st, const colinfer_row_stats& sd,
+                                          float mt, float md, float inv_t, float inv_d) {
+    float p = 0.0f, q = 0.0f;
+    if (lt >= st.lcut && lt > CI_NEG_INF) p = exp2f((scale_logit(lt, st.tc) - mt) * CI_LOG2E) * inv_t;
+    if (ld >= sd.lcut && ld > CI_NEG_INF) q = exp2f((scale_logit(ld, sd.tc) - md) * CI_LOG2E) * inv_d;
+    const float rres = p - q;
+    return rres > 0.0f ? __float2ull_rn(rres * CI_MASS_SCALE) : 0ull;
+}
+
+__global__ void __launch_bounds__(VF_THREADS) k_verify_finish(const __grid_constant__ VerifyArgs a) {
+    __shared__ int s_j;
+    __shared__ int s_mode;                 // 0: token already known, 1: residual draw needed
+    __shared__ long long s_token;
+    __shared__ u64 wtot[VF_THREADS / 32];
+    const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k = a.k, V = a.V;
+    const colinfer_row_stats* st_t = a.st_t + (size_t)b * (k + 1);
+    const colinfer_row_stats* st_d = a.st_d + (size_t)b * k;
+    if (threadIdx.x == 0) {
+        const bool greedy = !(a.temperature[b] > 0.0f);
+        int j = 0;
+        for (; j < k; ++j) {
+            const long long d = a.draft_ids[(size_t)b * k + j];
+            bool ok;
+            if (greedy) ok = (d == st_t[j].argmax);
+            else if (d < 0 || d >= V) ok = false;
+            else {
+                const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
+                float lt = load_logit(a.tl, a.dtype, ((size_t)b * (k + 1) + j) * V + d);
+                float ld = load_logit(a.dl, a.dtype, ((size_t)b * k + j) * V + d);
+                if (!mask_allows(mrow, (int)d)) { lt = CI_NEG_INF; ld = CI_NEG_INF; }
+                const double p = token_prob(st_t[j], lt, d), q = token_prob(st_d[j], ld, d);
+                ok = (double)a.ua[(size_t)b * k + j] * q <= p;
+            }
+            if (!ok) break;
+        }
+        s_j = j;
+        if (greedy) { s_mode = 0; s_token = st_t[j].argmax; }
+        else if (j == k) { s_mode = 0; s_token = a.samp_t[(size_t)b * (k + 1) + k]; }
+        else if ((st_t[j].status | st_d[j].status) & (COLINFER_ROW_DEGENERATE | COLINFER_ROW_TIMEOUT)) {
+            s_mode = 0; s_token = a.samp_t[(size_t)b * (k + 1) + j];
+        } else s_mode = 1;
+    }
+    __syncthreads();
+    const int j = s_j;
+    if (s_mode == 1) {
+        const colinfer_row_stats st = st_t[j], sd = st_d[j];
+        const float mt = scale_logit(st.lmax, st.tc), md = scale_logit(sd.lmax, sd.tc);
+        const float inv_t = (float)(1099511627776.0 / (double)st.mass_q), inv_d = (float)(1099511627776.0 / (double)sd.mass_q);
+        const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
+        const size_t bt = ((size_t)b * (k + 1) + j) * V, bd = ((size_t)b * k + j) * V;
+        const int nwarps = VF_THREADS / 32;
+        const int reg = (((V + 31) / 32 + nwarps - 1) / nwarps) * 32;
+        const int lo = min(warp * reg, V), hi = min(lo + reg, V);
+        u64 acc = 0;
+        for (int i = lo + lane; i < hi; i += 32) {
+            if (mask_allows(mrow, i))
+                acc += residual_q(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i), st, sd, mt, md, inv_t, inv_d);
+        }
+        const u64 wt = warp_sum_u64(acc);
+        if (lane == 0) wtot[warp] = wt;
+        if (threadIdx.x == 0) s_token = -1;
+        __syncthreads();
+        u64 total = 0, woff = 0;
+        for (int w = 0; w < nwarps; ++w) { if (w < warp) woff += wtot[w]; total += wtot[w]; }
+        if (total == 0) {
+            if (threadIdx.x == 0) s_token = a.samp_t[(size_t)b * (k + 1) + j];   // no residual mass: draw from p_j
+        } else {
+            double t = ceil((double)a.us[(size_t)b * (k + 1) + j] * (double)total);
+            u64 target = t <= 1.0 ? 1ull : (u64)t;
+            if (target > total) target = total;
+            if (woff < target && target <= woff + wt) {
+                u64 run = woff;
+                for (int i0 = lo; i0 < hi; i0 += 32) {
+                    const int i = i0 + lane;
+                    u64 v = 0;
+                    if (i < hi && mask_allows(mrow, i))
+                        v = residual_q(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i), st, sd, mt, md, inv_t, inv_d);
+                    const u64 incl = warp_incl_scan_u64(v, lane);
+                    const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
+                    if (hit) {
+                        if (lane == __ffs(hit) - 1) s_token = i;
+                        break;
+                    }
+                    run += __shfl_sync(0xffffffffu, incl, 31);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        int64_t* o = a.out_tok + (size_t)b * (k + 1);
+        for (int i = 0; i <= k; ++i) o[i] = i < j ? a.draft_ids[(size_t)b * k + i] : -1;
+        o[j] = s_token;
+        a.n[b] = j + 1;
+    }
+}
+
+extern "C" int64_t colinfer_spec_verify_stats_bytes(int B, int k) { return (int64_t)B * (2 * k + 1) * (int64_t)sizeof(colinfer_row_stats); }
+extern "C" int64_t colinfer_spec_verify_ids_bytes(int B, int k) { return (int64_t)B * (k + 1) * 8; }
+
+extern "C" int colinfer_spec_verify(const void* target_logits, const void* draft_logits, int dtype, const int32_t* mask,
+                                    int W, const colinfer_sampler_params* params, const int64_t* draft_ids,
+                                    const float* ua, const float* us, int64_t* out_tok, int32_t* n,
+                                    colinfer_row_stats* scratch_stats, int64_t* scratch_ids, int B, int k, int V,
+                                    void* stream) {
+    if (!target_logits || !draft_logits || !params || !draft_ids || !ua || !us || !out_tok || !n || !scratch_stats ||
+        !scratch_ids || B < 0 || k < 1 || V <= 0)
+        return (int)cudaErrorInvalidValue;
+    if (params->history != nullptr) return (int)cudaErrorInvalidValue;   // penalties are not part of the verify step
+    if (B == 0) return 0;
+    colinfer_row_stats* st_t = scratch_stats;
+    colinfer_row_stats* st_d = scratch_stats + (size_t)B * (k + 1);
+    // target rows: statistics and the plain draw of every row with its sampling uniform
+    int e = colinfer_sample(target_logits, dtype, mask, k + 1, W, params, nullptr, 0, us, scratch_ids, st_t, nullptr,
+                            B, k + 1, V, 0, stream);
+    if (e) return e;
+    // draft rows: statistics only (the first k mask rows of each slot apply)
+    e = colinfer_sample(draft_logits, dtype, mask, k + 1, W, params, nullptr, 0, nullptr, nullptr, st_d, nullptr,
+                        B, k, V, 0, stream);
+    if (e) return e;
+    VerifyArgs a;
+    a.tl = target_logits; a.dl = draft_logits; a.dtype = dtype; a.mask = mask; a.W = W;
+    a.temperature = params->temperature; a.draft_ids = draft_ids; a.ua = ua; a.us = us;
+    a.st_t = st_t; a.st_d = st_d; a.samp_t = scratch_ids; a.out_tok = out_tok; a.n = n; a.B = B; a.k = k; a.V = V;
+    k_verify_finish<<<B, VF_THREADS, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int colinfer_version(void) { return 100; }

@@ -1,0 +1,131 @@
+/* colinfer_b200.h -- C ABI of the B200 (sm_100a) logits -> token path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA stream it is given (a cudaStream_t
+ * passed as void*), performs no host synchronisation and no allocation (except where stated), and returns a
+ * cudaError_t value as int (0 = success; cudaErrorInvalidValue = 1 for a bad shape, as the reference's launch_*
+ * functions do, csrc/sampling.cu:79, 112).  Inputs are borrowed, outputs are caller-allocated.  No entry point ever
+ * traps or asserts on the device: anomalies are reported through the optional per-row status words.
+ *
+ * "Reference" citations name files of the colinfer tree (engine/..., csrc/...).
+ */
+#ifndef COLINFER_B200_H
+#define COLINFER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Per-slot sampling parameters: the device buffers of the reference's SamplerParams (engine/runtime/sampler.py:23-31),
+ * each [B], plus this project's optional penalty fields (NULL = neutral). */
+typedef struct colinfer_sampler_params {
+    const float*   temperature;        /* [B]  <= 0 selects the argmax of the slot's rows */
+    const int32_t* top_k;              /* [B]  <= 0 or >= V disables top-k */
+    const float*   top_p;              /* [B]  >= 1 disables top-p */
+    const float*   log_min_p;          /* [B]  -inf disables min-p */
+    const int64_t* seed;               /* [B]  may be NULL when explicit uniforms are passed */
+    const float*   repetition_penalty; /* [B] or NULL (= 1) */
+    const float*   presence_penalty;   /* [B] or NULL (= 0) */
+    const float*   frequency_penalty;  /* [B] or NULL (= 0) */
+    const int32_t* history;            /* [B, hist_stride] token ids of each slot, or NULL */
+    const int32_t* hist_len;           /* [B] valid ids per slot, or NULL (= hist_stride) */
+    int32_t        hist_stride;
+} colinfer_sampler_params;
+
+/* Per-row description of the processed distribution, written by colinfer_sample when `stats` is not NULL.
+ * The kept set of the row is { t : logit'(t) >= lcut } (logit' = after penalties and mask) and
+ * P(t) = exp(logit'(t) / tc - lmax / tc) / (mass_q * 2^-40) on that set. */
+typedef struct colinfer_row_stats {
+    float    lmax;      /* largest logit' of the row */
+    float    lcut;      /* smallest kept logit' value (a threshold; -inf keeps all) */
+    float    tc;        /* max(temperature, 1e-6) */
+    int32_t  status;    /* COLINFER_ROW_* bits */
+    int64_t  argmax;    /* lowest index of the largest logit' */
+    uint64_t mass_q;    /* kept mass in units of 2^-40 */
+} colinfer_row_stats;
+
+enum {
+    COLINFER_ROW_DEGENERATE = 1,  /* no finite maximum (every token masked, or an infinite logit): argmax emitted */
+    COLINFER_ROW_TIMEOUT    = 2,  /* a bounded on-chip wait gave up; the row's outputs are undefined */
+    COLINFER_ROW_HIST_SLOW  = 4   /* more distinct history ids in one vocabulary slice than the fast table holds */
+};
+
+enum { COLINFER_F32 = 0, COLINFER_BF16 = 1 };
+
+/* Flags of colinfer_sample. */
+enum {
+    COLINFER_FORCE_DISTRIBUTION = 1  /* build the distribution even for temperature <= 0 (processed_probs does) */
+};
+
+/* Replaces ops().philox_uniform (csrc/sampling.cu:25-35, csrc/bindings.cpp:538-544):
+ * out[b, i] = U(0, 1] of Philox4x32-10 keyed by mix(seed[b]) at counter offset[b] + i.  out is [B, n] fp32. */
+int colinfer_philox_uniform(const int64_t* seed, const int64_t* offset, float* out, int B, int n, void* stream);
+
+/* Replaces apply_mask (engine/runtime/sampler.py:50-56): out = logits with every token whose bit (t % 32 of int32 word
+ * t / 32) is clear set to -inf.  logits, out: [rows, V] fp32 (out may alias logits); mask: [rows, W] int32, W >= ceil(V/32). */
+int colinfer_apply_mask(const float* logits, const int32_t* mask, float* out, int64_t rows, int V, int W, void* stream);
+
+/* Replaces draw / sample (engine/spec/accept.py:43-52, engine/runtime/sampler.py:59-62) fused with apply_mask and the
+ * penalties: one pass over HBM per row.
+ *   logits  [B, R, V] fp32 or bf16 (dtype), contiguous
+ *   mask    [B, mask_rows, W] int32 or NULL; row r of slot b uses mask[b, r]
+ *   pos     [B] int32 or int64 (pos_is_i64) device positions: row r draws the uniform at counter pos[b] + r
+ *   u       [B, R] explicit uniforms in (0, 1], or NULL to use Philox(seed, pos)
+ *   out_ids [B, R] int64 (may be NULL when only stats are wanted; then u, pos and seed may be NULL too)
+ *   stats   [B, R] or NULL;  status [B, R] int32 or NULL */
+int colinfer_sample(const void* logits, int dtype, const int32_t* mask, int mask_rows, int W,
+                    const colinfer_sampler_params* params, const void* pos, int pos_is_i64, const float* u,
+                    int64_t* out_ids, colinfer_row_stats* stats, int32_t* status,
+                    int B, int R, int V, int flags, void* stream);
+
+/* Replaces processed_probs (engine/spec/accept.py:23-33).  logits [R, V] fp32; temperature, top_k, top_p, log_min_p:
+ * 1-element device arrays; out [R, V] fp32 renormalised probabilities; scratch: R colinfer_row_stats (device). */
+int colinfer_processed_probs(const float* logits, const float* temperature, const int32_t* top_k, const float* top_p,
+                             const float* log_min_p, float* out, colinfer_row_stats* scratch, int R, int V, void* stream);
+
+/* Replaces inverse_cdf (engine/spec/accept.py:36-40): out[r] = #{ j : cumsum(P[r])_j < u[r] * sum(P[r]) }, clamped to
+ * V - 1.  P [R, V] fp32, u [R], out [R] int64. */
+int colinfer_inverse_cdf(const float* P, const float* u, int64_t* out, int R, int V, void* stream);
+
+/* Replaces the accept / bonus / stop-cut lines of the speculative cycle (engine/spec/mtp.py:406-415, 422-423;
+ * engine/spec/mtp4.py:538-547).  pred, tok: [B, k1] int64 (k1 = k + 1; tok[:, 1:] are the drafts); stop_ids [B, S]
+ * int64 (-1 = unused) or NULL; active [B] int32 or NULL (= 1).  out_tok [B, k1] int64, n [B] int32. */
+int colinfer_spec_accept(const int64_t* pred, const int64_t* tok, const int64_t* stop_ids, const int32_t* active,
+                         int64_t* out_tok, int32_t* n, int B, int k1, int S, void* stream);
+
+/* Rejection verify with the (p - q)+ residual resample (no counterpart in the reference, which accepts by exact match;
+ * semantics: accept draft i iff ua[i] * q_i(d_i) <= p_i(d_i); at the first rejection j emit a draw from
+ * normalize(max(p_j - q_j, 0)) with us[j]; if none is rejected emit a draw from p_k with us[k]; temperature <= 0 uses
+ * the argmax rule).  target_logits [B, k+1, V], draft_logits [B, k, V] (dtype), mask [B, k+1, W] or NULL (applies to
+ * both), draft_ids [B, k] int64, ua [B, k], us [B, k+1].  scratch: B * (2k + 1) colinfer_row_stats and B * (k + 1)
+ * int64 (device).  out_tok [B, k+1] int64 (accepted drafts, then the emitted token, then -1), n [B] int32 = accepted + 1. */
+int colinfer_spec_verify(const void* target_logits, const void* draft_logits, int dtype, const int32_t* mask, int W,
+                         const colinfer_sampler_params* params, const int64_t* draft_ids, const float* ua,
+                         const float* us, int64_t* out_tok, int32_t* n, colinfer_row_stats* scratch_stats,
+                         int64_t* scratch_ids, int B, int k, int V, void* stream);
+
+/* Bytes of scratch_stats / scratch_ids that colinfer_spec_verify needs. */
+int64_t colinfer_spec_verify_stats_bytes(int B, int k);
+int64_t colinfer_spec_verify_ids_bytes(int B, int k);
+
+/* Geometry the sampler would use for a vocabulary (for tests and benchmarks): CTAs per row (thread-block cluster
+ * size), elements per CTA slice, dynamic shared memory per CTA, and whether the bulk-copy (TMA) load path applies. */
+typedef struct colinfer_geometry {
+    int32_t cluster;
+    int32_t slice_elems;
+    int32_t smem_bytes;
+    int32_t bulk_copy;
+} colinfer_geometry;
+int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geometry* out);
+
+/* Test hook: force the cluster size (1, 2, 4 or 8; 0 = automatic) of later colinfer_sample calls of this process. */
+int colinfer_set_cluster_override(int cluster);
+
+/* Library version (major * 100 + minor). */
+int colinfer_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
