@@ -1,0 +1,269 @@
+"""Benchmark of the logits -> token path: sampled rows/s and achieved HBM bandwidth at vocabulary 151,936.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+Workload (config.workload): the batched sampling sweep -- fp32 logits [B, 151936] ~ N(0, 2^2), per-row histories of
+2,048 ids with repetition / presence / frequency penalties, per-row temperature in U[0.5, 1.2], top_k in {0, 20, 100},
+top_p in U[0.8, 1.0], Philox draws keyed by (seed, position) -- seeded synthetic tensors standing in for model logits.
+One step = one fused draw() over the batch (B rows per GPU; with N GPUs every rank holds its own B rows -- weak
+scaling -- and the sampled ids are all-gathered over NCCL inside the timed region).  The batch (B x 608 KB = 630 MB at
+B = 1024) is larger than the 126 MB L2, so no step is served from cache.
+
+value   whole-job rows/s with inputs resident in HBM (CUDA events on the launching stream, max over ranks).
+e2e     the same through the public API with HOST buffers: every step copies the step's logits, histories and
+        positions from pinned host memory to the device and the sampled ids back.
+roofline  algorithmic bytes per row (one read of every input + outputs) x rows / measured kernel time, against the
+        measured HBM copy rate of MEASURED_PEAKS.json (fallback 6,650 GB/s).
+cpu_baseline  the reference's torch path restated for the CPU (oracle/torch_cpu_path.py), timed on this box's host
+        cores on a bounded sample of the same batch.  --impl reference times only that.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+V = 151_936
+HIST = 2048
+CPU_SAMPLE_ROWS = 256
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_sample launch divided by its rows (ncu capture summarised in
+# profiles/k_sample_config3.md); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_ROW = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_baseline_rows_per_s(w, reps: int, warm: int):
+    """The reference's torch path on host cores over the first CPU_SAMPLE_ROWS rows of the batch."""
+    import torch
+    from oracle import torch_cpu_path as T
+    n = min(CPU_SAMPLE_ROWS, w["logits"].shape[0])
+    sub = {k: (v[:n] if isinstance(v, torch.Tensor) else v) for k, v in w.items() if k != "params"}
+    sub["params"] = {k: v[:n] for k, v in w["params"].items()}
+    times = []
+    for i in range(warm + reps):
+        t0 = time.perf_counter()
+        T.draw(sub["logits"], sub["params"], sub["pos"], chunk=8)
+        if i >= warm:
+            times.append(time.perf_counter() - t0)
+    return n, times, torch.get_num_threads()
+
+
+def run_reference(args):
+    """--impl reference: the CPU restatement of the reference path, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from colinfer_b200 import workloads as wl
+    w = wl.config3(CPU_SAMPLE_ROWS, V=V, H=HIST)
+    n, times, threads = cpu_baseline_rows_per_s(w, reps=args.steps, warm=args.warmup)
+    total = sum(times)
+    value = n * len(times) / total
+    line = {"impl": "reference", "metric": "sampled rows/s", "value": value, "unit": "rows/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"config3 batched sampling sweep, vocab {V}, history {HIST}", "rows_per_step": n},
+            "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
+                             "sample": f"{n} rows of the batch per step (torch CPU restatement of the reference path, "
+                                       f"{os.cpu_count()} host cpus)"},
+            "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1024, help="rows per GPU")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from colinfer_b200 import _lib, workloads as wl
+    from colinfer_b200.sharding import gather_ids
+    from colinfer_b200.spec.accept import draw
+
+    _lib.lib()                                             # fail loudly if the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B = args.batch
+    n_rows = B * world
+
+    # every rank generates its own B rows (same distribution, rank-dependent seed offset through the row seeds)
+    w = wl.config3(B, V=V, H=HIST)
+    if rank:
+        g = torch.Generator().manual_seed(7 + rank)
+        w["logits"] = torch.randn(B, 1, V, generator=g) * 2.0
+        w["params"]["seed"] = w["params"]["seed"] + rank * 1_000_003
+    sp = wl.sampler_params(w["params"], V, dev)
+    logits = w["logits"].to(dev)
+    pos = w["pos"].to(dev)
+    bytes_row = wl.bytes_per_row(V, 4, False, HIST)
+
+    def step():
+        ids = draw(logits, sp, pos)
+        pos.add_(1)
+        return gather_ids(ids, n_rows) if world > 1 else ids
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            ids = step()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    # kernel-only time of the same launches (no gather), events on the launching stream
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    k0.record()
+    for _ in range(args.steps):
+        draw(logits, sp, pos)
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / args.steps
+
+    # end to end: host buffers in, ids out, every step
+    h_logits = w["logits"].pin_memory()
+    h_hist = w["params"]["history"].pin_memory()
+    h_pos = w["pos"].pin_memory()
+    h_ids = torch.empty(B, 1, dtype=torch.int64).pin_memory()
+    d_logits, d_hist, d_pos = torch.empty_like(logits), torch.empty_like(sp.history), torch.empty_like(pos)
+    sp_e = sp.view(0, B)
+    sp_e.history = d_hist
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        d_logits.copy_(h_logits, non_blocking=True)
+        d_hist.copy_(h_hist, non_blocking=True)
+        d_pos.copy_(h_pos, non_blocking=True)
+        out = draw(d_logits, sp_e, d_pos)
+        out = gather_ids(out, n_rows) if world > 1 else out
+        h_ids.copy_(out[:B] if world > 1 else out, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    x0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    x1.record()
+    barrier()
+    e2e_ms = x0.elapsed_time(x1)
+
+    t = torch.tensor([ms, kernel_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, kernel_ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        achieved = bytes_row * B / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": "sampled rows/s", "value": n_rows * args.steps / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"config3 batched sampling sweep: fp32 logits [{B}, {V}] per GPU, history {HIST}, "
+                                   "penalties, T~U[0.5,1.2], top_k in {0,20,100}, top_p~U[0.8,1.0]",
+                       "rows_per_gpu": B, "vocab": V, "l2": "inputs (630 MB per GPU) larger than L2, no flush needed",
+                       "sharding": f"rows x{world}, ids all-gathered" if world > 1 else "single GPU"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind} copy rate", "frac_of_nominal_8000": achieved / 8000.0,
+                         "bytes_per_row": bytes_row, "kernel": "k_sample", "kernel_ms": kernel_ms,
+                         "traffic": None if NCU_TRAFFIC_BYTES_PER_ROW is None else NCU_TRAFFIC_BYTES_PER_ROW * B},
+            "e2e": {"value": n_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "steps": e2e_steps,
+                    "h2d_bytes_per_step": int(h_logits.numel() * 4 + h_hist.numel() * 4 + h_pos.numel() * 4),
+                    "d2h_bytes_per_step": int(h_ids.numel() * 8)},
+            "gpu_launches": args.steps,
+            "clocks": clk.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            n, times, threads = cpu_baseline_rows_per_s(w, reps=3, warm=1)
+            line["cpu_baseline"] = {"value": n / statistics.median(times), "unit": "rows/s", "cores": threads, "kind": "port",
+                                    "sample": f"first {n} rows of the batch, median of 3 (torch CPU restatement of the "
+                                              f"reference path, {os.cpu_count()} host cpus)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

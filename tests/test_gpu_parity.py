@@ -1,0 +1,599 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle and with the reference's own pins.
+
+Integer work (Philox words, masks, argmax, accept decisions, token ids) is compared bit for bit.  Sampled tokens must be
+identical to the oracle's whenever the oracle's decision margins (distance of u * mass from the nearest CDF step, of
+the top-p target from the nearest cumulative-mass step) exceed MARGIN; probabilities are compared at 1e-5 relative.
+"""
+import ctypes as C
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from colinfer_b200 import _lib
+from colinfer_b200 import workloads as wl
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+MARGIN = 1e-6          # fp32 exponentials differ from float64 ones by ~1e-7 relative
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_cuda():
+    assert torch.cuda.is_available(), "the gpu tests need a CUDA device"
+    _lib.lib()
+    yield
+    _lib.lib().colinfer_set_cluster_override(0)
+
+
+def mods():
+    from colinfer_b200.kernels import ops
+    from colinfer_b200.runtime.sampler import SamplerParams, apply_mask, sample
+    from colinfer_b200.spec.accept import draw, inverse_cdf, processed_probs
+    from colinfer_b200.spec.verify import spec_accept, spec_verify
+    return dict(ops=ops, SamplerParams=SamplerParams, apply_mask=apply_mask, sample=sample, draw=draw,
+                inverse_cdf=inverse_cdf, processed_probs=processed_probs, spec_accept=spec_accept, spec_verify=spec_verify)
+
+
+def np_params(p):
+    d = {k: v.cpu().numpy() for k, v in p.items() if k not in ("history", "hist_len")}
+    return d
+
+
+def check_tokens(got, want, info, what=""):
+    """Token identity, except where the oracle says the decision was closer than MARGIN to flipping."""
+    got, want = np.asarray(got).reshape(-1), np.asarray(want).reshape(-1)
+    bad = np.flatnonzero(got != want)
+    for i in bad:
+        m = min(info[i]["margin"], info[i]["margin_top_p"])
+        assert m < MARGIN, f"{what}: row {i}: got {got[i]}, oracle {want[i]}, margin {m:.3e}"
+    assert len(bad) <= max(1, len(got) // 200), f"{what}: {len(bad)} boundary rows of {len(got)}"
+    return len(bad)
+
+
+def run_workload(w, V, cluster=0, use_philox=False):
+    """draw() on a workload dict vs the oracle.  Returns (#boundary mismatches, tokens)."""
+    m = mods()
+    _lib.lib().colinfer_set_cluster_override(cluster)
+    dev = "cuda"
+    logits = w["logits"].to(dev)
+    sp = wl.sampler_params(w["params"], V, dev)
+    mask = w.get("mask")
+    u = w.get("u")
+    pos = w["pos"].to(dev)
+    kw = dict(mask=None if mask is None else mask.to(dev))
+    if u is not None and not use_philox:
+        kw["u"] = u.to(dev)
+    out, st = m["draw"](logits, sp, pos, status=True, **kw)
+    torch.cuda.synchronize()
+    pr = np_params(w["params"])
+    hist = w["params"].get("history")
+    want, info = O.draw(logits.float().cpu().numpy(), pr, w["pos"].numpy(),
+                        mask=None if mask is None else mask.numpy(),
+                        history=None if hist is None else hist.numpy(),
+                        hist_len=None if hist is None else w["params"]["hist_len"].numpy(),
+                        u=None if (u is None or use_philox) else u.numpy())
+    assert (st.cpu().numpy() & ~_lib.ROW_HIST_SLOW == 0).all(), st.unique()
+    nb = check_tokens(out.cpu().numpy(), want, info, w.get("name", ""))
+    return nb, out
+
+
+# ------------------------------------------------------------------------------------------------ Philox
+def test_philox_uniform_bit_exact_vs_oracle():
+    m = mods()
+    seed = torch.tensor([7, 7, 123, -5, 2**62 - 1], device="cuda")
+    off = torch.tensor([0, 0, 5 << 20, (1 << 40) + 3, 2**33 + 1], device="cuda")
+    for n in (1, 3, 16, 4096):
+        u = torch.empty(5, n, device="cuda")
+        m["ops"]().philox_uniform(seed, off, u)
+        assert np.array_equal(u.cpu().numpy(), O.philox_uniform(seed.cpu().numpy(), off.cpu().numpy(), n))
+    assert float(u.min()) > 0.0 and float(u.max()) <= 1.0
+    with pytest.raises(RuntimeError):
+        m["ops"]().philox_uniform(seed[:2], off, u)             # shape check, as the reference's binding raises
+
+
+def test_philox_uniform_bit_exact_vs_reference_kernel():
+    """The reference's own csrc/sampling.cu, built unmodified into oracle/_ref by oracle/Makefile."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_sampling.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/libref_sampling.so was not built (needs the reference checkout at build time)")
+    ref = C.CDLL(path)
+    fn = getattr(ref, "_Z21launch_philox_uniformPKlS0_PfiiP11CUstream_st")
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    m = mods()
+    g = torch.Generator().manual_seed(0)
+    B = 64
+    seed = torch.randint(-2**62, 2**62, (B,), generator=g).cuda()
+    off = torch.randint(0, 2**40, (B,), generator=g).cuda()
+    for n in (1, 9, 16, 700):
+        a, b = torch.empty(B, n, device="cuda"), torch.zeros(B, n, device="cuda")
+        m["ops"]().philox_uniform(seed, off, a)
+        assert fn(seed.data_ptr(), off.data_ptr(), b.data_ptr(), B, n, torch.cuda.current_stream().cuda_stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------------------------------------ mask
+def test_apply_mask_matches_reference_vectors(golden):
+    m = mods()
+    out = m["apply_mask"](torch.from_numpy(golden["mask_logits"]).cuda(), torch.from_numpy(golden["mask_words"]).cuda())
+    assert np.array_equal(out.cpu().numpy(), golden["mask_out"])
+
+
+@pytest.mark.parametrize("V", [1, 31, 33, 1000, 4099, 151936])
+def test_apply_mask_sizes_and_identity(V):
+    m = mods()
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(2, 2, V, generator=g)
+    allowed = torch.rand(2, 2, V, generator=g) < 0.4
+    mask = wl.pack_mask(allowed)
+    out = m["apply_mask"](logits.cuda(), mask.cuda()).cpu()
+    assert np.array_equal(out.numpy(), O.apply_mask(logits.numpy(), mask.numpy()))
+    ones = torch.full_like(mask, -1)
+    assert torch.equal(m["apply_mask"](logits.cuda(), ones.cuda()).cpu(), logits)       # all-ones: identity, new tensor
+
+
+# ------------------------------------------------------------------------------------------------ draw: small grids
+GRID = [(0.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.7, 20, 1.0, 0.0), (1.0, 0, 0.8, 0.0), (1.3, 50, 0.9, 0.05),
+        (0.5, 1, 1.0, 0.0), (1.0, 0, 1e-4, 0.0), (1e-9, 0, 0.9, 0.0), (2.0, 5000, 0.999, 0.3)]
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+@pytest.mark.parametrize("V", [1, 31, 33, 1000, 4099])
+def test_draw_vs_oracle_grid(V, cluster):
+    m = mods()
+    _lib.lib().colinfer_set_cluster_override(cluster)
+    g = torch.Generator().manual_seed(100 + V)
+    B, R = len(GRID), 2
+    logits = torch.randn(B, R, V, generator=g) * 2
+    sp = m["SamplerParams"](B, V, "cuda")
+    for b, (T, k, tp, mp) in enumerate(GRID):
+        sp.set(b, temperature=T, top_k=k, top_p=tp, min_p=mp, seed=b)
+    u = wl.open_unit(g, B, R)
+    allowed = torch.rand(B, R, V, generator=g) < 0.5
+    allowed[..., V // 2] = True
+    mask = wl.pack_mask(allowed)
+    H = 48
+    hist = torch.randint(0, V, (B, H), generator=g, dtype=torch.int32)
+    hist[:, :8] = hist[:, 8:16]                                   # duplicates
+    hist[:, 20] = V + 5                                            # out of range: skipped
+    hist[:, 21] = -3
+    sp.set_history(hist.cuda(), torch.full((B,), H - 4, dtype=torch.int32, device="cuda"))
+    for b in range(B):
+        sp.set_penalties(b, 1.3, 0.4, 0.25)
+    out, st = m["draw"](logits.cuda(), sp, torch.zeros(B, dtype=torch.int32, device="cuda"), u=u.cuda(), mask=mask.cuda(),
+                        status=True)
+    pr = dict(temperature=sp.temperature.cpu().numpy(), top_k=sp.top_k.cpu().numpy(), top_p=sp.top_p.cpu().numpy(),
+              log_min_p=sp.log_min_p.cpu().numpy(), repetition_penalty=sp.repetition_penalty.cpu().numpy(),
+              presence_penalty=sp.presence_penalty.cpu().numpy(), frequency_penalty=sp.frequency_penalty.cpu().numpy())
+    want, info = O.draw(logits.numpy(), pr, None, mask=mask.numpy(), history=hist.numpy(),
+                        hist_len=np.full(B, H - 4), u=u.numpy())
+    assert (st == 0).all()
+    check_tokens(out.cpu().numpy(), want, info, f"V={V} cluster={cluster}")
+
+
+def test_masked_argmax_picks_lowest_allowed_index():
+    """Reference tests/test_grammar.py:116-160 (the LowHalf stub): next token has logit 10, all others 0; outside the
+    mask the argmax is the lowest allowed token."""
+    m = mods()
+    V = 64
+    logits = torch.zeros(3, 1, V)
+    logits[0, 0, 40] = 10
+    logits[1, 0, 5] = 10
+    logits[2, 0, 31] = 10
+    mask = torch.zeros(3, 1, 2, dtype=torch.int32)
+    mask[:, :, 0] = -1
+    sp = m["SamplerParams"](3, V, "cuda")
+    out = m["draw"](logits.cuda(), sp, torch.zeros(3, dtype=torch.int32, device="cuda"), mask=mask.cuda())
+    assert out[:, 0].tolist() == [0, 5, 31]
+    masked = m["apply_mask"](logits.cuda(), mask.cuda())
+    assert masked.argmax(-1)[:, 0].tolist() == [0, 5, 31]
+
+
+def test_degenerate_rows_report_status_and_never_trap():
+    m = mods()
+    V = 200
+    logits = torch.randn(3, 1, V)
+    mask = torch.full((3, 1, 7), -1, dtype=torch.int32)
+    mask[0] = 0                                                    # nothing allowed
+    mask[1] = 0
+    mask[1, 0, 3] = 1 << 9                                         # exactly one token allowed: 105
+    sp = m["SamplerParams"](3, V, "cuda")
+    for b in range(3):
+        sp.set(b, temperature=1.0, top_k=10, top_p=0.9, seed=b)
+    out, st = m["draw"](logits.cuda(), sp, torch.zeros(3, dtype=torch.int32, device="cuda"), mask=mask.cuda(), status=True)
+    assert st[:, 0].tolist() == [_lib.ROW_DEGENERATE, 0, 0]
+    assert out[0, 0] == 0 and out[1, 0] == 105 and 0 <= out[2, 0] < V
+    assert m["draw"](torch.empty(0, 1, V, device="cuda"), m["SamplerParams"](0, V, "cuda"),
+                     torch.zeros(0, dtype=torch.int32, device="cuda")).shape == (0, 1)
+
+
+def test_neutral_penalties_are_a_bit_exact_no_op():
+    m = mods()
+    V, B = 4099, 6
+    g = torch.Generator().manual_seed(5)
+    logits = (torch.randn(B, 1, V, generator=g) * 2).cuda()
+    hist = torch.randint(0, V, (B, 300), generator=g, dtype=torch.int32).cuda()
+    pos = torch.arange(B, dtype=torch.int32, device="cuda")
+    outs = []
+    for with_hist in (False, True):
+        sp = m["SamplerParams"](B, V, "cuda")
+        for b in range(B):
+            sp.set(b, temperature=0.9 if b else 0.0, top_k=0, top_p=0.95, seed=b + 3)
+        if with_hist:
+            sp.set_history(hist)
+            sp.set_penalties(0, 1.0, 0.0, 0.0)
+        o, rs = m["draw"](logits, sp, pos, stats=True)
+        outs.append((o, rs))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_many_distinct_history_ids_use_the_slow_count_path():
+    """More than 2048 distinct history ids inside one vocabulary slice: counts come from scanning the history."""
+    m = mods()
+    V, H = 8192, 6000
+    _lib.lib().colinfer_set_cluster_override(1)
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(1, 1, V, generator=g) * 2
+    hist = torch.randint(0, V, (1, H), generator=g, dtype=torch.int32)
+    sp = m["SamplerParams"](1, V, "cuda")
+    sp.set(0, temperature=0.0)
+    sp.set_history(hist.cuda())
+    sp.set_penalties(0, 1.2, 0.3, 0.7)
+    out, st = m["draw"](logits.cuda(), sp, torch.zeros(1, dtype=torch.int32, device="cuda"), status=True)
+    want = O.argmax(O.penalties(logits[0, 0].numpy(), hist[0].numpy(), 1.2, 0.3, 0.7))
+    assert int(out) == want and int(st) == _lib.ROW_HIST_SLOW
+
+
+# ------------------------------------------------------------------------------------------------ processed_probs / inverse_cdf
+def test_processed_probs_known_answers():
+    """Reference tests/test_spec_accept.py:39-48."""
+    m = mods()
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]], device="cuda"))
+    one = lambda v, dt=torch.float32: torch.tensor([v], dtype=dt, device="cuda")  # noqa: E731
+    want = torch.tensor([0.625, 0.375, 0, 0], device="cuda")
+    p = m["processed_probs"](logits, one(1.0), one(2, torch.int32), one(1.0), one(float("-inf")))
+    torch.testing.assert_close(p[0], want, atol=1e-5, rtol=0)
+    p = m["processed_probs"](logits, one(1.0), one(4, torch.int32), one(0.7), one(float("-inf")))
+    torch.testing.assert_close(p[0], want, atol=1e-5, rtol=0)
+    p = m["processed_probs"](logits, one(1.0), one(4, torch.int32), one(1.0), one(math.log(0.4)))
+    torch.testing.assert_close(p[0], want, atol=1e-5, rtol=0)
+
+
+@pytest.mark.parametrize("V", [1000, 151936])
+@pytest.mark.parametrize("T,k,tp,mp", [(1.0, 0, 1.0, 0.0), (0.7, 20, 1.0, 0.0), (1.0, 0, 0.8, 0.0), (1.3, 50, 0.9, 0.05), (0.0, 0, 0.9, 0.0)])
+def test_processed_probs_vs_oracle(V, T, k, tp, mp):
+    m = mods()
+    g = torch.Generator().manual_seed(V + k)
+    logits = torch.randn(3, V, generator=g) * 2
+    prm = O.sampler_params_set(V, T, k, tp, mp)
+    one = lambda v, dt: torch.tensor([v], dtype=dt, device="cuda")  # noqa: E731
+    got = m["processed_probs"](logits.cuda(), one(float(prm["temperature"]), torch.float32), one(int(prm["top_k"]), torch.int32),
+                               one(float(prm["top_p"]), torch.float32), one(float(prm["log_min_p"]), torch.float32)).cpu().numpy()
+    for r in range(3):
+        pr = O.processed(logits[r].numpy(), prm["temperature"], prm["top_k"], prm["top_p"], prm["log_min_p"])
+        if pr["margin_top_p"] < MARGIN:
+            continue
+        want = pr["probs"]
+        assert np.array_equal(got[r] > 0, want > 1e-44), "support set"
+        nz = want > 1e-30
+        assert np.allclose(got[r][nz], want[nz], rtol=1e-5, atol=0)
+        assert abs(got[r].astype(np.float64).sum() - 1.0) < 1e-5
+
+
+def test_inverse_cdf_matches_reference_vectors(golden):
+    m = mods()
+    out = m["inverse_cdf"](torch.from_numpy(golden["icdf_P"]).cuda(), torch.from_numpy(golden["icdf_u"]).cuda())
+    assert np.array_equal(out.cpu().numpy(), golden["icdf_out"])
+    out = m["inverse_cdf"](torch.from_numpy(golden["icdf_W"]).cuda(), torch.from_numpy(golden["icdf_uw"]).cuda())
+    assert np.array_equal(out.cpu().numpy(), golden["icdf_wout"])
+
+
+def test_inverse_cdf_marginal_is_exact():
+    """Reference tests/test_spec_accept.py:12-21."""
+    m = mods()
+    torch.manual_seed(0)
+    V, trials = 50, 200000
+    P = torch.softmax(torch.randn(1, V, device="cuda") * 1.5, -1)
+    P[0, 7] = 0
+    P /= P.sum()
+    x = m["inverse_cdf"](P.expand(trials, V).contiguous(), torch.rand(trials, device="cuda").clamp_min(1e-7))
+    emp = torch.bincount(x, minlength=V).float() / trials
+    assert emp[7] == 0
+    assert 0.5 * (emp - P[0]).abs().sum().item() < 0.01
+
+
+# ------------------------------------------------------------------------------------------------ the reference's sampler tests
+def expected(logits, t, k, p, min_p):
+    """The reference's exact truncated softmax (tests/test_sampler.py:13-27), on the CPU in float64."""
+    z = logits.double() / t
+    probs = torch.softmax(z, -1)
+    keep = probs >= min_p * probs.max()
+    order = torch.argsort(z, descending=True)
+    keep_k = torch.zeros_like(keep)
+    keep_k[order[:k]] = True
+    keep &= keep_k
+    pr = torch.softmax(z.masked_fill(~keep, float("-inf")), -1)
+    srt, idx = torch.sort(pr, descending=True)
+    cut = (srt.cumsum(0) - srt) < p
+    final = torch.zeros_like(pr)
+    final[idx[cut]] = srt[cut]
+    return final / final.sum()
+
+
+@pytest.mark.parametrize("t,k,p,min_p", [(1.0, 0, 1.0, 0.0), (0.7, 20, 1.0, 0.0), (1.0, 0, 0.8, 0.0), (1.3, 50, 0.9, 0.05)])
+def test_distribution(t, k, p, min_p):
+    """Reference tests/test_sampler.py:30-49: 100k draws, nothing outside the allowed set, total variation < 0.03."""
+    m = mods()
+    V = 1000
+    torch.manual_seed(0)
+    base = torch.randn(V) * 2
+    B, rounds = 4000, 25
+    params = m["SamplerParams"](B, V, "cuda")
+    params.temperature.fill_(t)
+    params.top_k.fill_(k if k > 0 else V)
+    params.top_p.fill_(p)
+    params.log_min_p.fill_(math.log(min_p) if min_p > 0 else float("-inf"))
+    params.seed.copy_(torch.arange(B, device="cuda") * 7919)
+    counts = torch.zeros(V, device="cuda")
+    logits = base.cuda().expand(B, V).contiguous()
+    for r in range(rounds):
+        counts += torch.bincount(m["sample"](logits, params, torch.full((B,), r, device="cuda")), minlength=V).float()
+    emp = (counts / counts.sum()).cpu().double()
+    want = expected(base, t, k if k > 0 else V, p, min_p)
+    assert emp[want == 0].sum() == 0, "sampled a token outside the allowed set"
+    assert 0.5 * (emp - want).abs().sum().item() < 0.03
+
+
+def test_slot_independence():
+    """Reference tests/test_sampler.py:52-62."""
+    m = mods()
+    V = 1000
+    torch.manual_seed(3)
+    logits = torch.randn(2, V, device="cuda")
+    outs = []
+    for other_seed in (0, 12345):
+        p = m["SamplerParams"](2, V, "cuda")
+        p.set(0, temperature=1.0, seed=other_seed)
+        p.set(1, temperature=1.0, seed=9)
+        outs.append([int(m["sample"](logits, p, torch.full((2,), i, device="cuda"))[1]) for i in range(10)])
+    assert outs[0] == outs[1]
+
+
+def test_greedy_slots_and_seed_determinism():
+    """Reference tests/test_sampler.py:65-78."""
+    m = mods()
+    V = 1000
+    torch.manual_seed(1)
+    logits = torch.randn(3, V, device="cuda")
+    p = m["SamplerParams"](3, V, "cuda")
+    p.set(0, temperature=0.0)
+    p.set(1, temperature=1.0, seed=7)
+    p.set(2, temperature=1.0, seed=7)
+    pos = lambda i: torch.full((3,), i, device="cuda")  # noqa: E731
+    out = m["sample"](logits, p, pos(0))
+    assert out[0] == logits[0].argmax()
+    a = [int(m["sample"](logits, p, pos(i))[1]) for i in range(20)]
+    b = [int(m["sample"](logits, p, pos(i))[1]) for i in range(20)]
+    assert a == b and len(set(a)) > 1
+    assert [int(m["sample"](logits[[1, 1, 1]], p, pos(i))[2]) for i in range(20)] == a
+
+
+def test_captured_in_cuda_graph_follows_position():
+    """Reference tests/test_sampler.py:81-101: capturable, the position is read from device memory at replay."""
+    m = mods()
+    V = 1000
+    torch.manual_seed(2)
+    logits = torch.zeros(2, V, device="cuda")
+    p = m["SamplerParams"](2, V, "cuda")
+    p.set(0, temperature=1.0, seed=3)
+    p.set(1, temperature=1.0, seed=4)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    pos = torch.zeros(2, dtype=torch.int32, device="cuda")
+    with torch.cuda.stream(s):
+        m["sample"](logits, p, pos)
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = m["sample"](logits, p, pos)
+        pos += 1
+    draws = []
+    for _ in range(30):
+        g.replay()
+        draws.append(tuple(out.tolist()))
+    assert len(set(draws)) > 20
+
+
+def test_draw_rows_match_single_row_draws():
+    """Reference tests/test_spec_accept.py:24-36 (V = 248,320, R = 4): verifying k+1 rows at once draws what k+1
+    single-row steps draw at those positions."""
+    m = mods()
+    torch.manual_seed(1)
+    V, R = 248320, 4
+    logits = torch.randn(2, R, V, device="cuda") * 3
+    p = m["SamplerParams"](2, V, "cuda")
+    p.set(0, temperature=0.8, top_k=20, top_p=0.95, seed=11)
+    p.set(1, temperature=1.0, top_p=0.9, min_p=0.02, seed=12)
+    pos = torch.tensor([100, 7], device="cuda", dtype=torch.int32)
+    many = m["draw"](logits, p, pos)
+    one = torch.stack([m["draw"](logits[:, r:r + 1].contiguous(), p, pos + r)[:, 0] for r in range(R)], 1)
+    assert torch.equal(many, one)
+    # and the oracle agrees, Philox uniforms included
+    pr = dict(temperature=p.temperature.cpu().numpy(), top_k=p.top_k.cpu().numpy(), top_p=p.top_p.cpu().numpy(),
+              log_min_p=p.log_min_p.cpu().numpy(), seed=p.seed.cpu().numpy())
+    want, info = O.draw(logits.cpu().numpy(), pr, pos.cpu().numpy())
+    check_tokens(many.cpu().numpy(), want, info, "V=248320")
+
+
+# ------------------------------------------------------------------------------------------------ benchmark configurations
+def test_config0_single_row():
+    w = wl.config0()
+    nb, out = run_workload(w, wl.V_QWEN)
+    assert nb == 0
+    # greedy on the same logits (temperature 0): the argmax of the penalised row
+    w["params"]["temperature"] = torch.zeros(1)
+    nb, out = run_workload(w, wl.V_QWEN)
+    assert nb == 0
+    # and with the Philox uniform at (seed, pos) instead of the explicit one
+    w = wl.config0()
+    assert run_workload(w, wl.V_QWEN, use_philox=True)[0] == 0
+
+
+def test_config1_grammar_mask():
+    w = wl.config1()
+    assert run_workload(w, wl.V_QWEN)[0] == 0
+    w["params"]["temperature"] = torch.zeros(1)
+    nb, out = run_workload(w, wl.V_QWEN)
+    allowed = O.mask_bits(w["mask"][0, 0].numpy(), wl.V_QWEN)
+    assert nb == 0 and allowed[int(out)]
+
+
+@pytest.mark.parametrize("B", [8, 64])
+def test_config3_batched_sweep_vs_oracle(B):
+    w = wl.config3(B)
+    run_workload(w, wl.V_QWEN, use_philox=True)
+
+
+def test_config3_full_batch_properties():
+    """B = 1024 at full size: deterministic across launches, independent of the batch a row rides in (row invariance),
+    and equal to the oracle on a sample of rows."""
+    m = mods()
+    B, V = 1024, wl.V_QWEN
+    w = wl.config3(B)
+    dev = "cuda"
+    logits = w["logits"].to(dev)
+    sp = wl.sampler_params(w["params"], V, dev)
+    pos = w["pos"].to(dev)
+    a = m["draw"](logits, sp, pos)
+    b = m["draw"](logits, sp, pos)
+    assert torch.equal(a, b)
+    rows = [0, 1, 17, 333, 512, 1023]
+    for r in rows:
+        one = m["draw"](logits[r:r + 1].contiguous(), sp.view(r, r + 1), pos[r:r + 1].contiguous())
+        assert torch.equal(one[0], a[r])
+    perm = torch.randperm(B, generator=torch.Generator().manual_seed(0))
+    sp2 = wl.sampler_params({k: v[perm] for k, v in w["params"].items()}, V, dev)
+    c = m["draw"](logits[perm.to(dev)].contiguous(), sp2, pos[perm.to(dev)].contiguous())
+    assert torch.equal(c, a[perm.to(dev)])
+    sub = {k: (v[rows] if isinstance(v, torch.Tensor) and v.size(0) == B else v) for k, v in w.items() if k != "params"}
+    sub["params"] = {k: v[rows] for k, v in w["params"].items()}
+    want, info = O.draw(sub["logits"].numpy(), np_params(sub["params"]), sub["pos"].numpy(),
+                        history=sub["params"]["history"].numpy(), hist_len=sub["params"]["hist_len"].numpy())
+    check_tokens(a[rows].cpu().numpy(), want, info, "config3 B=1024 sample")
+    # every sampled token lies in [0, V) and greedy rows would be the penalised argmax
+    assert int(a.min()) >= 0 and int(a.max()) < V
+
+
+def test_config4_bf16_large_vocab():
+    w = wl.config4(B=6)
+    nb, out = run_workload(w, wl.V_LARGE, use_philox=True)
+    allowed = np.stack([O.mask_bits(w["mask"][b, 0].numpy(), wl.V_LARGE) for b in range(6)])
+    assert all(allowed[b, int(out[b, 0])] for b in range(6))
+
+
+# ------------------------------------------------------------------------------------------------ speculative verify
+def test_spec_accept_vs_oracle():
+    m = mods()
+    g = torch.Generator().manual_seed(11)
+    for k in (1, 3, 7, 15):
+        B = 257
+        pred = torch.randint(0, 6, (B, k + 1), generator=g)
+        tok = torch.randint(0, 6, (B, k + 1), generator=g)
+        agree = torch.rand(B, k, generator=g) < 0.7
+        tok[:, 1:] = torch.where(agree, pred[:, :k], tok[:, 1:])
+        stop = torch.randint(-1, 8, (B, 8), generator=g)
+        stop[stop > 5] = -1
+        active = (torch.rand(B, generator=g) < 0.9).int()
+        out, n = m["spec_accept"](pred.cuda(), tok.cuda(), stop.cuda(), active.cuda())
+        want_out, want_n = O.spec_accept(pred.numpy(), tok.numpy(), stop.numpy(), active.numpy())
+        assert np.array_equal(n.cpu().numpy(), want_n) and np.array_equal(out.cpu().numpy(), want_out)
+        out2, n2 = m["spec_accept"](pred.cuda(), tok.cuda())
+        w2o, w2n = O.spec_accept(pred.numpy(), tok.numpy(), np.full((B, 1), -1), np.ones(B))
+        assert np.array_equal(n2.cpu().numpy(), w2n) and np.array_equal(out2.cpu().numpy(), w2o)
+
+
+def test_spec_accept_lengths_cover_every_n():
+    """Reference tests/test_mtp4.py:285-312: n == j + 1 for j correct drafts."""
+    m = mods()
+    k = 7
+    pred = torch.arange(100, 100 + k + 1)[None].repeat(k + 1, 1)
+    tok = torch.ones(k + 1, k + 1, dtype=torch.int64)
+    tok[:, 1:] = pred[:, :k]
+    for j in range(k):
+        tok[j, 1 + j] = 5
+    out, n = m["spec_accept"](pred.cuda(), tok.cuda())
+    assert n.tolist() == list(range(1, k + 2))
+    for j in range(k + 1):
+        assert out[j, j] == pred[j, j]
+
+
+def verify_case(target, draft, ud, ua, us, params, V, k, mask=None):
+    """Draft tokens are drawn from the draft's processed distribution with ud; then the verify is compared."""
+    m = mods()
+    B = target.shape[0]
+    sp = wl.sampler_params(params, V, "cuda")
+    kw = {} if mask is None else dict(mask=mask[:, :k].contiguous().cuda())
+    d_ids = m["draw"](draft.cuda(), sp, None, u=ud.cuda(), **kw)
+    out, n = m["spec_verify"](target.cuda(), draft.cuda(), d_ids, sp, ua.cuda(), us.cuda(),
+                              mask=None if mask is None else mask.cuda())
+    torch.cuda.synchronize()
+    out, n, d_np = out.cpu().numpy(), n.cpu().numpy(), d_ids.cpu().numpy()
+    pr = np_params(params)
+    boundary = 0
+    for b in range(B):
+        r = O.spec_verify_reject(target[b].float().numpy(), draft[b].float().numpy(), d_np[b], pr["temperature"][b], pr["top_k"][b],
+                                 pr["top_p"][b], pr["log_min_p"][b], ua[b].numpy(), us[b].numpy(),
+                                 target_mask=None if mask is None else mask[b].numpy())
+        ok = (n[b] == r["n_accept"] + 1 and out[b, r["n_accept"]] == r["token"]
+              and list(out[b, :r["n_accept"]]) == list(d_np[b, :r["n_accept"]]) and (out[b, n[b]:] == -1).all())
+        if not ok:
+            assert min(r["margin"], r["accept_margin"]) < 1e-5, (b, n[b], out[b], r)
+            boundary += 1
+    assert boundary <= max(1, B // 100)
+    return n
+
+
+def test_config2_speculative_verify_greedy_and_sampled():
+    w = wl.config2()
+    V, k = wl.V_QWEN, w["k"]
+    n = verify_case(w["target"], w["draft"], w["ud"], w["ua"], w["us"], w["params"], V, k)
+    assert 1 <= int(n[0]) <= k + 1
+    greedy = dict(w["params"])
+    greedy["temperature"] = torch.zeros(1)
+    verify_case(w["target"], w["draft"], w["ud"], w["ua"], w["us"], greedy, V, k)
+
+
+def test_spec_verify_small_vocab_many_slots():
+    g = torch.Generator().manual_seed(21)
+    B, k, V = 96, 4, 1000
+    target = torch.randn(B, k + 1, V, generator=g) * 2
+    draft = (target[:, :k] + torch.randn(B, k, V, generator=g) * 0.7).contiguous()
+    allowed = torch.rand(B, k + 1, V, generator=g) < 0.6
+    allowed[..., 3] = True
+    params = wl._params(B, V, torch.where(torch.arange(B) % 5 == 0, 0.0, 0.9), 40, 0.9, 0.02)
+    n = verify_case(target, draft, wl.open_unit(g, B, k), wl.open_unit(g, B, k), wl.open_unit(g, B, k + 1), params, V, k,
+                    mask=wl.pack_mask(allowed))
+    assert len(set(n.tolist())) >= 3                               # several accept lengths occur
+
+
+def test_spec_verify_preserves_the_target_distribution():
+    """The first emitted token of a rejection verify follows p_0 whatever the draft distribution is."""
+    m = mods()
+    V, B = 64, 60000
+    g = torch.Generator().manual_seed(4)
+    tl = torch.randn(1, 2, V, generator=g) * 1.5
+    dl = tl[:, :1] + torch.randn(1, 1, V, generator=g)
+    sp = m["SamplerParams"](B, V, "cuda")
+    sp.temperature.fill_(1.0)
+    target = tl.expand(B, 2, V).contiguous().cuda()
+    draft = dl.expand(B, 1, V).contiguous().cuda()
+    d_ids = m["draw"](draft, sp, None, u=wl.open_unit(g, B, 1).cuda())
+    out, n = m["spec_verify"](target, draft, d_ids, sp, wl.open_unit(g, B, 1).cuda(), wl.open_unit(g, B, 2).cuda())
+    emp = torch.bincount(out[:, 0], minlength=V).double().cpu() / B
+    p = torch.softmax(tl[0, 0].double(), -1)
+    assert 0.5 * (emp - p).abs().sum().item() < 0.02
