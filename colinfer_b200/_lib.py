@@ -47,6 +47,8 @@ SIGNATURES = {
     "colinfer_spec_verify_ids_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.POINTER(Geometry)]),
     "colinfer_set_cluster_override": (C.c_int, [C.c_int]),
+    "colinfer_set_profile_buffer": (C.c_int, [C.c_void_p, C.c_int]),
+    "colinfer_max_active_clusters": (C.c_int, [C.c_int, C.c_int]),
     "colinfer_version": (C.c_int, []),
 }
 

@@ -10,7 +10,9 @@ typedef unsigned long long u64;
 
 #define CI_NEG_INF (__int_as_float(0xff800000))
 #define CI_LOG2E 1.4426950408889634f
-#define CI_MASS_SCALE 1099511627776.0f  // 2^40: kept masses are summed as integers in units of 2^-40
+#define CI_MASS_BITS 30
+#define CI_MASS_SCALE 1073741824.0f     // 2^30: kept masses are summed as integers in units of 2^-30
+#define CI_MASS_INV (1.0 / 1073741824.0)
 
 // ------------------------------------------------------------------------------------------------ ordered float keys
 // Order-preserving map float -> uint32 (ascending).  -0 is folded onto +0 so that equal floats get equal keys.
@@ -42,13 +44,23 @@ __device__ __forceinline__ float lower_logit_for(float zt, float tc, float start
     return key2f(k);
 }
 
-// Kept mass of one element in units of 2^-40: exp(z - m), z = l / tc.  The same function feeds every histogram and
+// Kept mass of one element in units of 2^-30: exp(z - m), z = l / tc.  The same function feeds every histogram and
 // every prefix sum, so all sums are exact integer sums of the same addends (order independent, reproducible).
-__device__ __forceinline__ u64 mass_q(float l, float tc, float m) {
-    const float d = scale_logit(l, tc) - m;
-    const float e = exp2f(d * CI_LOG2E);
-    return __float2ull_rn(e * CI_MASS_SCALE);
-}
+// The division is the two-FMA sequence q = l * r, q += fma(-q, tc, l) * r with r = 1 / tc rounded to nearest, which
+// gives the IEEE quotient for every operand in range (it can be one unit off only when tc's significand is all ones);
+// it only feeds masses -- thresholds and ties always use the exact division.  The exponential is the hardware
+// ex2.approx (relative error ~2^-22); results below 2^-31 round to zero mass.
+struct MassFn {
+    float tc, rinv, m;
+    __device__ __forceinline__ void init(float tc_, float m_) { tc = tc_; rinv = __frcp_rn(tc_); m = m_; }
+    __device__ __forceinline__ uint32_t operator()(float l) const {
+        const float q0 = l * rinv;
+        const float z = fmaf(fmaf(-q0, tc, l), rinv, q0);
+        float e;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((z - m) * CI_LOG2E));
+        return __float2uint_rn(e * CI_MASS_SCALE);
+    }
+};
 
 // ------------------------------------------------------------------------------------------------ Philox4x32-10
 // Salmon et al. 2011; keyed and indexed as the reference's csrc/sampling.cu:11-30 (counter (n / 4, 0), word n % 4).

@@ -83,7 +83,7 @@ __global__ void k_write_probs(const float* __restrict__ logits, const colinfer_r
     float* dst = out + (size_t)row * V;
     const bool bad = (st.status & (COLINFER_ROW_DEGENERATE | COLINFER_ROW_TIMEOUT)) != 0 || st.mass_q == 0;
     const float m = scale_logit(st.lmax, st.tc);
-    const float S = (float)((double)st.mass_q * (1.0 / 1099511627776.0));
+    const float S = (float)((double)st.mass_q * CI_MASS_INV);
     for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < V; g += gridDim.x * blockDim.x) {
         const float l = __ldg(src + g);
         float p;
@@ -243,16 +243,16 @@ __device__ double token_prob(const colinfer_row_stats& st, float l, long long to
     if (st.status & COLINFER_ROW_DEGENERATE) return tok == st.argmax ? 1.0 : 0.0;
     if (!(l >= st.lcut) || !(l > CI_NEG_INF) || st.mass_q == 0) return 0.0;
     const float d = scale_logit(l, st.tc) - scale_logit(st.lmax, st.tc);
-    return exp((double)d) / ((double)st.mass_q * (1.0 / 1099511627776.0));
+    return exp((double)d) / ((double)st.mass_q * CI_MASS_INV);
 }
-// residual mass of one token in units of 2^-40 (fp32 arithmetic, integer result)
+// residual mass of one token in units of 2^-40 (fp32 arithmetic, integer result: order-independent sums)
 __device__ __forceinline__ u64 residual_q(float lt, float ld, const colinfer_row_stats& st, const colinfer_row_stats& sd,
                                           float mt, float md, float inv_t, float inv_d) {
     float p = 0.0f, q = 0.0f;
     if (lt >= st.lcut && lt > CI_NEG_INF) p = exp2f((scale_logit(lt, st.tc) - mt) * CI_LOG2E) * inv_t;
     if (ld >= sd.lcut && ld > CI_NEG_INF) q = exp2f((scale_logit(ld, sd.tc) - md) * CI_LOG2E) * inv_d;
     const float rres = p - q;
-    return rres > 0.0f ? __float2ull_rn(rres * CI_MASS_SCALE) : 0ull;
+    return rres > 0.0f ? __float2ull_rn(rres * 1099511627776.0f) : 0ull;   // units of 2^-40
 }
 
 __global__ void __launch_bounds__(VF_THREADS) k_verify_finish(const __grid_constant__ VerifyArgs a) {
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_finish(const __grid_const
     if (s_mode == 1) {
         const colinfer_row_stats st = st_t[j], sd = st_d[j];
         const float mt = scale_logit(st.lmax, st.tc), md = scale_logit(sd.lmax, sd.tc);
-        const float inv_t = (float)(1099511627776.0 / (double)st.mass_q), inv_d = (float)(1099511627776.0 / (double)sd.mass_q);
+        const float inv_t = (float)(1.0 / ((double)st.mass_q * CI_MASS_INV)), inv_d = (float)(1.0 / ((double)sd.mass_q * CI_MASS_INV));
         const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
         const size_t bt = ((size_t)b * (k + 1) + j) * V, bd = ((size_t)b * k + j) * V;
         const int nwarps = VF_THREADS / 32;

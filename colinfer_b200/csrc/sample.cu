@@ -6,11 +6,14 @@
 // penalties, grammar mask, row maximum / argmax, the min-p / top-k / top-p threshold selects and the inverse-CDF draw --
 // works on shared memory, so HBM is read once per row whatever the sampling parameters are.
 //
-// Selection is exact and order independent.  The kept set is always {logit >= threshold}; thresholds are found by a
-// three-level radix select over the order-preserving 32-bit key of the logit, with count histograms for top-k and
-// mass histograms for top-p.  Masses are exp(z - max) rounded to integers in units of 2^-40 and summed as integers:
-// every histogram, every prefix sum and the CDF crossing are therefore independent of thread, CTA and cluster geometry
-// and of the other rows in the launch (the reference's row-invariance property).
+// Selection is exact.  The kept set is always {logit >= threshold}.  Masses are exp(z - max) rounded to integers in
+// units of 2^-30 and summed as integers, so every sum, every cumulative-mass crossing and the CDF crossing are
+// independent of thread, CTA and cluster geometry and of the other rows in the launch (the reference's row-invariance
+// property).  Thresholds are found in two steps: a fine count histogram over the distance from the row maximum
+// (4096 buckets) locates the bucket of the k-th largest logit exactly, and the bucket of the top-p pivot approximately;
+// the few hundred logits around it are gathered into a list (in token order) and the pivot is found exactly on the
+// list.  If a list would overflow, or the estimated top-p band misses the true pivot, an exact 4-level radix select
+// over the order-preserving 32-bit keys runs instead (slower, same result).
 //
 // What the reference does in ~25 torch / FlashInfer launches per slot (engine/spec/accept.py:23-52 after
 // engine/runtime/sampler.py:50-56) is one launch here.
@@ -21,9 +24,15 @@
 #define CI_WARPS (CI_THREADS / 32)
 #define CI_CHUNK 4096            // elements per bulk copy
 #define CI_MAX_CHUNKS 16
-#define CI_NB 2048               // radix buckets per level (11 bits)
+#define CI_NB1 4096              // fine buckets over the distance from the row maximum
+#define CI_RANGE 25.0f           // the buckets cover distances up to CI_RANGE * temperature
+#define CI_WLIST 64              // list entries per warp
+#define CI_GLIST 1365            // gathered list entries (16 KB)
+#define CI_FB_NB 256             // radix buckets per level of the fallback select (8 bits)
+#define CI_MAX_CAND 128          // tied / neighbouring candidates examined one by one in the final list step
 #define CI_PEN_TABLE 2048        // distinct history ids per slice with an O(1) count
 #define CI_WAIT_CYCLES 400000000LL
+#define CI_FLT_MAX 3.402823466e38f
 
 struct SampleArgs {
     const void* logits; int dtype; int use_bulk;
@@ -32,19 +41,31 @@ struct SampleArgs {
     const void* pos; int pos_i64; const float* u;
     int64_t* out; colinfer_row_stats* stats; int32_t* status;
     int B, R, V; int slice_elems; int flags;
+    long long* prof; int prof_slots;   // optional per-CTA phase timestamps (profiling hook)
 };
+#define CI_PROF(slot) do { if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) a.prof[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+
+struct ListEntry { uint32_t idx; float l; uint32_t q; };
 
 // Values one CTA publishes to its cluster peers.
 struct Xch {
     float lmax; int lidx;          // slice maximum and its lowest global index
-    u64 segtot;                    // total of this CTA's reduced histogram segment
-    u64 cta_mass;                  // kept mass of this CTA's slice
+    u64 seg_cnt, seg_est;          // totals of this CTA's reduced bucket segment: counts, estimated mass
+    u64 fb_segtot;                 // the same for the fallback radix select
+    u64 s_all, s_above;            // band pass: kept mass of the slice, and of its part above the band
+    u64 cta_mass;                  // kept mass of the slice under the final threshold
+    unsigned short wcount[CI_WARPS];   // entries in each warp's list
+    int list_overflow;
 };
 
 struct Scratch {
     u64 warp_tot[CI_WARPS];
+    u64 warp_aux[CI_WARPS];
     float warp_f[CI_WARPS]; int warp_i[CI_WARPS];
+    uint32_t warp_u[CI_WARPS], warp_v[CI_WARPS];
+    unsigned short pcount[8 * CI_WARPS]; unsigned short poff[8 * CI_WARPS + 1];
     int found_idx; u64 found_before;
+    int ncand; float sel_value; int sel_ok;
     int fail;
     int hist_slow;
 };
@@ -90,27 +111,144 @@ __device__ u64 block_sum_u64(u64 v, Scratch* s) {
     return t;
 }
 
-// Effective logit of one token outside the resident row: penalties (by scanning the history) and mask.  Used by the
-// verify finish kernel; one thread.
-__device__ float effective_logit(float l, int tok, int V, const int32_t* hist, int hlen, float rp, float pp, float fp,
-                                 const int32_t* mask_row) {
-    if (hist != nullptr && hlen > 0 && !(rp == 1.0f && pp == 0.0f && fp == 0.0f)) {
-        int cnt = 0;
-        for (int i = 0; i < hlen; ++i) cnt += (hist[i] == tok);
-        if (cnt > 0) {
-            l = l > 0.0f ? __fdiv_rn(l, rp) : __fmul_rn(l, rp);
-            l = __fsub_rn(l, __fmul_rn(fp, (float)cnt));
-            l = __fsub_rn(l, pp);
-        }
-    }
-    if (mask_row != nullptr && !((mask_row[tok >> 5] >> (tok & 31)) & 1)) l = CI_NEG_INF;
-    return l;
-}
-
 __device__ __forceinline__ float apply_penalty(float l, int cnt, float rp, float pp, float fp) {
     l = l > 0.0f ? __fdiv_rn(l, rp) : __fmul_rn(l, rp);
     l = __fsub_rn(l, __fmul_rn(fp, (float)cnt));
     return __fsub_rn(l, pp);
+}
+
+// Estimated mass (units of 2^-30) of one element in distance bucket b: exp(-(b + 0.5) * CI_RANGE / CI_NB1).
+__device__ __forceinline__ u64 bucket_mass_est(int b) {
+    return (u64)__float2uint_rn(exp2f(-((float)b + 0.5f) * (CI_RANGE * CI_LOG2E / (float)CI_NB1)) * CI_MASS_SCALE);
+}
+
+// Exact weighted selection on a gathered list: the value v among the entries with wt > 0 such that
+// W(l > v) < target <= W(l >= v).  256 coarse bins over the entries' key range, then the entries of the pivot bin one by
+// one (a warp each).  Returns false when the pivot bin holds more than CI_MAX_CAND entries.  All threads call.
+template <class W>
+__device__ bool list_select(const ListEntry* gl, int n, W wt, u64 target, u64* bins, uint32_t* cand, Scratch* sc, float& value) {
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
+    for (int i = tid; i < n; i += CI_THREADS) {
+        if (wt(i) > 0) { const uint32_t k = f2key(gl[i].l); kmin = min(kmin, k); kmax = max(kmax, k); }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+        kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    }
+    if (lane == 0) { sc->warp_u[warp] = kmin; sc->warp_v[warp] = kmax; }
+    for (int i = tid; i < 256; i += CI_THREADS) bins[i] = 0;
+    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; sc->sel_value = 0.0f; }
+    __syncthreads();
+    for (int w = 0; w < CI_WARPS; ++w) { kmin = min(kmin, sc->warp_u[w]); kmax = max(kmax, sc->warp_v[w]); }
+    const u64 span = (u64)(kmax - kmin) + 1ull;
+    auto bin_of = [&](uint32_t k) { return (int)((((u64)(kmax - k)) << 8) / span); };   // descending, 0..255
+    for (int i = tid; i < n; i += CI_THREADS) {
+        const u64 w = wt(i);
+        if (w > 0) atomicAdd(&bins[bin_of(f2key(gl[i].l))], w);
+    }
+    __syncthreads();
+    int b_star; u64 before;
+    block_find([&](int i) { return bins[i]; }, 256, target, sc, b_star, before);
+    for (int i = tid; i < n; i += CI_THREADS) {
+        if (wt(i) > 0 && bin_of(f2key(gl[i].l)) == b_star) {
+            const int slot = atomicAdd(&sc->ncand, 1);
+            if (slot < CI_MAX_CAND) cand[slot] = (uint32_t)i;
+        }
+    }
+    __syncthreads();
+    const int nc = sc->ncand;
+    if (nc > CI_MAX_CAND) { __syncthreads(); return false; }
+    for (int c = warp; c < nc; c += CI_WARPS) {
+        const uint32_t kc = f2key(gl[cand[c]].l);
+        u64 gt = 0, eq = 0;
+        for (int i = lane; i < n; i += 32) {
+            const u64 w = wt(i);
+            if (w > 0) {
+                const uint32_t k = f2key(gl[i].l);
+                if (bin_of(k) == b_star) { if (k > kc) gt += w; else if (k == kc) eq += w; }
+            }
+        }
+        gt = warp_sum_u64(gt); eq = warp_sum_u64(eq);
+        if (lane == 0 && before + gt < target && target <= before + gt + eq) { sc->sel_value = gl[cand[c]].l; sc->sel_ok = 1; }
+    }
+    __syncthreads();
+    value = sc->sel_value;
+    const bool ok = sc->sel_ok != 0;
+    __syncthreads();
+    return ok;
+}
+
+// Exact radix select over the order-preserving 32-bit keys of the logits >= lcut, four levels of 8 bits, across the
+// cluster.  by_mass: the pivot where the descending cumulative mass first reaches top_p of the total; else the kk-th
+// largest.  Returns false when the filter removes nothing (fewer survivors than kk); else pivot holds the pivot logit.
+// Every CTA of the cluster calls it with identical arguments and takes identical decisions.
+struct RadixCtx {
+    const float* rowbuf; int n_pad; u64* fb_hist; u64* fb_seg; Xch* xch; Scratch* sc; int rank, CS;
+};
+__device__ bool radix_select(cg::cluster_group& cluster, const RadixCtx& c, const MassFn& mass, float lcut, bool by_mass,
+                             u64 kk, float topp, float& pivot) {
+    const int tid = threadIdx.x;
+    const float lk = fmaxf(lcut, -CI_FLT_MAX);
+    uint32_t prefix = 0;
+    u64 target = by_mass ? 0 : kk;
+    for (int lvl = 0; lvl < 4; ++lvl) {
+        const int shift = 24 - 8 * lvl;
+        for (int i = tid; i < CI_FB_NB; i += CI_THREADS) c.fb_hist[i] = 0;
+        __syncthreads();
+        const float4* row4 = reinterpret_cast<const float4*>(c.rowbuf);
+        for (int i = tid; i * 4 < c.n_pad; i += CI_THREADS) {
+            const float4 v = row4[i];
+            const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float l = e4[j];
+                if (l >= lk) {
+                    const uint32_t key = f2key(l);
+                    if (lvl == 0 || (key >> (shift + 8)) == prefix)
+                        atomicAdd(&c.fb_hist[CI_FB_NB - 1 - (int)((key >> shift) & 0xFFu)], by_mass ? (u64)mass(l) : 1ull);
+                }
+            }
+        }
+        __syncthreads();
+        cluster.sync();                                                    // local histograms complete
+        const int G = CI_FB_NB / c.CS;
+        u64 part = 0;
+        for (int g = tid; g < G; g += CI_THREADS) {
+            u64 sum = 0;
+            for (int q = 0; q < c.CS; ++q) sum += cluster.map_shared_rank(c.fb_hist, q)[c.rank * G + g];
+            c.fb_seg[g] = sum;
+            part += sum;
+        }
+        const u64 tot = block_sum_u64(part, c.sc);
+        if (tid == 0) c.xch->fb_segtot = tot;
+        __syncthreads();
+        cluster.sync();                                                    // reduced segments published
+        u64 grand = 0, segtots[8];
+        for (int q = 0; q < c.CS; ++q) { segtots[q] = cluster.map_shared_rank(c.xch, q)->fb_segtot; grand += segtots[q]; }
+        if (lvl == 0) {
+            if (by_mass) {
+                double t = ceil((double)topp * (double)grand);
+                u64 tq = t <= 1.0 ? 1ull : (u64)t;
+                if (tq > grand) tq = grand;
+                target = tq;
+            } else if (target >= grand) return false;
+        }
+        if (grand == 0) return false;
+        int s_star = c.CS - 1; u64 before_seg = 0, run = 0;
+        for (int q = 0; q < c.CS; ++q) {
+            if (run + segtots[q] >= target) { s_star = q; before_seg = run; break; }
+            run += segtots[q];
+        }
+        const u64* pseg = cluster.map_shared_rank(c.fb_seg, s_star);
+        int g_star; u64 before;
+        block_find([&](int i) { return pseg[i]; }, G, target - before_seg, c.sc, g_star, before);
+        target -= before_seg + before;
+        prefix = (prefix << 8) | (uint32_t)(CI_FB_NB - 1 - (s_star * G + g_star));
+    }
+    pivot = key2f(prefix);
+    return true;
 }
 
 extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __grid_constant__ SampleArgs a) {
@@ -129,14 +267,20 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* rowbuf = reinterpret_cast<float*>(smem_raw);
-    u64* hist64 = reinterpret_cast<u64*>(smem_raw + (size_t)slice_cap * 4);
-    uint32_t* hist32 = reinterpret_cast<uint32_t*>(hist64);
-    u64* seg = hist64 + CI_NB;
-    u64* mbar = seg + CI_NB;
+    unsigned char* hreg = smem_raw + (size_t)slice_cap * 4;                 // 24 KB work area
+    uint32_t* hist1 = reinterpret_cast<uint32_t*>(hreg);                      // [CI_NB1] fine counts
+    uint32_t* segcnt = reinterpret_cast<uint32_t*>(hreg + CI_NB1 * 4);        // [<= 2048] reduced segment
+    ListEntry* glist = reinterpret_cast<ListEntry*>(hreg);                    // gathered list, over hist1
+    u64* bins = reinterpret_cast<u64*>(hreg + CI_NB1 * 4);                    // [256] list_select bins, over segcnt
+    uint32_t* cand = reinterpret_cast<uint32_t*>(hreg + CI_NB1 * 4 + 256 * 8);
+    u64* fb_hist = reinterpret_cast<u64*>(hreg);                              // fallback radix, over hist1
+    u64* fb_seg = fb_hist + CI_FB_NB;
+    ListEntry* ownlist = reinterpret_cast<ListEntry*>(hreg + 24 * 1024);      // [CI_WARPS][CI_WLIST]
+    u64* mbar = reinterpret_cast<u64*>(hreg + 24 * 1024 + CI_WARPS * CI_WLIST * sizeof(ListEntry));
     Xch* xch = reinterpret_cast<Xch*>(mbar + CI_MAX_CHUNKS);
     Scratch* sc = reinterpret_cast<Scratch*>(xch + 1);
-    // penalty tables alias the histogram area (used before the first histogram)
-    uint32_t* pen_bits = hist32;
+    // penalty tables alias the work area (used before the first histogram)
+    uint32_t* pen_bits = reinterpret_cast<uint32_t*>(hreg);
     const int nw = slice_cap >> 5;
     uint32_t* pen_prefix = pen_bits + nw;
     uint32_t* pen_cnt = pen_prefix + nw;
@@ -155,6 +299,12 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     const int32_t* mrow = a.mask ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
     const int nchunks = (slice_len + CI_CHUNK - 1) / CI_CHUNK;
 
+    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
+        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.prof[(size_t)blockIdx.x * 16 + 15] = (long long)gt; a.prof[(size_t)blockIdx.x * 16 + 14] = smid;
+    }
+    CI_PROF(0);
     // ---------------------------------------------------------------------------------------- start the HBM read
     if (tid == 0) {
         sc->fail = 0; sc->hist_slow = 0;
@@ -214,6 +364,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         __syncthreads();
     }
 
+    CI_PROF(1);
     // ---------------------------------------------------------------------------------------- pass A: land, penalise, mask, maximum
     float lmax = CI_NEG_INF;
     int lidx = 0x7fffffff;
@@ -298,6 +449,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             }
         }
     }
+    CI_PROF(2);
     // block reduce (largest value, lowest index among equals)
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
@@ -313,10 +465,12 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             const float om = sc->warp_f[w]; const int oi = sc->warp_i[w];
             if (om > bm || (om == bm && oi < bi)) { bm = om; bi = oi; }
         }
-        xch->lmax = bm; xch->lidx = bi;
+        xch->lmax = bm; xch->lidx = bi; xch->list_overflow = 0;
     }
     __syncthreads();
+    CI_PROF(3);
     cluster.sync();                                                                    // (1) slice maxima published
+    CI_PROF(4);
     float L = CI_NEG_INF; int aidx = 0x7fffffff; int any_fail = 0;
     for (int q = 0; q < CS; ++q) {
         const Xch* px = cluster.map_shared_rank(xch, q);
@@ -338,189 +492,431 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 
     if (do_dist) {
         const float m = scale_logit(L, tc);
+        MassFn mass;
+        mass.init(tc, m);
         // ------------------------------------------------------------------------------------ min-p threshold
-        const float lmp = a.p.log_min_p[b];
-        const float thr = __fadd_rn(m, lmp);
+        const float thr = __fadd_rn(m, a.p.log_min_p[b]);
         lcut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
-        int kk = a.p.top_k[b];
-        const bool do_topk = kk > 0 && kk < V;
+        const int kk = a.p.top_k[b];
         const float topp = a.p.top_p[b];
-        const bool do_topp = topp < 1.0f;
+        bool need_topk = kk > 0 && kk < V;
+        bool need_topp = topp < 1.0f;
 
-        // ------------------------------------------------------------------------------------ radix selects
-        // stage 0: k-th largest by count; stage 1: top-p pivot by mass.  Three levels each (11 + 11 + 10 key bits).
-        for (int stage = 0; stage < 2; ++stage) {
-            if (stage == 0 && !do_topk) continue;
-            if (stage == 1 && !do_topp) continue;
-            const bool by_mass = stage == 1;
-            uint32_t prefix = 0;
-            u64 target = by_mass ? 0 : (u64)kk;
-            bool skip = false;
-            for (int lvl = 0; lvl < 3; ++lvl) {
-                const int shift = lvl == 0 ? 21 : lvl == 1 ? 10 : 0;
-                const int nbits = lvl == 2 ? 10 : 11;
-                const int nb = 1 << nbits;
-                for (int i = tid; i < nb; i += CI_THREADS) hist64[i] = 0;
-                __syncthreads();
+        // warp w owns the contiguous region [r_lo, r_hi) of the slice; lanes interleave float4 groups, so the token
+        // order inside a region is (step, lane, component).
+        const int reg = ((n_pad / 128 + CI_WARPS - 1) / CI_WARPS) * 128;
+        const int r_lo = min(warp * reg, n_pad), r_hi = min(r_lo + reg, n_pad);
+        ListEntry* mylist = ownlist + warp * CI_WLIST;
+
+        enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
+        int path = PATH_PURE;
+        float t_hi = CI_NEG_INF, t_lo = __int_as_float(0x7f800000);   // band thresholds (PATH_BAND), list threshold (PATH_LIST: t_lo)
+
+        if (need_topk || need_topp) {
+            // -------------------------------------------------------------------------------- fine count histogram
+            const float SC = (float)CI_NB1 / (CI_RANGE * tc);
+            const float lk = fmaxf(lcut, -CI_FLT_MAX);         // excludes -inf (masked / padding) as well
+            for (int i = tid; i < CI_NB1; i += CI_THREADS) hist1[i] = 0u;
+            __syncthreads();
+            {
                 const float4* row4 = reinterpret_cast<const float4*>(rowbuf);
                 for (int i = tid; i * 4 < n_pad; i += CI_THREADS) {
                     const float4 v = row4[i];
                     const float e4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float l = e4[j];
-                        if (l >= lcut && l > CI_NEG_INF) {
-                            const uint32_t key = f2key(l);
-                            if (lvl == 0 || (key >> (shift + nbits)) == prefix) {
-                                const int bk = nb - 1 - (int)((key >> shift) & (uint32_t)(nb - 1));
-                                if (by_mass) atomicAdd(&hist64[bk], mass_q(l, tc, m));
-                                else atomicAdd(&hist32[bk * 2], 1u);   // low word of the 64-bit slot
-                            }
+                        if (e4[j] >= lk) atomicAdd(&hist1[min(CI_NB1 - 1, __float2int_rz((L - e4[j]) * SC))], 1u);
+                    }
+                }
+            }
+            __syncthreads();
+            cluster.sync();                                                            // (A) local histograms complete
+            // each CTA reduces its segment of the buckets over the cluster
+            const int G = CI_NB1 / CS;
+            uint32_t* myseg = (CS == 1) ? hist1 : segcnt;
+            u64 pc = 0, pe = 0;
+            for (int g = tid; g < G; g += CI_THREADS) {
+                uint32_t sum = 0;
+                if (CS == 1) sum = hist1[g];
+                else {
+                    for (int q = 0; q < CS; ++q) sum += cluster.map_shared_rank(hist1, q)[rank * G + g];
+                    segcnt[g] = sum;
+                }
+                pc += sum;
+                pe += (u64)sum * bucket_mass_est(rank * G + g);
+            }
+            const u64 totc = block_sum_u64(pc, sc);
+            const u64 tote = block_sum_u64(pe, sc);
+            if (tid == 0) { xch->seg_cnt = totc; xch->seg_est = tote; }
+            __syncthreads();
+            cluster.sync();                                                            // (B) reduced segments published
+            u64 segc[8], sege[8], survivors = 0, est_total = 0;
+            for (int q = 0; q < CS; ++q) {
+                const Xch* px = cluster.map_shared_rank(xch, q);
+                segc[q] = px->seg_cnt; sege[q] = px->seg_est;
+                survivors += segc[q]; est_total += sege[q];
+            }
+            if (need_topk && (u64)kk >= survivors) need_topk = false;   // fewer survivors than k: top-k removes nothing
+            if (need_topk) {
+                // bucket of the k-th largest logit, exactly
+                int s_star = CS - 1; u64 before_seg = 0, run = 0;
+                for (int q = 0; q < CS; ++q) {
+                    if (run + segc[q] >= (u64)kk) { s_star = q; before_seg = run; break; }
+                    run += segc[q];
+                }
+                const uint32_t* pseg = cluster.map_shared_rank(myseg, s_star);
+                int g_star; u64 before;
+                block_find([&](int i) { return (u64)pseg[i]; }, G, (u64)kk - before_seg, sc, g_star, before);
+                const int bk = s_star * G + g_star;
+                const u64 n_upto = before_seg + before + pseg[g_star];
+                if (bk >= CI_NB1 - 3 || n_upto > CI_GLIST - 64) path = PATH_FALLBACK;
+                else {
+                    path = PATH_LIST;
+                    // every element of buckets <= bk + 1 satisfies l >= t_lo (a slightly wider set is harmless)
+                    t_lo = L - ((float)(bk + 2) + 0.01f) / SC;
+                    t_lo = t_lo - fabsf(L) * 1e-6f;
+                }
+            } else if (need_topp) {
+                // bucket where the descending cumulative estimated mass reaches top_p of the estimated total
+                if (est_total == 0) path = PATH_FALLBACK;
+                else {
+                    double te = ceil((double)topp * (double)est_total);
+                    u64 target = te <= 1.0 ? 1ull : (u64)te;
+                    if (target > est_total) target = est_total;
+                    int s_star = CS - 1; u64 before_seg = 0, run = 0;
+                    for (int q = 0; q < CS; ++q) {
+                        if (run + sege[q] >= target) { s_star = q; before_seg = run; break; }
+                        run += sege[q];
+                    }
+                    const uint32_t* pseg = cluster.map_shared_rank(myseg, s_star);
+                    int g_star; u64 before;
+                    block_find([&](int i) { return (u64)pseg[i] * bucket_mass_est(s_star * G + i); }, G, target - before_seg, sc, g_star, before);
+                    const int bp = s_star * G + g_star;
+                    const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
+                    if (bp + dn + 2 >= CI_NB1) path = PATH_FALLBACK;
+                    else {
+                        path = PATH_BAND;
+                        t_hi = bp - up <= 0 ? __int_as_float(0x7f800000) : L - (float)(bp - up) / SC;
+                        t_lo = L - (float)(bp + dn + 1) / SC;
+                    }
+                }
+            }
+        }
+        CI_PROF(5);
+
+        // ------------------------------------------------------------------------------------ list path: top-k (then top-p) on a gathered list
+        bool done = false;
+        if (path == PATH_LIST) {
+            const float tl = fmaxf(fmaxf(t_lo, lcut), -CI_FLT_MAX);
+            int wn = 0;
+            for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                const int i = i0 + lane * 4;
+                const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+                const unsigned mk = (v.x >= tl ? 1u : 0u) | (v.y >= tl ? 2u : 0u) | (v.z >= tl ? 4u : 0u) | (v.w >= tl ? 8u : 0u);
+                const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
+                if (any) {
+                    const int c = __popc(mk);
+                    int pre = c;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += t; }
+                    const int tot = __shfl_sync(0xffffffffu, pre, 31);
+                    int at = wn + pre - c;
+                    const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (mk & (1u << j)) {
+                            if (at < CI_WLIST) { mylist[at].idx = (uint32_t)(slice_lo + i + j); mylist[at].l = e4[j]; mylist[at].q = 0u; }
+                            ++at;
                         }
                     }
+                    wn += tot;
+                }
+            }
+            if (lane == 0) {
+                xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
+                if (wn > CI_WLIST) xch->list_overflow = 1;
+            }
+            __syncthreads();
+            cluster.sync();                                                            // (L) lists published
+            // gather every CTA's lists, in token order
+            int overflow = 0;
+            for (int q = 0; q < CS; ++q) overflow |= cluster.map_shared_rank(xch, q)->list_overflow;
+            if (tid < CS * CI_WARPS) sc->pcount[tid] = cluster.map_shared_rank(xch, tid / CI_WARPS)->wcount[tid % CI_WARPS];
+            __syncthreads();
+            if (tid == 0) {
+                int run = 0;
+                for (int p = 0; p < CS * CI_WARPS; ++p) { sc->poff[p] = (unsigned short)run; run += sc->pcount[p]; }
+                sc->poff[CS * CI_WARPS] = (unsigned short)min(run, 65535);
+            }
+            __syncthreads();
+            const int n = sc->poff[CS * CI_WARPS];
+            if (overflow || n > CI_GLIST || n == 0) path = PATH_FALLBACK;
+            else {
+                for (int e = tid; e < n; e += CI_THREADS) {
+                    int lo = 0, hi = CS * CI_WARPS - 1;                 // last p with poff[p] <= e
+                    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sc->poff[mid] <= e) lo = mid; else hi = mid - 1; }
+                    const ListEntry* src = cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]);
+                    ListEntry en = *src;
+                    en.q = mass(en.l);
+                    glist[e] = en;
                 }
                 __syncthreads();
-                cluster.sync();                                                        // (A) local histograms complete
-                const int G = nb / CS;
-                u64 part = 0;
-                for (int g = tid; g < G; g += CI_THREADS) {
-                    u64 sum = 0;
-                    for (int q = 0; q < CS; ++q) {
-                        const u64* ph = cluster.map_shared_rank(hist64, q);
-                        u64 x = ph[rank * G + g];
-                        if (!by_mass) x &= 0xFFFFFFFFull;
-                        sum += x;
-                    }
-                    seg[g] = sum;
-                    part += sum;
+                // k-th largest of the list = k-th largest of the row
+                float lk_val;
+                bool ok = list_select(glist, n, [&](int i) { return (u64)(glist[i].l >= lcut ? 1 : 0); }, (u64)kk, bins, cand, sc, lk_val);
+                float cut2 = lcut;
+                if (ok) {
+                    cut2 = fmaxf(lcut, lower_logit_for(scale_logit(lk_val, tc), tc, lk_val));
+                    if (cut2 < tl) ok = false;                           // a tie partner could lie outside the list
                 }
-                const u64 tot = block_sum_u64(part, sc);
-                if (tid == 0) xch->segtot = tot;
-                __syncthreads();
-                cluster.sync();                                                        // (B) reduced segments published
-                u64 grand = 0;
-                u64 segtots[8];
-                for (int q = 0; q < CS; ++q) { segtots[q] = cluster.map_shared_rank(xch, q)->segtot; grand += segtots[q]; }
-                if (lvl == 0) {
-                    if (by_mass) {
-                        // target = smallest integer >= top_p * mass, at least 1
-                        double t = ceil((double)topp * (double)grand);
-                        u64 tq = t <= 1.0 ? 1ull : (u64)t;
-                        if (tq > grand) tq = grand;
-                        target = tq;
-                    } else if (target >= grand) {
-                        skip = true;                          // fewer survivors than k: top-k removes nothing
+                if (ok && need_topp) {
+                    u64 part = 0;
+                    for (int i = tid; i < n; i += CI_THREADS) if (glist[i].l >= cut2) part += glist[i].q;
+                    const u64 s1 = block_sum_u64(part, sc);
+                    double te = ceil((double)topp * (double)s1);
+                    u64 target = te <= 1.0 ? 1ull : (u64)te;
+                    if (target > s1) target = s1;
+                    float lp_val;
+                    ok = s1 > 0 && list_select(glist, n, [&](int i) { return (u64)(glist[i].l >= cut2 ? glist[i].q : 0u); }, target, bins, cand, sc, lp_val);
+                    if (ok) {
+                        cut2 = fmaxf(cut2, lower_logit_for(scale_logit(lp_val, tc), tc, lp_val));
+                        if (cut2 < tl) ok = false;
                     }
                 }
-                if (grand == 0) skip = true;
-                if (skip) break;                              // identical decision in every CTA
-                int s_star = CS - 1; u64 before_seg = 0;
-                {
-                    u64 run = 0;
-                    for (int q = 0; q < CS; ++q) {
-                        if (run + segtots[q] >= target) { s_star = q; before_seg = run; break; }
-                        run += segtots[q];
+                if (!ok) path = PATH_FALLBACK;
+                else {
+                    lcut = cut2;
+                    u64 part = 0;
+                    for (int i = tid; i < n; i += CI_THREADS) if (glist[i].l >= lcut) part += glist[i].q;
+                    total_mass = block_sum_u64(part, sc);
+                    float u = 1.0f;
+                    if (a.u != nullptr) u = a.u[row];
+                    else if (a.pos != nullptr && a.p.seed != nullptr) {
+                        const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
+                                                       : (long long)reinterpret_cast<const int*>(a.pos)[b];
+                        u = u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
                     }
+                    double tu = ceil((double)u * (double)total_mass);
+                    u64 target = tu <= 1.0 ? 1ull : (u64)tu;
+                    if (target > total_mass) target = total_mass;
+                    int at; u64 before;
+                    block_find([&](int i) { return (u64)(glist[i].l >= lcut ? glist[i].q : 0u); }, n, target, sc, at, before);
+                    token = total_mass > 0 ? (long long)glist[at].idx : (long long)aidx;
+                    if (total_mass == 0) status |= COLINFER_ROW_DEGENERATE;
+                    done = true;
                 }
-                const u64* pseg = cluster.map_shared_rank(seg, s_star);
-                int g_star; u64 before;
-                block_find([&](int i) { return pseg[i]; }, G, target - before_seg, sc, g_star, before);
-                const int b_star = s_star * G + g_star;
-                target -= before_seg + before;
-                prefix = (prefix << nbits) | (uint32_t)(nb - 1 - b_star);
             }
-            if (!skip) {
-                const float lpiv = key2f(prefix);
-                const float zc = scale_logit(lpiv, tc);
-                lcut = fmaxf(lcut, lower_logit_for(zc, tc, lpiv));
-            }
-            // make sure no peer still reads this CTA's segment when the next stage rewrites it: the next stage's
-            // sync (A) orders that; after the last stage the CDF sync below does.
         }
 
-        // ------------------------------------------------------------------------------------ inverse CDF over the kept set
-        // warp w owns the contiguous region [w * reg, (w + 1) * reg) of the slice; lanes interleave float4 groups.
-        const int reg = ((n_pad / 128 + CI_WARPS - 1) / CI_WARPS) * 128;
-        const int r_lo = min(warp * reg, n_pad), r_hi = min(r_lo + reg, n_pad);
-        u64 lane_mass = 0;
-        for (int i = r_lo + lane * 4; i < r_hi; i += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-            if (v.x >= lcut) lane_mass += mass_q(v.x, tc, m);
-            if (v.y >= lcut) lane_mass += mass_q(v.y, tc, m);
-            if (v.z >= lcut) lane_mass += mass_q(v.z, tc, m);
-            if (v.w >= lcut) lane_mass += mass_q(v.w, tc, m);
+        // ------------------------------------------------------------------------------------ fallback: exact radix select over the 32-bit keys
+        if (path == PATH_FALLBACK) {
+            // (a CTA reaches this point only after every peer finished reading its reduced segment: the reads happen
+            // before the peers' next cluster barrier, and the first write below follows this CTA's next barrier (A))
+            const RadixCtx rc = {rowbuf, n_pad, fb_hist, fb_seg, xch, sc, rank, CS};
+            float lpiv;
+            if (kk > 0 && kk < V && radix_select(cluster, rc, mass, lcut, false, (u64)kk, topp, lpiv))
+                lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+            if (need_topp && radix_select(cluster, rc, mass, lcut, true, 0, topp, lpiv))
+                lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+            path = PATH_PURE;
+            t_hi = CI_NEG_INF; t_lo = __int_as_float(0x7f800000);
         }
-        const u64 wtot = warp_sum_u64(lane_mass);
-        if (lane == 0) sc->warp_tot[warp] = wtot;
-        __syncthreads();
-        if (tid == 0) {
-            u64 t = 0;
-            for (int w = 0; w < CI_WARPS; ++w) t += sc->warp_tot[w];
-            xch->cta_mass = t;
-        }
-        __syncthreads();
-        cluster.sync();                                                                // (C) slice masses published
-        u64 my_off = 0;
-        for (int q = 0; q < CS; ++q) {
-            const u64 cm = cluster.map_shared_rank(xch, q)->cta_mass;
-            if (q < rank) my_off += cm;
-            total_mass += cm;
-        }
-        // the uniform of this row
-        float u = 1.0f;
-        if (a.u != nullptr) u = a.u[row];
-        else if (a.pos != nullptr && a.p.seed != nullptr) {
-            const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
-                                           : (long long)reinterpret_cast<const int*>(a.pos)[b];
-            u = u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
-        }
-        u64 target;
-        {
-            double t = ceil((double)u * (double)total_mass);
-            target = t <= 1.0 ? 1ull : (u64)t;
-            if (target > total_mass) target = total_mass;
-        }
-        const u64 my_mass = xch->cta_mass;
-        token = -1;
-        if (total_mass > 0 && my_off < target && target <= my_off + my_mass) {
-            // the crossing lies in this CTA: find the warp region, then the element
-            u64 woff = my_off;
-            for (int w = 0; w < warp; ++w) woff += sc->warp_tot[w];
-            if (woff < target && target <= woff + wtot) {
-                u64 run = woff;
-                for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-                    const int i = i0 + lane * 4;
-                    u64 q4[4] = {0, 0, 0, 0};
-                    if (i < r_hi) {
-                        const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-                        if (v.x >= lcut) q4[0] = mass_q(v.x, tc, m);
-                        if (v.y >= lcut) q4[1] = mass_q(v.y, tc, m);
-                        if (v.z >= lcut) q4[2] = mass_q(v.z, tc, m);
-                        if (v.w >= lcut) q4[3] = mass_q(v.w, tc, m);
+
+        // ------------------------------------------------------------------------------------ mass pass and inverse CDF over the row
+        if (!done) {
+            const bool band = path == PATH_BAND;
+            const float lk = fmaxf(lcut, -CI_FLT_MAX);
+            u64 acc_all = 0, acc_above = 0;
+            int wn = 0;
+            for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                const int i = i0 + lane * 4;
+                const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+                const float e4[4] = {v.x, v.y, v.z, v.w};
+                uint32_t q4[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) q4[j] = e4[j] >= lk ? mass(e4[j]) : 0u;
+                acc_all += (u64)q4[0] + q4[1];
+                acc_all += (u64)q4[2] + q4[3];
+                if (band) {
+                    uint32_t a4[4];
+                    unsigned mk = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        a4[j] = e4[j] > t_hi ? q4[j] : 0u;
+                        if (e4[j] <= t_hi && e4[j] >= t_lo && e4[j] >= lk) mk |= 1u << j;
                     }
-                    const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
-                    const u64 incl = warp_incl_scan_u64(s4, lane);
-                    const u64 grp = __shfl_sync(0xffffffffu, incl, 31);
-                    if (run + grp >= target) {
-                        const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
-                        const int first = __ffs(hit) - 1;
-                        if (lane == first) {
-                            u64 c = run + incl - s4;
-                            int j = 0;
-                            for (; j < 3; ++j) { c += q4[j]; if (c >= target) break; }
-                            if (a.out) a.out[row] = (long long)(slice_lo + i + j);
+                    acc_above += (u64)a4[0] + a4[1];
+                    acc_above += (u64)a4[2] + a4[3];
+                    const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
+                    if (any) {
+                        const int c = __popc(mk);
+                        int pre = c;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += t; }
+                        const int tot = __shfl_sync(0xffffffffu, pre, 31);
+                        int at = wn + pre - c;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (mk & (1u << j)) {
+                                if (at < CI_WLIST) { mylist[at].idx = (uint32_t)(slice_lo + i + j); mylist[at].l = e4[j]; mylist[at].q = q4[j]; }
+                                ++at;
+                            }
                         }
-                        break;
+                        wn += tot;
                     }
-                    run += grp;
                 }
             }
+            u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
+            const u64 wall = warp_sum_u64(acc_all);
+            if (band) {
+                if (lane == 0) {
+                    sc->warp_tot[warp] = wkeep; sc->warp_aux[warp] = wall;
+                    xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
+                    if (wn > CI_WLIST) xch->list_overflow = 1;
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    u64 ta = 0, tb = 0;
+                    for (int w = 0; w < CI_WARPS; ++w) { ta += sc->warp_aux[w]; tb += sc->warp_tot[w]; }
+                    xch->s_all = ta; xch->s_above = tb;
+                }
+                __syncthreads();
+                cluster.sync();                                                        // (L) band lists and sums published
+                int overflow = 0;
+                u64 s1 = 0, s_above = 0;
+                for (int q = 0; q < CS; ++q) {
+                    const Xch* px = cluster.map_shared_rank(xch, q);
+                    overflow |= px->list_overflow; s1 += px->s_all; s_above += px->s_above;
+                }
+                if (tid < CS * CI_WARPS) sc->pcount[tid] = cluster.map_shared_rank(xch, tid / CI_WARPS)->wcount[tid % CI_WARPS];
+                __syncthreads();
+                if (tid == 0) {
+                    int run = 0;
+                    for (int p = 0; p < CS * CI_WARPS; ++p) { sc->poff[p] = (unsigned short)run; run += sc->pcount[p]; }
+                    sc->poff[CS * CI_WARPS] = (unsigned short)min(run, 65535);
+                }
+                __syncthreads();
+                const int n = sc->poff[CS * CI_WARPS];
+                bool ok = !overflow && n <= CI_GLIST && s1 > 0;
+                float cut2 = lcut;
+                if (ok) {
+                    for (int e = tid; e < n; e += CI_THREADS) {
+                        int lo = 0, hi = CS * CI_WARPS - 1;
+                        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sc->poff[mid] <= e) lo = mid; else hi = mid - 1; }
+                        glist[e] = *(cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]));
+                    }
+                    __syncthreads();
+                    u64 part = 0;
+                    for (int i = tid; i < n; i += CI_THREADS) part += glist[i].q;
+                    const u64 s_band = block_sum_u64(part, sc);
+                    double te = ceil((double)topp * (double)s1);
+                    u64 target = te <= 1.0 ? 1ull : (u64)te;
+                    if (target > s1) target = s1;
+                    ok = s_above < target && target <= s_above + s_band;       // the pivot lies inside the band
+                    if (ok) {
+                        float lp_val;
+                        ok = list_select(glist, n, [&](int i) { return (u64)glist[i].q; }, target - s_above, bins, cand, sc, lp_val);
+                        if (ok) {
+                            cut2 = fmaxf(lcut, lower_logit_for(scale_logit(lp_val, tc), tc, lp_val));
+                            if (cut2 < t_lo) ok = false;                       // a tie partner could lie below the band
+                        }
+                    }
+                }
+                if (ok) {
+                    lcut = cut2;
+                    // add the kept band entries of this warp's own list to its region's kept mass
+                    u64 add = 0;
+                    const int mine = min(wn, CI_WLIST);
+                    for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mylist[j].q;
+                    wkeep += warp_sum_u64(add);
+                } else {
+                    // The estimated band missed the pivot (or a list overflowed): every CTA takes the exact radix
+                    // select by mass, then recomputes its regions' kept mass.  Rare; same result, more time.
+                    const RadixCtx rc = {rowbuf, n_pad, fb_hist, fb_seg, xch, sc, rank, CS};
+                    float lpiv;
+                    if (radix_select(cluster, rc, mass, lcut, true, 0, topp, lpiv))
+                        lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+                    // kept mass of this warp's region under the exact threshold
+                    const float lk3 = fmaxf(lcut, -CI_FLT_MAX);
+                    u64 acc = 0;
+                    for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                        const float4 v = *reinterpret_cast<const float4*>(rowbuf + i0 + lane * 4);
+                        acc += (u64)(v.x >= lk3 ? mass(v.x) : 0u) + (v.y >= lk3 ? mass(v.y) : 0u);
+                        acc += (u64)(v.z >= lk3 ? mass(v.z) : 0u) + (v.w >= lk3 ? mass(v.w) : 0u);
+                    }
+                    wkeep = warp_sum_u64(acc);
+                }
+            }
+            __syncthreads();
+            if (lane == 0) sc->warp_tot[warp] = wkeep;
+            __syncthreads();
+            if (tid == 0) {
+                u64 t = 0;
+                for (int w = 0; w < CI_WARPS; ++w) t += sc->warp_tot[w];
+                xch->cta_mass = t;
+            }
+            __syncthreads();
+            CI_PROF(6);
+            cluster.sync();                                                            // (C) slice masses published
+            CI_PROF(7);
+            u64 my_off = 0;
+            for (int q = 0; q < CS; ++q) {
+                const u64 cm = cluster.map_shared_rank(xch, q)->cta_mass;
+                if (q < rank) my_off += cm;
+                total_mass += cm;
+            }
+            float u = 1.0f;
+            if (a.u != nullptr) u = a.u[row];
+            else if (a.pos != nullptr && a.p.seed != nullptr) {
+                const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
+                                               : (long long)reinterpret_cast<const int*>(a.pos)[b];
+                u = u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
+            }
+            u64 target;
+            {
+                double t = ceil((double)u * (double)total_mass);
+                target = t <= 1.0 ? 1ull : (u64)t;
+                if (target > total_mass) target = total_mass;
+            }
+            const u64 my_mass = xch->cta_mass;
+            token = -1;
+            if (total_mass > 0 && my_off < target && target <= my_off + my_mass) {
+                // the crossing lies in this CTA: find the warp region, then the element
+                u64 woff = my_off;
+                for (int w = 0; w < warp; ++w) woff += sc->warp_tot[w];
+                if (woff < target && target <= woff + wkeep) {
+                    const float lkf = fmaxf(lcut, -CI_FLT_MAX);
+                    u64 run = woff;
+                    for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                        const int i = i0 + lane * 4;
+                        const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+                        u64 q4[4];
+                        q4[0] = v.x >= lkf ? mass(v.x) : 0u; q4[1] = v.y >= lkf ? mass(v.y) : 0u;
+                        q4[2] = v.z >= lkf ? mass(v.z) : 0u; q4[3] = v.w >= lkf ? mass(v.w) : 0u;
+                        const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
+                        const u64 incl = warp_incl_scan_u64(s4, lane);
+                        const u64 grp = __shfl_sync(0xffffffffu, incl, 31);
+                        if (run + grp >= target) {
+                            const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
+                            const int first = __ffs(hit) - 1;
+                            if (lane == first) {
+                                u64 c = run + incl - s4;
+                                int j = 0;
+                                for (; j < 3; ++j) { c += q4[j]; if (c >= target) break; }
+                                if (a.out) a.out[row] = (long long)(slice_lo + i + j);
+                            }
+                            break;
+                        }
+                        run += grp;
+                    }
+                }
+            }
+            if (total_mass == 0) { status |= COLINFER_ROW_DEGENERATE; token = aidx; }
         }
-        if (total_mass == 0) { status |= COLINFER_ROW_DEGENERATE; token = aidx; }
     }
 
     if (rank == 0 && tid == 0) {
-        if (token >= 0 && a.out) a.out[row] = token;                   // greedy, degenerate or failed rows
+        if (token >= 0 && a.out) a.out[row] = token;           // greedy, list-path, degenerate or failed rows
         int hs = 0;
         for (int q = 0; q < CS; ++q) hs |= cluster.map_shared_rank(sc, q)->hist_slow;
         if (hs) status |= COLINFER_ROW_HIST_SLOW;
@@ -531,12 +927,21 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             a.stats[row] = st;
         }
     }
+    CI_PROF(8);
     cluster.sync();                                            // no CTA leaves while a peer may still read its shared memory
+    CI_PROF(9);
+    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
+        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        a.prof[(size_t)blockIdx.x * 16 + 13] = (long long)gt;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ host side
 static int g_cluster_override = 0;
-static const int kFixedSmem = CI_NB * 8 * 2 + CI_MAX_CHUNKS * 8 + (int)sizeof(Xch) + (int)sizeof(Scratch) + 64;
+static long long* g_prof = nullptr;
+static int g_prof_slots = 0;
+static const int kFixedSmem = 24 * 1024 + CI_WARPS * CI_WLIST * (int)sizeof(ListEntry) + CI_MAX_CHUNKS * 8 +
+                              (int)sizeof(Xch) + (int)sizeof(Scratch) + 64;
 
 static int pick_geometry(int V, int dtype, const void* logits, colinfer_geometry* g) {
     if (V <= 0) return 1;
@@ -564,6 +969,37 @@ extern "C" int colinfer_sample_geometry(int V, int dtype, const void* logits, co
     return pick_geometry(V, dtype, logits, out) ? (int)cudaErrorInvalidValue : 0;
 }
 
+extern "C" int colinfer_set_profile_buffer(void* dev, int ctas) {
+    g_prof = reinterpret_cast<long long*>(dev);
+    g_prof_slots = dev ? ctas : 0;
+    return 0;
+}
+
+static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, const colinfer_geometry& g, long long rows, cudaStream_t st) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3((unsigned)(rows * g.cluster), 1, 1);
+    cfg.blockDim = dim3(CI_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)g.smem_bytes;
+    cfg.stream = st;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)g.cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+}
+
+extern "C" int colinfer_max_active_clusters(int V, int dtype) {
+    colinfer_geometry g;
+    if (pick_geometry(V, dtype, nullptr, &g)) return -1;
+    if (cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes) != cudaSuccess) return -2;
+    cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
+    fill_launch(cfg, attr, g, 1024, nullptr);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, k_sample, &cfg) != cudaSuccess) return -3;
+    return n;
+}
+
 extern "C" int colinfer_set_cluster_override(int cluster) {
     if (cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
     g_cluster_override = cluster;
@@ -574,12 +1010,13 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
                                const colinfer_sampler_params* params, const void* pos, int pos_is_i64, const float* u,
                                int64_t* out_ids, colinfer_row_stats* stats, int32_t* status,
                                int B, int R, int V, int flags, void* stream) {
-    if (!logits || !params || (!out_ids && !stats) || B < 0 || R < 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    if (B < 0 || R < 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    if ((long long)B * R == 0) return 0;
+    if (!logits || !params || (!out_ids && !stats)) return (int)cudaErrorInvalidValue;
     if (dtype != COLINFER_F32 && dtype != COLINFER_BF16) return (int)cudaErrorInvalidValue;
     if (!params->temperature || !params->top_k || !params->top_p || !params->log_min_p) return (int)cudaErrorInvalidValue;
     if (out_ids && u == nullptr && (pos == nullptr || params->seed == nullptr)) return (int)cudaErrorInvalidValue;
     if (mask && (W < (V + 31) / 32 || mask_rows < R)) return (int)cudaErrorInvalidValue;
-    if ((long long)B * R == 0) return 0;
     colinfer_geometry g;
     if (pick_geometry(V, dtype, logits, &g)) return (int)cudaErrorInvalidValue;
     if ((long long)B * R * g.cluster > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
@@ -591,21 +1028,12 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     a.pos = pos; a.pos_i64 = pos_is_i64; a.u = u;
     a.out = out_ids; a.stats = stats; a.status = status;
     a.B = B; a.R = R; a.V = V; a.slice_elems = g.slice_elems; a.flags = flags;
+    a.prof = g_prof; a.prof_slots = g_prof_slots;
 
     cudaError_t e = cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return (int)e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((long long)B * R * g.cluster), 1, 1);
-    cfg.blockDim = dim3(CI_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = (size_t)g.smem_bytes;
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)g.cluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
+    fill_launch(cfg, attr, g, (long long)B * R, (cudaStream_t)stream);
     e = cudaLaunchKernelEx(&cfg, k_sample, a);
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();

@@ -137,6 +137,8 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
             raise RuntimeError("SamplerParams.seed is required when no uniforms are passed")
         pos_ptr, pos_i64 = pos.data_ptr(), int(pos.dtype == torch.int64)
     out = torch.empty(B, R, dtype=torch.int64, device=logits.device)
+    if B * R == 0 and not (status or stats):
+        return out
     st = torch.empty(B, R, dtype=torch.int32, device=logits.device) if status else None
     rs = torch.empty(B, R, _lib.ROW_STATS_BYTES, dtype=torch.uint8, device=logits.device) if stats else None
     _lib.check(_lib.lib().colinfer_sample(logits.data_ptr(), dt, mask_ptr, mask_rows, W, C.byref(ps), pos_ptr, pos_i64,

@@ -35,14 +35,14 @@ typedef struct colinfer_sampler_params {
 
 /* Per-row description of the processed distribution, written by colinfer_sample when `stats` is not NULL.
  * The kept set of the row is { t : logit'(t) >= lcut } (logit' = after penalties and mask) and
- * P(t) = exp(logit'(t) / tc - lmax / tc) / (mass_q * 2^-40) on that set. */
+ * P(t) = exp(logit'(t) / tc - lmax / tc) / (mass_q * 2^-30) on that set. */
 typedef struct colinfer_row_stats {
     float    lmax;      /* largest logit' of the row */
     float    lcut;      /* smallest kept logit' value (a threshold; -inf keeps all) */
     float    tc;        /* max(temperature, 1e-6) */
     int32_t  status;    /* COLINFER_ROW_* bits */
     int64_t  argmax;    /* lowest index of the largest logit' */
-    uint64_t mass_q;    /* kept mass in units of 2^-40 */
+    uint64_t mass_q;    /* kept mass in units of 2^-30 */
 } colinfer_row_stats;
 
 enum {
@@ -121,6 +121,13 @@ int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geom
 
 /* Test hook: force the cluster size (1, 2, 4 or 8; 0 = automatic) of later colinfer_sample calls of this process. */
 int colinfer_set_cluster_override(int cluster);
+
+/* Profiling hook: when dev is not NULL, the first `ctas` CTAs of later colinfer_sample launches write 16 int64 each
+ * (clock64 at phase boundaries, %smid, %globaltimer at entry and exit) to dev[ctas * 16].  NULL switches it off. */
+int colinfer_set_profile_buffer(void* dev, int ctas);
+
+/* How many clusters of the sampler's geometry for this vocabulary the current device holds at once (occupancy query). */
+int colinfer_max_active_clusters(int V, int dtype);
 
 /* Library version (major * 100 + minor). */
 int colinfer_version(void);

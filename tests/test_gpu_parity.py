@@ -21,10 +21,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 MARGIN = 1e-6          # fp32 exponentials differ from float64 ones by ~1e-7 relative
 
 
-@pytest.fixture(scope="module", autouse=True)
+@pytest.fixture(autouse=True)
 def _need_cuda():
     assert torch.cuda.is_available(), "the gpu tests need a CUDA device"
-    _lib.lib()
+    _lib.lib().colinfer_set_cluster_override(0)
     yield
     _lib.lib().colinfer_set_cluster_override(0)
 
