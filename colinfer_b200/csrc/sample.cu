@@ -9,11 +9,18 @@
 // Selection is exact.  The kept set is always {logit >= threshold}.  Masses are exp(z - max) rounded to integers in
 // units of 2^-30 and summed as integers, so every sum, every cumulative-mass crossing and the CDF crossing are
 // independent of thread, CTA and cluster geometry and of the other rows in the launch (the reference's row-invariance
-// property).  Thresholds are found in two steps: a fine count histogram over the distance from the row maximum
-// (4096 buckets) locates the bucket of the k-th largest logit exactly, and the bucket of the top-p pivot approximately;
-// the few hundred logits around it are gathered into a list (in token order) and the pivot is found exactly on the
-// list.  If a list would overflow, or the estimated top-p band misses the true pivot, an exact 4-level radix select
-// over the order-preserving 32-bit keys runs instead (slower, same result).
+// property).  How the threshold is found depends on the row's parameters:
+//   top_k <= 128   each CTA bounds its slice's k-th largest logit from below with a histogram of its threads' maxima,
+//                  collects the few logits above that bound in token order, and the cluster's first CTA finishes
+//                  top-k, top-p and the draw exactly on the gathered list (two cluster barriers in all);
+//   larger top_k   a fine count histogram over the distance from the row maximum (4096 buckets, reduced across the
+//                  cluster) gives the bucket of the k-th largest logit; the logits down to it are gathered as above;
+//   top_p alone    the same histogram with per-bucket mass estimates gives the bucket of the top-p pivot approximately;
+//                  one pass sums the exact mass above a narrow band around it and gathers the band, the pivot is found
+//                  exactly on the list, and the draw walks the row once more only inside one warp's region;
+//   neither        one mass pass and the draw.
+// If a list would overflow, or the estimated band misses the true pivot, an exact 4-level radix select over the
+// order-preserving 32-bit keys runs instead (slower, same result).
 //
 // What the reference does in ~25 torch / FlashInfer launches per slot (engine/spec/accept.py:23-52 after
 // engine/runtime/sampler.py:50-56) is one launch here.
@@ -26,13 +33,17 @@
 #define CI_MAX_CHUNKS 16
 #define CI_NB1 4096              // fine buckets over the distance from the row maximum
 #define CI_RANGE 25.0f           // the buckets cover distances up to CI_RANGE * temperature
+#define CI_FASTK 128             // largest top_k handled by the per-slice candidate lists
+#define CI_FASTK_SCALE 128.0f    // buckets per unit logit of the thread-maxima histogram (covers 32 units)
 #define CI_WLIST 64              // list entries per warp
 #define CI_GLIST 1365            // gathered list entries (16 KB)
+#define CI_SEL_BINS 512          // coarse bins of the exact selection on a gathered list
 #define CI_FB_NB 256             // radix buckets per level of the fallback select (8 bits)
 #define CI_MAX_CAND 128          // tied / neighbouring candidates examined one by one in the final list step
 #define CI_PEN_TABLE 2048        // distinct history ids per slice with an O(1) count
 #define CI_WAIT_CYCLES 400000000LL
 #define CI_FLT_MAX 3.402823466e38f
+#define CI_POS_INF (__int_as_float(0x7f800000))
 
 struct SampleArgs {
     const void* logits; int dtype; int use_bulk;
@@ -47,9 +58,11 @@ struct SampleArgs {
 
 struct ListEntry { uint32_t idx; float l; uint32_t q; };
 
-// Values one CTA publishes to its cluster peers.
+// What every CTA writes into each peer's shared memory before the first cluster barrier.
+struct Hello { float lmax; int lidx; int flags; int pad; };   // flags: 1 = a bounded wait gave up, 2 = list overflow, 4 = slow history path
+
+// Values one CTA publishes in its own shared memory for its peers to read after a later barrier.
 struct Xch {
-    float lmax; int lidx;          // slice maximum and its lowest global index
     u64 seg_cnt, seg_est;          // totals of this CTA's reduced bucket segment: counts, estimated mass
     u64 fb_segtot;                 // the same for the fallback radix select
     u64 s_all, s_above;            // band pass: kept mass of the slice, and of its part above the band
@@ -59,6 +72,7 @@ struct Xch {
 };
 
 struct Scratch {
+    Hello hello[8];
     u64 warp_tot[CI_WARPS];
     u64 warp_aux[CI_WARPS];
     float warp_f[CI_WARPS]; int warp_i[CI_WARPS];
@@ -68,6 +82,8 @@ struct Scratch {
     int ncand; float sel_value; int sel_ok;
     int fail;
     int hist_slow;
+    float bcast_f; int bcast_i;
+    u64 mass_in[8];                // kept mass of every CTA's slice, written by the peers
 };
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
@@ -122,9 +138,27 @@ __device__ __forceinline__ u64 bucket_mass_est(int b) {
     return (u64)__float2uint_rn(exp2f(-((float)b + 0.5f) * (CI_RANGE * CI_LOG2E / (float)CI_NB1)) * CI_MASS_SCALE);
 }
 
+__device__ __forceinline__ u64 ceil_target(float frac, u64 total) {
+    const double t = ceil((double)frac * (double)total);
+    u64 q = t <= 1.0 ? 1ull : (u64)t;
+    return q > total ? total : q;
+}
+
+// The row's uniform in (0, 1]: explicit, or Philox keyed by (seed, position + row of the slot), or 1 when no draw is asked.
+__device__ __forceinline__ float row_uniform(const SampleArgs& a, int row, int b, int r) {
+    if (a.u != nullptr) return a.u[row];
+    if (a.pos != nullptr && a.p.seed != nullptr) {
+        const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
+                                       : (long long)reinterpret_cast<const int*>(a.pos)[b];
+        return u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
+    }
+    return 1.0f;
+}
+
 // Exact weighted selection on a gathered list: the value v among the entries with wt > 0 such that
-// W(l > v) < target <= W(l >= v).  256 coarse bins over the entries' key range, then the entries of the pivot bin one by
-// one (a warp each).  Returns false when the pivot bin holds more than CI_MAX_CAND entries.  All threads call.
+// W(l > v) < target <= W(l >= v).  Up to 512 coarse bins over the entries' key range (a shift, so monotone), then the
+// entries of the pivot bin one by one (a warp each).  Returns false when the pivot bin holds more than CI_MAX_CAND
+// entries.  All threads of the CTA call; 1 <= target <= total weight.
 template <class W>
 __device__ bool list_select(const ListEntry* gl, int n, W wt, u64 target, u64* bins, uint32_t* cand, Scratch* sc, float& value) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
@@ -138,21 +172,21 @@ __device__ bool list_select(const ListEntry* gl, int n, W wt, u64 target, u64* b
         kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
     }
     if (lane == 0) { sc->warp_u[warp] = kmin; sc->warp_v[warp] = kmax; }
-    for (int i = tid; i < 256; i += CI_THREADS) bins[i] = 0;
+    for (int i = tid; i < CI_SEL_BINS; i += CI_THREADS) bins[i] = 0;
     if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; sc->sel_value = 0.0f; }
     __syncthreads();
     for (int w = 0; w < CI_WARPS; ++w) { kmin = min(kmin, sc->warp_u[w]); kmax = max(kmax, sc->warp_v[w]); }
-    const u64 span = (u64)(kmax - kmin) + 1ull;
-    auto bin_of = [&](uint32_t k) { return (int)((((u64)(kmax - k)) << 8) / span); };   // descending, 0..255
+    const uint32_t span = kmax - kmin;                                   // bins cover [0, span] >> sh, at most 512
+    const int sh = max(0, 32 - __clz(span) - 9);
     for (int i = tid; i < n; i += CI_THREADS) {
         const u64 w = wt(i);
-        if (w > 0) atomicAdd(&bins[bin_of(f2key(gl[i].l))], w);
+        if (w > 0) atomicAdd(&bins[(kmax - f2key(gl[i].l)) >> sh], w);
     }
     __syncthreads();
     int b_star; u64 before;
-    block_find([&](int i) { return bins[i]; }, 256, target, sc, b_star, before);
+    block_find([&](int i) { return bins[i]; }, CI_SEL_BINS, target, sc, b_star, before);
     for (int i = tid; i < n; i += CI_THREADS) {
-        if (wt(i) > 0 && bin_of(f2key(gl[i].l)) == b_star) {
+        if (wt(i) > 0 && (int)((kmax - f2key(gl[i].l)) >> sh) == b_star) {
             const int slot = atomicAdd(&sc->ncand, 1);
             if (slot < CI_MAX_CAND) cand[slot] = (uint32_t)i;
         }
@@ -163,12 +197,10 @@ __device__ bool list_select(const ListEntry* gl, int n, W wt, u64 target, u64* b
     for (int c = warp; c < nc; c += CI_WARPS) {
         const uint32_t kc = f2key(gl[cand[c]].l);
         u64 gt = 0, eq = 0;
-        for (int i = lane; i < n; i += 32) {
-            const u64 w = wt(i);
-            if (w > 0) {
-                const uint32_t k = f2key(gl[i].l);
-                if (bin_of(k) == b_star) { if (k > kc) gt += w; else if (k == kc) eq += w; }
-            }
+        for (int j = lane; j < nc; j += 32) {                            // only the pivot bin's entries matter
+            const uint32_t k = f2key(gl[cand[j]].l);
+            const u64 w = wt((int)cand[j]);
+            if (k > kc) gt += w; else if (k == kc) eq += w;
         }
         gt = warp_sum_u64(gt); eq = warp_sum_u64(eq);
         if (lane == 0 && before + gt < target && target <= before + gt + eq) { sc->sel_value = gl[cand[c]].l; sc->sel_ok = 1; }
@@ -228,12 +260,8 @@ __device__ bool radix_select(cg::cluster_group& cluster, const RadixCtx& c, cons
         u64 grand = 0, segtots[8];
         for (int q = 0; q < c.CS; ++q) { segtots[q] = cluster.map_shared_rank(c.xch, q)->fb_segtot; grand += segtots[q]; }
         if (lvl == 0) {
-            if (by_mass) {
-                double t = ceil((double)topp * (double)grand);
-                u64 tq = t <= 1.0 ? 1ull : (u64)t;
-                if (tq > grand) tq = grand;
-                target = tq;
-            } else if (target >= grand) return false;
+            if (by_mass) target = ceil_target(topp, grand);
+            else if (target >= grand) return false;
         }
         if (grand == 0) return false;
         int s_star = c.CS - 1; u64 before_seg = 0, run = 0;
@@ -251,8 +279,112 @@ __device__ bool radix_select(cg::cluster_group& cluster, const RadixCtx& c, cons
     return true;
 }
 
+// Gathers the per-warp lists of every CTA of the cluster into glist, in token order (CTA rank, warp, position).
+// Returns the number of entries, or -1 when a list overflowed or the total exceeds the capacity.  with_mass: compute
+// the entries' masses here (lists collected before the row maximum was known carry none).  All threads call.
+__device__ int gather_lists(cg::cluster_group& cluster, int CS, Xch* xch, ListEntry* ownlist, ListEntry* glist, Scratch* sc,
+                            const MassFn* mass) {
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    const int np = CS * CI_WARPS;                                          // (CTA, warp) pairs, at most 128
+    int overflow = 0;
+    if (tid < CS) overflow = cluster.map_shared_rank(xch, tid)->list_overflow;
+    if (tid < np) sc->pcount[tid] = cluster.map_shared_rank(xch, tid / CI_WARPS)->wcount[tid % CI_WARPS];
+    overflow = __syncthreads_or(overflow);
+    if (warp == 0) {                                                       // exclusive prefix of up to 128 counts
+        int c4[4], s = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { c4[j] = lane * 4 + j < np ? sc->pcount[lane * 4 + j] : 0; s += c4[j]; }
+        int incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+        int run = incl - s;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { if (lane * 4 + j < np) sc->poff[lane * 4 + j] = (unsigned short)run; run += c4[j]; }
+        if (lane == 31) sc->poff[np] = (unsigned short)min(incl, 65535);
+    }
+    __syncthreads();
+    const int n = sc->poff[np];
+    if (overflow || n > CI_GLIST) return -1;
+    for (int e = tid; e < n; e += CI_THREADS) {
+        int lo = 0, hi = np - 1;                                           // last pair p with poff[p] <= e
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sc->poff[mid] <= e) lo = mid; else hi = mid - 1; }
+        ListEntry en = *(cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]));
+        if (mass) en.q = (*mass)(en.l);
+        glist[e] = en;
+    }
+    __syncthreads();
+    return n;
+}
+
+// Top-k, top-p and the draw on a gathered list that is known to hold every logit >= tl of the row (tl below the
+// top-k pivot).  Returns false when the result cannot be trusted from the list alone (the caller falls back).
+// On success: token, lcut (final threshold) and total (kept mass).  All threads of the CTA call.
+__device__ bool finish_on_list(const ListEntry* glist, int n, float tl, float lcut_in, float tc, int kk, bool need_topp,
+                               float topp, float u, u64* bins, uint32_t* cand, Scratch* sc,
+                               long long& token, float& lcut, u64& total) {
+    const int tid = threadIdx.x;
+    float cut = lcut_in;
+    u64 cnt = 0;
+    for (int i = tid; i < n; i += CI_THREADS) cnt += glist[i].l >= cut ? 1 : 0;
+    const u64 survivors = block_sum_u64(cnt, sc);
+    if (survivors == 0) return false;
+    if ((u64)kk <= survivors) {                                            // else fewer than k survive min-p: top-k removes nothing
+        float lk_val;
+        if (!list_select(glist, n, [&](int i) { return (u64)(glist[i].l >= cut ? 1 : 0); }, (u64)kk, bins, cand, sc, lk_val))
+            return false;
+        cut = fmaxf(cut, lower_logit_for(scale_logit(lk_val, tc), tc, lk_val));
+        if (cut < tl) return false;                                        // a tie partner could lie outside the list
+    }
+    if (need_topp) {
+        u64 part = 0;
+        for (int i = tid; i < n; i += CI_THREADS) if (glist[i].l >= cut) part += glist[i].q;
+        const u64 s1 = block_sum_u64(part, sc);
+        if (s1 == 0) return false;
+        float lp_val;
+        const float c0 = cut;
+        if (!list_select(glist, n, [&](int i) { return (u64)(glist[i].l >= c0 ? glist[i].q : 0u); }, ceil_target(topp, s1), bins,
+                         cand, sc, lp_val))
+            return false;
+        cut = fmaxf(cut, lower_logit_for(scale_logit(lp_val, tc), tc, lp_val));
+        if (cut < tl) return false;
+    }
+    u64 part = 0;
+    for (int i = tid; i < n; i += CI_THREADS) if (glist[i].l >= cut) part += glist[i].q;
+    total = block_sum_u64(part, sc);
+    if (total == 0) return false;
+    int at; u64 before;
+    block_find([&](int i) { return (u64)(glist[i].l >= cut ? glist[i].q : 0u); }, n, ceil_target(u, total), sc, at, before);
+    token = (long long)glist[at].idx;
+    lcut = cut;
+    return true;
+}
+
+// Appends the components of one float4 group selected by the 4-bit mask mk to the warp's list, in token order.
+// wn is the warp's running count (uniform over the warp); entries beyond CI_WLIST are dropped and counted.
+__device__ __forceinline__ void warp_append(ListEntry* mylist, int& wn, unsigned mk, const float* e4, const uint32_t* q4,
+                                            uint32_t idx0, int lane) {
+    const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
+    if (!any) return;
+    const int c = __popc(mk);
+    int pre = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += t; }
+    const int tot = __shfl_sync(0xffffffffu, pre, 31);
+    int at = wn + pre - c;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (mk & (1u << j)) {
+            if (at < CI_WLIST) { mylist[at].idx = idx0 + j; mylist[at].l = e4[j]; mylist[at].q = q4 ? q4[j] : 0u; }
+            ++at;
+        }
+    }
+    wn += tot;
+}
+
 extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __grid_constant__ SampleArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
+    // Every CTA announces that it runs; the matching wait comes just before the first write into a peer's shared memory.
+    cluster.barrier_arrive();
     const int CS = (int)cluster.num_blocks();
     const int rank = (int)cluster.block_rank();
     const int row = blockIdx.x / CS;
@@ -264,6 +396,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     const int slice_lo = rank * slice_cap;
     const int slice_len = max(0, min(slice_cap, V - slice_lo));
     const int n_pad = (slice_len + 127) & ~127;               // processed elements (tail holds -inf)
+    const int nchunks = (slice_len + CI_CHUNK - 1) / CI_CHUNK;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* rowbuf = reinterpret_cast<float*>(smem_raw);
@@ -271,8 +404,8 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     uint32_t* hist1 = reinterpret_cast<uint32_t*>(hreg);                      // [CI_NB1] fine counts
     uint32_t* segcnt = reinterpret_cast<uint32_t*>(hreg + CI_NB1 * 4);        // [<= 2048] reduced segment
     ListEntry* glist = reinterpret_cast<ListEntry*>(hreg);                    // gathered list, over hist1
-    u64* bins = reinterpret_cast<u64*>(hreg + CI_NB1 * 4);                    // [256] list_select bins, over segcnt
-    uint32_t* cand = reinterpret_cast<uint32_t*>(hreg + CI_NB1 * 4 + 256 * 8);
+    u64* bins = reinterpret_cast<u64*>(hreg + CI_NB1 * 4);                    // [512] selection bins, over segcnt
+    uint32_t* cand = reinterpret_cast<uint32_t*>(hreg + CI_NB1 * 4 + CI_SEL_BINS * 8);
     u64* fb_hist = reinterpret_cast<u64*>(hreg);                              // fallback radix, over hist1
     u64* fb_seg = fb_hist + CI_FB_NB;
     ListEntry* ownlist = reinterpret_cast<ListEntry*>(hreg + 24 * 1024);      // [CI_WARPS][CI_WLIST]
@@ -284,6 +417,29 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     const int nw = slice_cap >> 5;
     uint32_t* pen_prefix = pen_bits + nw;
     uint32_t* pen_cnt = pen_prefix + nw;
+
+    // ---------------------------------------------------------------------------------------- start the HBM read
+    // One thread sets up the mbarriers and issues every bulk copy of the slice at once, before anything else.
+    if (tid == 0) {
+        sc->fail = 0; sc->hist_slow = 0; xch->list_overflow = 0;
+        if (a.use_bulk) {
+            for (int c = 0; c < nchunks; ++c) mbar_init(&mbar[c], 1);
+            fence_mbar_init();
+            fence_proxy_async();
+            const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)row * V + slice_lo;
+            for (int c = 0; c < nchunks; ++c) {
+                const int len = min(CI_CHUNK, slice_len - c * CI_CHUNK);
+                mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
+                bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
+            }
+        }
+    }
+    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
+        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.prof[(size_t)blockIdx.x * 16 + 15] = (long long)gt; a.prof[(size_t)blockIdx.x * 16 + 14] = smid;
+    }
+    CI_PROF(0);
 
     // ---------------------------------------------------------------------------------------- parameters of the slot
     const float T = a.p.temperature[b];
@@ -297,35 +453,14 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     hlen = max(0, min(hlen, a.p.hist_stride));
     const bool has_pen = hlen > 0 && !(rp == 1.0f && pp == 0.0f && fp == 0.0f);
     const int32_t* mrow = a.mask ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
-    const int nchunks = (slice_len + CI_CHUNK - 1) / CI_CHUNK;
+    const int kk = a.p.top_k[b];
+    const float topp = a.p.top_p[b];
+    const float log_min_p = a.p.log_min_p[b];
+    const bool fastk = sampled && kk >= 1 && kk <= CI_FASTK && kk < V;     // identical in every CTA of the cluster
 
-    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
-        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        a.prof[(size_t)blockIdx.x * 16 + 15] = (long long)gt; a.prof[(size_t)blockIdx.x * 16 + 14] = smid;
-    }
-    CI_PROF(0);
-    // ---------------------------------------------------------------------------------------- start the HBM read
-    if (tid == 0) {
-        sc->fail = 0; sc->hist_slow = 0;
-        if (a.use_bulk) {
-            for (int c = 0; c < nchunks; ++c) mbar_init(&mbar[c], 1);
-            fence_mbar_init();
-            fence_proxy_async();
-        }
-    }
-    __syncthreads();
-    if (a.use_bulk && tid == 0) {
-        const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)row * V + slice_lo;
-        for (int c = 0; c < nchunks; ++c) {
-            const int len = min(CI_CHUNK, slice_len - c * CI_CHUNK);
-            mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
-            bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
-        }
-    }
     // tail of the slice buffer: -inf (never selected, zero mass); disjoint from the bulk-copy destinations
     for (int i = slice_len + tid; i < n_pad; i += CI_THREADS) rowbuf[i] = CI_NEG_INF;
-    __syncthreads();
+    __syncthreads();                                           // mbarriers initialised, tail filled
 
     // ---------------------------------------------------------------------------------------- penalty tables
     // bitmap of the slice's tokens that occur in the history, their ranks, and the occurrence count per rank
@@ -450,6 +585,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         }
     }
     CI_PROF(2);
+    const float tmax = lmax;                                    // this thread's own maximum (used by the top-k bound)
     // block reduce (largest value, lowest index among equals)
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
@@ -458,468 +594,424 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (om > lmax || (om == lmax && oi < lidx)) { lmax = om; lidx = oi; }
     }
     if (lane == 0) { sc->warp_f[warp] = lmax; sc->warp_i[warp] = lidx; }
+    if (fastk) for (int i = tid; i < CI_NB1; i += CI_THREADS) hist1[i] = 0u;   // (the penalty tables are done with)
     __syncthreads();
-    if (tid == 0) {
+    {
         float bm = sc->warp_f[0]; int bi = sc->warp_i[0];
+#pragma unroll
         for (int w = 1; w < CI_WARPS; ++w) {
             const float om = sc->warp_f[w]; const int oi = sc->warp_i[w];
             if (om > bm || (om == bm && oi < bi)) { bm = om; bi = oi; }
         }
-        xch->lmax = bm; xch->lidx = bi; xch->list_overflow = 0;
+        lmax = bm; lidx = bi;                                   // the slice maximum, in every thread
     }
-    __syncthreads();
+
+    // warp w owns the contiguous region [r_lo, r_hi) of the slice; lanes interleave float4 groups, so the token
+    // order inside a region is (step, lane, component).
+    const int reg = ((n_pad / 128 + CI_WARPS - 1) / CI_WARPS) * 128;
+    const int r_lo = min(warp * reg, n_pad), r_hi = min(r_lo + reg, n_pad);
+    ListEntry* mylist = ownlist + warp * CI_WLIST;
+
+    // ---------------------------------------------------------------------------------------- small top-k: candidates of the slice
+    // The k-th largest of the threads' maxima bounds the slice's k-th largest logit from below, and every logit of the
+    // row's top k is among its own slice's top k: the logits >= that bound, over all slices, contain the row's top k.
+    float tl_fast = CI_NEG_INF;
+    int my_count = 0;
+    if (fastk) {
+        if (tmax > CI_NEG_INF) atomicAdd(&hist1[min(CI_NB1 - 1, __float2int_rz((lmax - tmax) * CI_FASTK_SCALE))], 1u);
+        __syncthreads();
+        u64 part = 0;
+        for (int i = tid; i < CI_NB1; i += CI_THREADS) part += hist1[i];
+        const u64 have = block_sum_u64(part, sc);
+        if (have >= (u64)kk) {
+            int bk; u64 before;
+            block_find([&](int i) { return (u64)hist1[i]; }, CI_NB1, (u64)kk, sc, bk, before);
+            tl_fast = bk >= CI_NB1 - 1 ? -CI_FLT_MAX : lmax - ((float)(bk + 1) + 0.01f) / CI_FASTK_SCALE - fabsf(lmax) * 1e-6f;
+        } else tl_fast = -CI_FLT_MAX;                           // fewer than k threads saw a finite logit: take them all
+        int wn = 0;
+        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+            const int i = i0 + lane * 4;
+            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+            const float e4[4] = {v.x, v.y, v.z, v.w};
+            const unsigned mk = (v.x >= tl_fast ? 1u : 0u) | (v.y >= tl_fast ? 2u : 0u) | (v.z >= tl_fast ? 4u : 0u) | (v.w >= tl_fast ? 8u : 0u);
+            warp_append(mylist, wn, mk, e4, nullptr, (uint32_t)(slice_lo + i), lane);
+        }
+        if (lane == 0) {
+            xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
+            sc->warp_i[warp] = wn;
+        }
+        __syncthreads();
+        for (int w = 0; w < CI_WARPS; ++w) my_count += sc->warp_i[w];
+        if (my_count > 0xFFFF) my_count = 0xFFFF;
+        for (int w = 0; w < CI_WARPS; ++w) if (sc->warp_i[w] > CI_WLIST) my_count = 0xFFFF;   // overflow marker
+    }
+
+    // ---------------------------------------------------------------------------------------- first exchange
     CI_PROF(3);
-    cluster.sync();                                                                    // (1) slice maxima published
+    cluster.barrier_wait();                                     // every CTA of the cluster runs: peers' memory may be written
+    if (tid < CS) {
+        Hello h;
+        h.lmax = lmax; h.lidx = lidx;
+        h.flags = (sc->fail ? 1 : 0) | (sc->hist_slow ? 4 : 0);
+        h.pad = my_count;
+        cluster.map_shared_rank(sc, tid)->hello[rank] = h;
+    }
+    cluster.sync();                                                                    // (1) slice maxima (and list sizes) exchanged
     CI_PROF(4);
-    float L = CI_NEG_INF; int aidx = 0x7fffffff; int any_fail = 0;
+    float L = CI_NEG_INF; int aidx = 0x7fffffff; int hflags = 0; int fast_total = 0; bool fast_overflow = false;
     for (int q = 0; q < CS; ++q) {
-        const Xch* px = cluster.map_shared_rank(xch, q);
-        const Scratch* ps = cluster.map_shared_rank(sc, q);
-        const float om = px->lmax; const int oi = px->lidx;
-        if (om > L || (om == L && oi < aidx)) { L = om; aidx = oi; }
-        any_fail |= ps->fail;
+        const Hello h = sc->hello[q];
+        if (h.lmax > L || (h.lmax == L && h.lidx < aidx)) { L = h.lmax; aidx = h.lidx; }
+        hflags |= h.flags;
+        fast_total += h.pad;
+        if (h.pad >= 0xFFFF) fast_overflow = true;
     }
     if (aidx == 0x7fffffff) aidx = 0;
 
-    int status = any_fail ? COLINFER_ROW_TIMEOUT : 0;
-    const bool finite_max = (L > CI_NEG_INF) && (L < __int_as_float(0x7f800000));
+    int status = ((hflags & 1) ? COLINFER_ROW_TIMEOUT : 0) | ((hflags & 4) ? COLINFER_ROW_HIST_SLOW : 0);
+    const bool finite_max = (L > CI_NEG_INF) && (L < CI_POS_INF);
     if (sampled && !finite_max) status |= COLINFER_ROW_DEGENERATE;
-    const bool do_dist = sampled && finite_max && !any_fail;   // identical in every CTA of the cluster
+    const bool do_dist = sampled && finite_max && !(hflags & 1);   // identical in every CTA of the cluster
 
     float lcut = CI_NEG_INF;
     u64 total_mass = 0;
     long long token = aidx;
 
-    if (do_dist) {
-        const float m = scale_logit(L, tc);
-        MassFn mass;
-        mass.init(tc, m);
-        // ------------------------------------------------------------------------------------ min-p threshold
-        const float thr = __fadd_rn(m, a.p.log_min_p[b]);
-        lcut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
-        const int kk = a.p.top_k[b];
-        const float topp = a.p.top_p[b];
-        bool need_topk = kk > 0 && kk < V;
-        bool need_topp = topp < 1.0f;
+    if (!do_dist) {
+        // greedy, degenerate or failed row: the argmax.  Nobody reads a peer's memory after the barrier: leave at once.
+        if (rank == 0 && tid == 0) {
+            if (a.out) a.out[row] = token;
+            if (a.status) a.status[row] = status;
+            if (a.stats) {
+                colinfer_row_stats st;
+                st.lmax = L; st.lcut = lcut; st.tc = tc; st.status = status; st.argmax = aidx; st.mass_q = 0;
+                a.stats[row] = st;
+            }
+        }
+        return;
+    }
 
-        // warp w owns the contiguous region [r_lo, r_hi) of the slice; lanes interleave float4 groups, so the token
-        // order inside a region is (step, lane, component).
-        const int reg = ((n_pad / 128 + CI_WARPS - 1) / CI_WARPS) * 128;
-        const int r_lo = min(warp * reg, n_pad), r_hi = min(r_lo + reg, n_pad);
-        ListEntry* mylist = ownlist + warp * CI_WLIST;
+    const float m = scale_logit(L, tc);
+    MassFn mass;
+    mass.init(tc, m);
+    // ---------------------------------------------------------------------------------------- min-p threshold
+    const float thr = __fadd_rn(m, log_min_p);
+    lcut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
+    bool need_topk = kk > 0 && kk < V;
+    const bool need_topp = topp < 1.0f;
+    const float u = row_uniform(a, row, b, r);
 
-        enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
-        int path = PATH_PURE;
-        float t_hi = CI_NEG_INF, t_lo = __int_as_float(0x7f800000);   // band thresholds (PATH_BAND), list threshold (PATH_LIST: t_lo)
+    // ---------------------------------------------------------------------------------------- small top-k: the first CTA finishes on the list
+    if (fastk) {
+        int ok = 0;
+        if (!fast_overflow && fast_total <= CI_GLIST && fast_total > 0) {
+            if (rank == 0) {
+                const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, &mass);
+                // the list holds every logit of the row's top k; entries below the min-p threshold carry no weight
+                float tl_all = CI_NEG_INF;                      // no lower bound is needed: the pivot is inside the list
+                if (n > 0 && finish_on_list(glist, n, tl_all, lcut, tc, kk, need_topp, topp, u, bins, cand, sc, token, lcut, total_mass)) ok = 1;
+            }
+        }
+        // the first CTA tells the others whether the row is done (they only wait; their lists had to stay readable)
+        if (rank == 0 && tid < CS) cluster.map_shared_rank(sc, tid)->bcast_i = ok;
+        cluster.sync();                                                                // (F) row finished, or not
+        ok = sc->bcast_i;
+        if (ok) {
+            if (rank == 0 && tid == 0) {
+                if (a.out) a.out[row] = token;
+                if (a.status) a.status[row] = status;
+                if (a.stats) {
+                    colinfer_row_stats st;
+                    st.lmax = L; st.lcut = lcut; st.tc = tc; st.status = status; st.argmax = aidx; st.mass_q = total_mass;
+                    a.stats[row] = st;
+                }
+            }
+            return;
+        }
+        __syncthreads();
+    }
 
-        if (need_topk || need_topp) {
-            // -------------------------------------------------------------------------------- fine count histogram
-            const float SC = (float)CI_NB1 / (CI_RANGE * tc);
-            const float lk = fmaxf(lcut, -CI_FLT_MAX);         // excludes -inf (masked / padding) as well
-            for (int i = tid; i < CI_NB1; i += CI_THREADS) hist1[i] = 0u;
-            __syncthreads();
-            {
-                const float4* row4 = reinterpret_cast<const float4*>(rowbuf);
-                for (int i = tid; i * 4 < n_pad; i += CI_THREADS) {
-                    const float4 v = row4[i];
-                    const float e4[4] = {v.x, v.y, v.z, v.w};
+    enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
+    int path = PATH_PURE;
+    float t_hi = CI_NEG_INF, t_lo = CI_POS_INF;                 // band thresholds (PATH_BAND), list threshold (PATH_LIST: t_lo)
+
+    if (need_topk || need_topp) {
+        // ------------------------------------------------------------------------------------ fine count histogram
+        const float SC = (float)CI_NB1 / (CI_RANGE * tc);
+        const float lk = fmaxf(lcut, -CI_FLT_MAX);             // excludes -inf (masked / padding) as well
+        for (int i = tid; i < CI_NB1; i += CI_THREADS) hist1[i] = 0u;
+        if (tid == 0) xch->list_overflow = 0;
+        __syncthreads();
+        {
+            const float4* row4 = reinterpret_cast<const float4*>(rowbuf);
+            for (int i = tid; i * 4 < n_pad; i += CI_THREADS) {
+                const float4 v = row4[i];
+                const float e4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (e4[j] >= lk) atomicAdd(&hist1[min(CI_NB1 - 1, __float2int_rz((L - e4[j]) * SC))], 1u);
-                    }
-                }
-            }
-            __syncthreads();
-            cluster.sync();                                                            // (A) local histograms complete
-            // each CTA reduces its segment of the buckets over the cluster
-            const int G = CI_NB1 / CS;
-            uint32_t* myseg = (CS == 1) ? hist1 : segcnt;
-            u64 pc = 0, pe = 0;
-            for (int g = tid; g < G; g += CI_THREADS) {
-                uint32_t sum = 0;
-                if (CS == 1) sum = hist1[g];
-                else {
-                    for (int q = 0; q < CS; ++q) sum += cluster.map_shared_rank(hist1, q)[rank * G + g];
-                    segcnt[g] = sum;
-                }
-                pc += sum;
-                pe += (u64)sum * bucket_mass_est(rank * G + g);
-            }
-            const u64 totc = block_sum_u64(pc, sc);
-            const u64 tote = block_sum_u64(pe, sc);
-            if (tid == 0) { xch->seg_cnt = totc; xch->seg_est = tote; }
-            __syncthreads();
-            cluster.sync();                                                            // (B) reduced segments published
-            u64 segc[8], sege[8], survivors = 0, est_total = 0;
-            for (int q = 0; q < CS; ++q) {
-                const Xch* px = cluster.map_shared_rank(xch, q);
-                segc[q] = px->seg_cnt; sege[q] = px->seg_est;
-                survivors += segc[q]; est_total += sege[q];
-            }
-            if (need_topk && (u64)kk >= survivors) need_topk = false;   // fewer survivors than k: top-k removes nothing
-            if (need_topk) {
-                // bucket of the k-th largest logit, exactly
-                int s_star = CS - 1; u64 before_seg = 0, run = 0;
-                for (int q = 0; q < CS; ++q) {
-                    if (run + segc[q] >= (u64)kk) { s_star = q; before_seg = run; break; }
-                    run += segc[q];
-                }
-                const uint32_t* pseg = cluster.map_shared_rank(myseg, s_star);
-                int g_star; u64 before;
-                block_find([&](int i) { return (u64)pseg[i]; }, G, (u64)kk - before_seg, sc, g_star, before);
-                const int bk = s_star * G + g_star;
-                const u64 n_upto = before_seg + before + pseg[g_star];
-                if (bk >= CI_NB1 - 3 || n_upto > CI_GLIST - 64) path = PATH_FALLBACK;
-                else {
-                    path = PATH_LIST;
-                    // every element of buckets <= bk + 1 satisfies l >= t_lo (a slightly wider set is harmless)
-                    t_lo = L - ((float)(bk + 2) + 0.01f) / SC;
-                    t_lo = t_lo - fabsf(L) * 1e-6f;
-                }
-            } else if (need_topp) {
-                // bucket where the descending cumulative estimated mass reaches top_p of the estimated total
-                if (est_total == 0) path = PATH_FALLBACK;
-                else {
-                    double te = ceil((double)topp * (double)est_total);
-                    u64 target = te <= 1.0 ? 1ull : (u64)te;
-                    if (target > est_total) target = est_total;
-                    int s_star = CS - 1; u64 before_seg = 0, run = 0;
-                    for (int q = 0; q < CS; ++q) {
-                        if (run + sege[q] >= target) { s_star = q; before_seg = run; break; }
-                        run += sege[q];
-                    }
-                    const uint32_t* pseg = cluster.map_shared_rank(myseg, s_star);
-                    int g_star; u64 before;
-                    block_find([&](int i) { return (u64)pseg[i] * bucket_mass_est(s_star * G + i); }, G, target - before_seg, sc, g_star, before);
-                    const int bp = s_star * G + g_star;
-                    const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
-                    if (bp + dn + 2 >= CI_NB1) path = PATH_FALLBACK;
-                    else {
-                        path = PATH_BAND;
-                        t_hi = bp - up <= 0 ? __int_as_float(0x7f800000) : L - (float)(bp - up) / SC;
-                        t_lo = L - (float)(bp + dn + 1) / SC;
-                    }
+                for (int j = 0; j < 4; ++j) {
+                    if (e4[j] >= lk) atomicAdd(&hist1[min(CI_NB1 - 1, __float2int_rz((L - e4[j]) * SC))], 1u);
                 }
             }
         }
-        CI_PROF(5);
-
-        // ------------------------------------------------------------------------------------ list path: top-k (then top-p) on a gathered list
-        bool done = false;
-        if (path == PATH_LIST) {
-            const float tl = fmaxf(fmaxf(t_lo, lcut), -CI_FLT_MAX);
-            int wn = 0;
-            for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-                const int i = i0 + lane * 4;
-                const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-                const unsigned mk = (v.x >= tl ? 1u : 0u) | (v.y >= tl ? 2u : 0u) | (v.z >= tl ? 4u : 0u) | (v.w >= tl ? 8u : 0u);
-                const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
-                if (any) {
-                    const int c = __popc(mk);
-                    int pre = c;
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += t; }
-                    const int tot = __shfl_sync(0xffffffffu, pre, 31);
-                    int at = wn + pre - c;
-                    const float e4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (mk & (1u << j)) {
-                            if (at < CI_WLIST) { mylist[at].idx = (uint32_t)(slice_lo + i + j); mylist[at].l = e4[j]; mylist[at].q = 0u; }
-                            ++at;
-                        }
-                    }
-                    wn += tot;
+        __syncthreads();
+        CI_PROF(10);
+        cluster.sync();                                                                // (A) local histograms complete
+        CI_PROF(11);
+        // each CTA reduces its segment of the buckets over the cluster
+        const int G = CI_NB1 / CS;
+        uint32_t* myseg = (CS == 1) ? hist1 : segcnt;
+        u64 pc = 0, pe = 0;
+        for (int g = tid; g < G; g += CI_THREADS) {
+            uint32_t sum = 0;
+            if (CS == 1) sum = hist1[g];
+            else {
+                for (int q = 0; q < CS; ++q) sum += cluster.map_shared_rank(hist1, q)[rank * G + g];
+                segcnt[g] = sum;
+            }
+            pc += sum;
+            pe += (u64)sum * bucket_mass_est(rank * G + g);
+        }
+        const u64 totc = block_sum_u64(pc, sc);
+        const u64 tote = block_sum_u64(pe, sc);
+        if (tid == 0) { xch->seg_cnt = totc; xch->seg_est = tote; }
+        __syncthreads();
+        cluster.sync();                                                                // (B) reduced segments published
+        CI_PROF(12);
+        u64 segc[8], sege[8], survivors = 0, est_total = 0;
+        for (int q = 0; q < CS; ++q) {
+            const Xch* px = cluster.map_shared_rank(xch, q);
+            segc[q] = px->seg_cnt; sege[q] = px->seg_est;
+            survivors += segc[q]; est_total += sege[q];
+        }
+        if (need_topk && (u64)kk >= survivors) need_topk = false;   // fewer survivors than k: top-k removes nothing
+        if (need_topk) {
+            // bucket of the k-th largest logit, exactly
+            int s_star = CS - 1; u64 before_seg = 0, run = 0;
+            for (int q = 0; q < CS; ++q) {
+                if (run + segc[q] >= (u64)kk) { s_star = q; before_seg = run; break; }
+                run += segc[q];
+            }
+            const uint32_t* pseg = cluster.map_shared_rank(myseg, s_star);
+            int g_star; u64 before;
+            block_find([&](int i) { return (u64)pseg[i]; }, G, (u64)kk - before_seg, sc, g_star, before);
+            const int bk = s_star * G + g_star;
+            const u64 n_upto = before_seg + before + pseg[g_star];
+            if (bk >= CI_NB1 - 3 || n_upto > CI_GLIST - 64) path = PATH_FALLBACK;
+            else {
+                path = PATH_LIST;
+                // every element of buckets <= bk + 1 satisfies l >= t_lo (a slightly wider set is harmless)
+                t_lo = L - ((float)(bk + 2) + 0.01f) / SC - fabsf(L) * 1e-6f;
+            }
+        } else if (need_topp) {
+            // bucket where the descending cumulative estimated mass reaches top_p of the estimated total
+            if (est_total == 0) path = PATH_FALLBACK;
+            else {
+                const u64 target = ceil_target(topp, est_total);
+                int s_star = CS - 1; u64 before_seg = 0, run = 0;
+                for (int q = 0; q < CS; ++q) {
+                    if (run + sege[q] >= target) { s_star = q; before_seg = run; break; }
+                    run += sege[q];
+                }
+                const uint32_t* pseg = cluster.map_shared_rank(myseg, s_star);
+                int g_star; u64 before;
+                block_find([&](int i) { return (u64)pseg[i] * bucket_mass_est(s_star * G + i); }, G, target - before_seg, sc, g_star, before);
+                const int bp = s_star * G + g_star;
+                const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
+                if (bp + dn + 2 >= CI_NB1) path = PATH_FALLBACK;
+                else {
+                    path = PATH_BAND;
+                    t_hi = bp - up <= 0 ? CI_POS_INF : L - (float)(bp - up) / SC;
+                    t_lo = L - (float)(bp + dn + 1) / SC;
                 }
             }
+        }
+    }
+    CI_PROF(5);
+
+    // ---------------------------------------------------------------------------------------- large top-k (then top-p) on a gathered list
+    bool done = false;
+    if (path == PATH_LIST) {
+        const float tl = fmaxf(fmaxf(t_lo, lcut), -CI_FLT_MAX);
+        int wn = 0;
+        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+            const int i = i0 + lane * 4;
+            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+            const float e4[4] = {v.x, v.y, v.z, v.w};
+            const unsigned mk = (v.x >= tl ? 1u : 0u) | (v.y >= tl ? 2u : 0u) | (v.z >= tl ? 4u : 0u) | (v.w >= tl ? 8u : 0u);
+            warp_append(mylist, wn, mk, e4, nullptr, (uint32_t)(slice_lo + i), lane);
+        }
+        if (lane == 0) {
+            xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
+            if (wn > CI_WLIST) xch->list_overflow = 1;
+        }
+        __syncthreads();
+        CI_PROF(6);
+        cluster.sync();                                                                // (L) lists published
+        // every CTA gathers the lists and finishes alike (identical inputs, identical decisions)
+        const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, &mass);
+        if (n > 0 && finish_on_list(glist, n, tl, lcut, tc, kk, need_topp, topp, u, bins, cand, sc, token, lcut, total_mass)) done = true;
+        else path = PATH_FALLBACK;
+    }
+
+    // ---------------------------------------------------------------------------------------- fallback: exact radix select over the 32-bit keys
+    if (path == PATH_FALLBACK) {
+        // (a CTA reaches this point only after every peer finished reading its reduced segment and its lists: those
+        // reads precede the peers' next cluster barrier, and the first write below follows this CTA's next barrier)
+        const RadixCtx rc = {rowbuf, n_pad, fb_hist, fb_seg, xch, sc, rank, CS};
+        float lpiv;
+        if (kk > 0 && kk < V && radix_select(cluster, rc, mass, lcut, false, (u64)kk, topp, lpiv))
+            lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+        if (need_topp && radix_select(cluster, rc, mass, lcut, true, 0, topp, lpiv))
+            lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+        path = PATH_PURE;
+        t_hi = CI_NEG_INF; t_lo = CI_POS_INF;
+    }
+
+    // ---------------------------------------------------------------------------------------- mass pass and inverse CDF over the row
+    if (!done) {
+        const bool band = path == PATH_BAND;
+        const float lk = fmaxf(lcut, -CI_FLT_MAX);
+        u64 acc_all = 0, acc_above = 0;
+        int wn = 0;
+        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+            const int i = i0 + lane * 4;
+            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+            const float e4[4] = {v.x, v.y, v.z, v.w};
+            uint32_t q4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q4[j] = e4[j] >= lk ? mass(e4[j]) : 0u;
+            acc_all += (u64)q4[0] + q4[1];
+            acc_all += (u64)q4[2] + q4[3];
+            if (band) {
+                uint32_t a4[4];
+                unsigned mk = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    a4[j] = e4[j] > t_hi ? q4[j] : 0u;
+                    if (e4[j] <= t_hi && e4[j] >= t_lo && e4[j] >= lk) mk |= 1u << j;
+                }
+                acc_above += (u64)a4[0] + a4[1];
+                acc_above += (u64)a4[2] + a4[3];
+                warp_append(mylist, wn, mk, e4, q4, (uint32_t)(slice_lo + i), lane);
+            }
+        }
+        u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
+        if (band) {
+            const u64 wall = warp_sum_u64(acc_all);
             if (lane == 0) {
+                sc->warp_tot[warp] = wkeep; sc->warp_aux[warp] = wall;
                 xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
                 if (wn > CI_WLIST) xch->list_overflow = 1;
             }
             __syncthreads();
-            cluster.sync();                                                            // (L) lists published
-            // gather every CTA's lists, in token order
-            int overflow = 0;
-            for (int q = 0; q < CS; ++q) overflow |= cluster.map_shared_rank(xch, q)->list_overflow;
-            if (tid < CS * CI_WARPS) sc->pcount[tid] = cluster.map_shared_rank(xch, tid / CI_WARPS)->wcount[tid % CI_WARPS];
-            __syncthreads();
             if (tid == 0) {
-                int run = 0;
-                for (int p = 0; p < CS * CI_WARPS; ++p) { sc->poff[p] = (unsigned short)run; run += sc->pcount[p]; }
-                sc->poff[CS * CI_WARPS] = (unsigned short)min(run, 65535);
+                u64 ta = 0, tb = 0;
+                for (int w = 0; w < CI_WARPS; ++w) { ta += sc->warp_aux[w]; tb += sc->warp_tot[w]; }
+                xch->s_all = ta; xch->s_above = tb;
             }
             __syncthreads();
-            const int n = sc->poff[CS * CI_WARPS];
-            if (overflow || n > CI_GLIST || n == 0) path = PATH_FALLBACK;
-            else {
-                for (int e = tid; e < n; e += CI_THREADS) {
-                    int lo = 0, hi = CS * CI_WARPS - 1;                 // last p with poff[p] <= e
-                    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sc->poff[mid] <= e) lo = mid; else hi = mid - 1; }
-                    const ListEntry* src = cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]);
-                    ListEntry en = *src;
-                    en.q = mass(en.l);
-                    glist[e] = en;
-                }
-                __syncthreads();
-                // k-th largest of the list = k-th largest of the row
-                float lk_val;
-                bool ok = list_select(glist, n, [&](int i) { return (u64)(glist[i].l >= lcut ? 1 : 0); }, (u64)kk, bins, cand, sc, lk_val);
-                float cut2 = lcut;
-                if (ok) {
-                    cut2 = fmaxf(lcut, lower_logit_for(scale_logit(lk_val, tc), tc, lk_val));
-                    if (cut2 < tl) ok = false;                           // a tie partner could lie outside the list
-                }
-                if (ok && need_topp) {
-                    u64 part = 0;
-                    for (int i = tid; i < n; i += CI_THREADS) if (glist[i].l >= cut2) part += glist[i].q;
-                    const u64 s1 = block_sum_u64(part, sc);
-                    double te = ceil((double)topp * (double)s1);
-                    u64 target = te <= 1.0 ? 1ull : (u64)te;
-                    if (target > s1) target = s1;
-                    float lp_val;
-                    ok = s1 > 0 && list_select(glist, n, [&](int i) { return (u64)(glist[i].l >= cut2 ? glist[i].q : 0u); }, target, bins, cand, sc, lp_val);
-                    if (ok) {
-                        cut2 = fmaxf(cut2, lower_logit_for(scale_logit(lp_val, tc), tc, lp_val));
-                        if (cut2 < tl) ok = false;
-                    }
-                }
-                if (!ok) path = PATH_FALLBACK;
-                else {
-                    lcut = cut2;
-                    u64 part = 0;
-                    for (int i = tid; i < n; i += CI_THREADS) if (glist[i].l >= lcut) part += glist[i].q;
-                    total_mass = block_sum_u64(part, sc);
-                    float u = 1.0f;
-                    if (a.u != nullptr) u = a.u[row];
-                    else if (a.pos != nullptr && a.p.seed != nullptr) {
-                        const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
-                                                       : (long long)reinterpret_cast<const int*>(a.pos)[b];
-                        u = u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
-                    }
-                    double tu = ceil((double)u * (double)total_mass);
-                    u64 target = tu <= 1.0 ? 1ull : (u64)tu;
-                    if (target > total_mass) target = total_mass;
-                    int at; u64 before;
-                    block_find([&](int i) { return (u64)(glist[i].l >= lcut ? glist[i].q : 0u); }, n, target, sc, at, before);
-                    token = total_mass > 0 ? (long long)glist[at].idx : (long long)aidx;
-                    if (total_mass == 0) status |= COLINFER_ROW_DEGENERATE;
-                    done = true;
-                }
-            }
-        }
-
-        // ------------------------------------------------------------------------------------ fallback: exact radix select over the 32-bit keys
-        if (path == PATH_FALLBACK) {
-            // (a CTA reaches this point only after every peer finished reading its reduced segment: the reads happen
-            // before the peers' next cluster barrier, and the first write below follows this CTA's next barrier (A))
-            const RadixCtx rc = {rowbuf, n_pad, fb_hist, fb_seg, xch, sc, rank, CS};
-            float lpiv;
-            if (kk > 0 && kk < V && radix_select(cluster, rc, mass, lcut, false, (u64)kk, topp, lpiv))
-                lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
-            if (need_topp && radix_select(cluster, rc, mass, lcut, true, 0, topp, lpiv))
-                lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
-            path = PATH_PURE;
-            t_hi = CI_NEG_INF; t_lo = __int_as_float(0x7f800000);
-        }
-
-        // ------------------------------------------------------------------------------------ mass pass and inverse CDF over the row
-        if (!done) {
-            const bool band = path == PATH_BAND;
-            const float lk = fmaxf(lcut, -CI_FLT_MAX);
-            u64 acc_all = 0, acc_above = 0;
-            int wn = 0;
-            for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-                const int i = i0 + lane * 4;
-                const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-                const float e4[4] = {v.x, v.y, v.z, v.w};
-                uint32_t q4[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) q4[j] = e4[j] >= lk ? mass(e4[j]) : 0u;
-                acc_all += (u64)q4[0] + q4[1];
-                acc_all += (u64)q4[2] + q4[3];
-                if (band) {
-                    uint32_t a4[4];
-                    unsigned mk = 0;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        a4[j] = e4[j] > t_hi ? q4[j] : 0u;
-                        if (e4[j] <= t_hi && e4[j] >= t_lo && e4[j] >= lk) mk |= 1u << j;
-                    }
-                    acc_above += (u64)a4[0] + a4[1];
-                    acc_above += (u64)a4[2] + a4[3];
-                    const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
-                    if (any) {
-                        const int c = __popc(mk);
-                        int pre = c;
-#pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += t; }
-                        const int tot = __shfl_sync(0xffffffffu, pre, 31);
-                        int at = wn + pre - c;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (mk & (1u << j)) {
-                                if (at < CI_WLIST) { mylist[at].idx = (uint32_t)(slice_lo + i + j); mylist[at].l = e4[j]; mylist[at].q = q4[j]; }
-                                ++at;
-                            }
-                        }
-                        wn += tot;
-                    }
-                }
-            }
-            u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
-            const u64 wall = warp_sum_u64(acc_all);
-            if (band) {
-                if (lane == 0) {
-                    sc->warp_tot[warp] = wkeep; sc->warp_aux[warp] = wall;
-                    xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
-                    if (wn > CI_WLIST) xch->list_overflow = 1;
-                }
-                __syncthreads();
-                if (tid == 0) {
-                    u64 ta = 0, tb = 0;
-                    for (int w = 0; w < CI_WARPS; ++w) { ta += sc->warp_aux[w]; tb += sc->warp_tot[w]; }
-                    xch->s_all = ta; xch->s_above = tb;
-                }
-                __syncthreads();
-                cluster.sync();                                                        // (L) band lists and sums published
-                int overflow = 0;
-                u64 s1 = 0, s_above = 0;
-                for (int q = 0; q < CS; ++q) {
-                    const Xch* px = cluster.map_shared_rank(xch, q);
-                    overflow |= px->list_overflow; s1 += px->s_all; s_above += px->s_above;
-                }
-                if (tid < CS * CI_WARPS) sc->pcount[tid] = cluster.map_shared_rank(xch, tid / CI_WARPS)->wcount[tid % CI_WARPS];
-                __syncthreads();
-                if (tid == 0) {
-                    int run = 0;
-                    for (int p = 0; p < CS * CI_WARPS; ++p) { sc->poff[p] = (unsigned short)run; run += sc->pcount[p]; }
-                    sc->poff[CS * CI_WARPS] = (unsigned short)min(run, 65535);
-                }
-                __syncthreads();
-                const int n = sc->poff[CS * CI_WARPS];
-                bool ok = !overflow && n <= CI_GLIST && s1 > 0;
-                float cut2 = lcut;
-                if (ok) {
-                    for (int e = tid; e < n; e += CI_THREADS) {
-                        int lo = 0, hi = CS * CI_WARPS - 1;
-                        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sc->poff[mid] <= e) lo = mid; else hi = mid - 1; }
-                        glist[e] = *(cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]));
-                    }
-                    __syncthreads();
-                    u64 part = 0;
-                    for (int i = tid; i < n; i += CI_THREADS) part += glist[i].q;
-                    const u64 s_band = block_sum_u64(part, sc);
-                    double te = ceil((double)topp * (double)s1);
-                    u64 target = te <= 1.0 ? 1ull : (u64)te;
-                    if (target > s1) target = s1;
-                    ok = s_above < target && target <= s_above + s_band;       // the pivot lies inside the band
-                    if (ok) {
-                        float lp_val;
-                        ok = list_select(glist, n, [&](int i) { return (u64)glist[i].q; }, target - s_above, bins, cand, sc, lp_val);
-                        if (ok) {
-                            cut2 = fmaxf(lcut, lower_logit_for(scale_logit(lp_val, tc), tc, lp_val));
-                            if (cut2 < t_lo) ok = false;                       // a tie partner could lie below the band
-                        }
-                    }
-                }
-                if (ok) {
-                    lcut = cut2;
-                    // add the kept band entries of this warp's own list to its region's kept mass
-                    u64 add = 0;
-                    const int mine = min(wn, CI_WLIST);
-                    for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mylist[j].q;
-                    wkeep += warp_sum_u64(add);
-                } else {
-                    // The estimated band missed the pivot (or a list overflowed): every CTA takes the exact radix
-                    // select by mass, then recomputes its regions' kept mass.  Rare; same result, more time.
-                    const RadixCtx rc = {rowbuf, n_pad, fb_hist, fb_seg, xch, sc, rank, CS};
-                    float lpiv;
-                    if (radix_select(cluster, rc, mass, lcut, true, 0, topp, lpiv))
-                        lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
-                    // kept mass of this warp's region under the exact threshold
-                    const float lk3 = fmaxf(lcut, -CI_FLT_MAX);
-                    u64 acc = 0;
-                    for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-                        const float4 v = *reinterpret_cast<const float4*>(rowbuf + i0 + lane * 4);
-                        acc += (u64)(v.x >= lk3 ? mass(v.x) : 0u) + (v.y >= lk3 ? mass(v.y) : 0u);
-                        acc += (u64)(v.z >= lk3 ? mass(v.z) : 0u) + (v.w >= lk3 ? mass(v.w) : 0u);
-                    }
-                    wkeep = warp_sum_u64(acc);
-                }
-            }
-            __syncthreads();
-            if (lane == 0) sc->warp_tot[warp] = wkeep;
-            __syncthreads();
-            if (tid == 0) {
-                u64 t = 0;
-                for (int w = 0; w < CI_WARPS; ++w) t += sc->warp_tot[w];
-                xch->cta_mass = t;
-            }
-            __syncthreads();
-            CI_PROF(6);
-            cluster.sync();                                                            // (C) slice masses published
-            CI_PROF(7);
-            u64 my_off = 0;
+            CI_PROF(11);
+            cluster.sync();                                                            // (L) band lists and sums published
+            u64 s1 = 0, s_above = 0;
             for (int q = 0; q < CS; ++q) {
-                const u64 cm = cluster.map_shared_rank(xch, q)->cta_mass;
-                if (q < rank) my_off += cm;
-                total_mass += cm;
+                const Xch* px = cluster.map_shared_rank(xch, q);
+                s1 += px->s_all; s_above += px->s_above;
             }
-            float u = 1.0f;
-            if (a.u != nullptr) u = a.u[row];
-            else if (a.pos != nullptr && a.p.seed != nullptr) {
-                const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
-                                               : (long long)reinterpret_cast<const int*>(a.pos)[b];
-                u = u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
-            }
-            u64 target;
-            {
-                double t = ceil((double)u * (double)total_mass);
-                target = t <= 1.0 ? 1ull : (u64)t;
-                if (target > total_mass) target = total_mass;
-            }
-            const u64 my_mass = xch->cta_mass;
-            token = -1;
-            if (total_mass > 0 && my_off < target && target <= my_off + my_mass) {
-                // the crossing lies in this CTA: find the warp region, then the element
-                u64 woff = my_off;
-                for (int w = 0; w < warp; ++w) woff += sc->warp_tot[w];
-                if (woff < target && target <= woff + wkeep) {
-                    const float lkf = fmaxf(lcut, -CI_FLT_MAX);
-                    u64 run = woff;
-                    for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-                        const int i = i0 + lane * 4;
-                        const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-                        u64 q4[4];
-                        q4[0] = v.x >= lkf ? mass(v.x) : 0u; q4[1] = v.y >= lkf ? mass(v.y) : 0u;
-                        q4[2] = v.z >= lkf ? mass(v.z) : 0u; q4[3] = v.w >= lkf ? mass(v.w) : 0u;
-                        const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
-                        const u64 incl = warp_incl_scan_u64(s4, lane);
-                        const u64 grp = __shfl_sync(0xffffffffu, incl, 31);
-                        if (run + grp >= target) {
-                            const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
-                            const int first = __ffs(hit) - 1;
-                            if (lane == first) {
-                                u64 c = run + incl - s4;
-                                int j = 0;
-                                for (; j < 3; ++j) { c += q4[j]; if (c >= target) break; }
-                                if (a.out) a.out[row] = (long long)(slice_lo + i + j);
-                            }
-                            break;
-                        }
-                        run += grp;
+            const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, nullptr);
+            bool ok = n >= 0 && s1 > 0;
+            float cut2 = lcut;
+            if (ok) {
+                u64 part = 0;
+                for (int i = tid; i < n; i += CI_THREADS) part += glist[i].q;
+                const u64 s_band = block_sum_u64(part, sc);
+                const u64 target = ceil_target(topp, s1);
+                ok = s_above < target && target <= s_above + s_band;           // the pivot lies inside the band
+                if (ok) {
+                    float lp_val;
+                    ok = list_select(glist, n, [&](int i) { return (u64)glist[i].q; }, target - s_above, bins, cand, sc, lp_val);
+                    if (ok) {
+                        cut2 = fmaxf(lcut, lower_logit_for(scale_logit(lp_val, tc), tc, lp_val));
+                        if (cut2 < t_lo) ok = false;                           // a tie partner could lie below the band
                     }
                 }
             }
-            if (total_mass == 0) { status |= COLINFER_ROW_DEGENERATE; token = aidx; }
+            if (ok) {
+                lcut = cut2;
+                // add the kept band entries of this warp's own list to its region's kept mass
+                u64 add = 0;
+                const int mine = min(wn, CI_WLIST);
+                for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mylist[j].q;
+                wkeep += warp_sum_u64(add);
+            } else {
+                // The estimated band missed the pivot (or a list overflowed): every CTA takes the exact radix select
+                // by mass, then recomputes its regions' kept mass.  Rare; same result, more time.
+                const RadixCtx rc = {rowbuf, n_pad, fb_hist, fb_seg, xch, sc, rank, CS};
+                float lpiv;
+                if (radix_select(cluster, rc, mass, lcut, true, 0, topp, lpiv))
+                    lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+                const float lk3 = fmaxf(lcut, -CI_FLT_MAX);
+                u64 acc = 0;
+                for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(rowbuf + i0 + lane * 4);
+                    acc += (u64)(v.x >= lk3 ? mass(v.x) : 0u) + (v.y >= lk3 ? mass(v.y) : 0u);
+                    acc += (u64)(v.z >= lk3 ? mass(v.z) : 0u) + (v.w >= lk3 ? mass(v.w) : 0u);
+                }
+                wkeep = warp_sum_u64(acc);
+            }
         }
+        __syncthreads();
+        if (lane == 0) sc->warp_tot[warp] = wkeep;
+        __syncthreads();
+        u64 my_mass = 0;
+        for (int w = 0; w < CI_WARPS; ++w) my_mass += sc->warp_tot[w];
+        if (tid < CS) cluster.map_shared_rank(sc, tid)->mass_in[rank] = my_mass;
+        CI_PROF(6);
+        cluster.sync();                                                                // (C) slice masses exchanged
+        CI_PROF(7);
+        u64 my_off = 0;
+        for (int q = 0; q < CS; ++q) {
+            const u64 cm = sc->mass_in[q];
+            if (q < rank) my_off += cm;
+            total_mass += cm;
+        }
+        const u64 target = ceil_target(u, total_mass);
+        token = -1;
+        if (total_mass > 0 && my_off < target && target <= my_off + my_mass) {
+            // the crossing lies in this CTA: find the warp region, then the element
+            u64 woff = my_off;
+            for (int w = 0; w < warp; ++w) woff += sc->warp_tot[w];
+            if (woff < target && target <= woff + wkeep) {
+                const float lkf = fmaxf(lcut, -CI_FLT_MAX);
+                u64 run = woff;
+                for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                    const int i = i0 + lane * 4;
+                    const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+                    u64 q4[4];
+                    q4[0] = v.x >= lkf ? mass(v.x) : 0u; q4[1] = v.y >= lkf ? mass(v.y) : 0u;
+                    q4[2] = v.z >= lkf ? mass(v.z) : 0u; q4[3] = v.w >= lkf ? mass(v.w) : 0u;
+                    const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
+                    const u64 incl = warp_incl_scan_u64(s4, lane);
+                    const u64 grp = __shfl_sync(0xffffffffu, incl, 31);
+                    if (run + grp >= target) {
+                        const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
+                        const int first = __ffs(hit) - 1;
+                        if (lane == first) {
+                            u64 c = run + incl - s4;
+                            int j = 0;
+                            for (; j < 3; ++j) { c += q4[j]; if (c >= target) break; }
+                            if (a.out) a.out[row] = (long long)(slice_lo + i + j);
+                        }
+                        break;
+                    }
+                    run += grp;
+                }
+            }
+        }
+        if (total_mass == 0) { status |= COLINFER_ROW_DEGENERATE; token = aidx; }
     }
 
     if (rank == 0 && tid == 0) {
-        if (token >= 0 && a.out) a.out[row] = token;           // greedy, list-path, degenerate or failed rows
-        int hs = 0;
-        for (int q = 0; q < CS; ++q) hs |= cluster.map_shared_rank(sc, q)->hist_slow;
-        if (hs) status |= COLINFER_ROW_HIST_SLOW;
+        if (token >= 0 && a.out) a.out[row] = token;           // list-path or degenerate rows (else the crossing lane stored it)
         if (a.status) a.status[row] = status;
         if (a.stats) {
             colinfer_row_stats st;
@@ -928,7 +1020,8 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         }
     }
     CI_PROF(8);
-    cluster.sync();                                            // no CTA leaves while a peer may still read its shared memory
+    // After the mass exchange nobody reads a peer's memory; after a list path peers may still be gathering: wait for them.
+    if (done) cluster.sync();
     CI_PROF(9);
     if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
         unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
