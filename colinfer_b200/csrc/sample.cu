@@ -54,7 +54,8 @@ struct SampleArgs {
     int B, R, V; int slice_elems; int flags;
     long long* prof; int prof_slots;   // optional per-CTA phase timestamps (profiling hook)
 };
-#define CI_PROF(slot) do { if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) a.prof[(size_t)blockIdx.x * 16 + (slot)] = clock64(); } while (0)
+// Profiling hook: thread 0 adds the cycles since its previous marker to the slot's total (summed over the CTA's rows).
+#define CI_PROF(slot) do { if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) { const long long t_ = clock64(); a.prof[(size_t)blockIdx.x * 16 + (slot)] += t_ - prof_last; prof_last = t_; } } while (0)
 
 struct ListEntry { uint32_t idx; float l; uint32_t q; };
 
@@ -72,7 +73,7 @@ struct Xch {
 };
 
 struct Scratch {
-    Hello hello[8];
+    Hello hello[2][8];             // written by the peers, one set per row parity
     u64 warp_tot[CI_WARPS];
     u64 warp_aux[CI_WARPS];
     float warp_f[CI_WARPS]; int warp_i[CI_WARPS];
@@ -82,8 +83,8 @@ struct Scratch {
     int ncand; float sel_value; int sel_ok;
     int fail;
     int hist_slow;
-    float bcast_f; int bcast_i;
-    u64 mass_in[8];                // kept mass of every CTA's slice, written by the peers
+    int bcast_i[2];                // written by the cluster's first CTA, per row parity
+    u64 mass_in[2][8];             // kept mass of every CTA's slice, written by the peers, per row parity
 };
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
@@ -387,8 +388,6 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     cluster.barrier_arrive();
     const int CS = (int)cluster.num_blocks();
     const int rank = (int)cluster.block_rank();
-    const int row = blockIdx.x / CS;
-    const int b = row / a.R, r = row % a.R;
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int V = a.V;
 
@@ -418,14 +417,27 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     uint32_t* pen_prefix = pen_bits + nw;
     uint32_t* pen_cnt = pen_prefix + nw;
 
+    // The mbarriers of the bulk copies are set up once; each row completes one phase of each.
+    if (tid == 0 && a.use_bulk) {
+        for (int c = 0; c < nchunks; ++c) mbar_init(&mbar[c], 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    const int n_clusters = (int)gridDim.x / CS;
+    const long long n_rows = (long long)a.B * a.R;
+    long long prof_last = clock64();
+    const long long prof_t0 = prof_last;
+
+    // One row of the batch.  `it` counts this cluster's rows: its parity selects the mbarrier phase and the exchange slots.
+    auto process_row = [&](const int row, const int it) {
+    const int par = it & 1;
+    const int b = row / a.R, r = row % a.R;
     // ---------------------------------------------------------------------------------------- start the HBM read
-    // One thread sets up the mbarriers and issues every bulk copy of the slice at once, before anything else.
+    // One thread issues every bulk copy of the slice at once, before anything else.
     if (tid == 0) {
         sc->fail = 0; sc->hist_slow = 0; xch->list_overflow = 0;
         if (a.use_bulk) {
-            for (int c = 0; c < nchunks; ++c) mbar_init(&mbar[c], 1);
-            fence_mbar_init();
-            fence_proxy_async();
+            fence_proxy_async();                               // the previous row's reads of the buffer precede these writes
             const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)row * V + slice_lo;
             for (int c = 0; c < nchunks; ++c) {
                 const int len = min(CI_CHUNK, slice_len - c * CI_CHUNK);
@@ -433,11 +445,6 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
                 bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
             }
         }
-    }
-    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
-        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        a.prof[(size_t)blockIdx.x * 16 + 15] = (long long)gt; a.prof[(size_t)blockIdx.x * 16 + 14] = smid;
     }
     CI_PROF(0);
 
@@ -509,7 +516,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         const int c_len = min(CI_CHUNK, n_pad - c_lo);          // multiple of 128
         if (c < nchunks) {
             if (a.use_bulk) {
-                if (!mbar_wait_bounded(&mbar[c], 0, CI_WAIT_CYCLES)) sc->fail = 1;
+                if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
             } else {
                 const int valid = min(CI_CHUNK, slice_len - c_lo);
                 const size_t g0 = (size_t)row * V + slice_lo + c_lo;
@@ -628,6 +635,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             block_find([&](int i) { return (u64)hist1[i]; }, CI_NB1, (u64)kk, sc, bk, before);
             tl_fast = bk >= CI_NB1 - 1 ? -CI_FLT_MAX : lmax - ((float)(bk + 1) + 0.01f) / CI_FASTK_SCALE - fabsf(lmax) * 1e-6f;
         } else tl_fast = -CI_FLT_MAX;                           // fewer than k threads saw a finite logit: take them all
+        CI_PROF(10);
         int wn = 0;
         for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
             const int i = i0 + lane * 4;
@@ -636,6 +644,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             const unsigned mk = (v.x >= tl_fast ? 1u : 0u) | (v.y >= tl_fast ? 2u : 0u) | (v.z >= tl_fast ? 4u : 0u) | (v.w >= tl_fast ? 8u : 0u);
             warp_append(mylist, wn, mk, e4, nullptr, (uint32_t)(slice_lo + i), lane);
         }
+        CI_PROF(11);
         if (lane == 0) {
             xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
             sc->warp_i[warp] = wn;
@@ -648,19 +657,19 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 
     // ---------------------------------------------------------------------------------------- first exchange
     CI_PROF(3);
-    cluster.barrier_wait();                                     // every CTA of the cluster runs: peers' memory may be written
+    if (it == 0) cluster.barrier_wait();                        // every CTA of the cluster runs: peers' memory may be written
     if (tid < CS) {
         Hello h;
         h.lmax = lmax; h.lidx = lidx;
         h.flags = (sc->fail ? 1 : 0) | (sc->hist_slow ? 4 : 0);
         h.pad = my_count;
-        cluster.map_shared_rank(sc, tid)->hello[rank] = h;
+        cluster.map_shared_rank(sc, tid)->hello[par][rank] = h;
     }
     cluster.sync();                                                                    // (1) slice maxima (and list sizes) exchanged
     CI_PROF(4);
     float L = CI_NEG_INF; int aidx = 0x7fffffff; int hflags = 0; int fast_total = 0; bool fast_overflow = false;
     for (int q = 0; q < CS; ++q) {
-        const Hello h = sc->hello[q];
+        const Hello h = sc->hello[par][q];
         if (h.lmax > L || (h.lmax == L && h.lidx < aidx)) { L = h.lmax; aidx = h.lidx; }
         hflags |= h.flags;
         fast_total += h.pad;
@@ -707,15 +716,19 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (!fast_overflow && fast_total <= CI_GLIST && fast_total > 0) {
             if (rank == 0) {
                 const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, &mass);
+                CI_PROF(5);
                 // the list holds every logit of the row's top k; entries below the min-p threshold carry no weight
                 float tl_all = CI_NEG_INF;                      // no lower bound is needed: the pivot is inside the list
                 if (n > 0 && finish_on_list(glist, n, tl_all, lcut, tc, kk, need_topp, topp, u, bins, cand, sc, token, lcut, total_mass)) ok = 1;
+                CI_PROF(6);
             }
         }
         // the first CTA tells the others whether the row is done (they only wait; their lists had to stay readable)
-        if (rank == 0 && tid < CS) cluster.map_shared_rank(sc, tid)->bcast_i = ok;
+        if (rank == 0 && tid < CS) cluster.map_shared_rank(sc, tid)->bcast_i[par] = ok;
+        CI_PROF(7);
         cluster.sync();                                                                // (F) row finished, or not
-        ok = sc->bcast_i;
+        CI_PROF(8);
+        ok = sc->bcast_i[par];
         if (ok) {
             if (rank == 0 && tid == 0) {
                 if (a.out) a.out[row] = token;
@@ -776,7 +789,6 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (tid == 0) { xch->seg_cnt = totc; xch->seg_est = tote; }
         __syncthreads();
         cluster.sync();                                                                // (B) reduced segments published
-        CI_PROF(12);
         u64 segc[8], sege[8], survivors = 0, est_total = 0;
         for (int q = 0; q < CS; ++q) {
             const Xch* px = cluster.map_shared_rank(xch, q);
@@ -964,13 +976,13 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         __syncthreads();
         u64 my_mass = 0;
         for (int w = 0; w < CI_WARPS; ++w) my_mass += sc->warp_tot[w];
-        if (tid < CS) cluster.map_shared_rank(sc, tid)->mass_in[rank] = my_mass;
+        if (tid < CS) cluster.map_shared_rank(sc, tid)->mass_in[par][rank] = my_mass;
         CI_PROF(6);
         cluster.sync();                                                                // (C) slice masses exchanged
         CI_PROF(7);
         u64 my_off = 0;
         for (int q = 0; q < CS; ++q) {
-            const u64 cm = sc->mass_in[q];
+            const u64 cm = sc->mass_in[par][q];
             if (q < rank) my_off += cm;
             total_mass += cm;
         }
@@ -1023,9 +1035,22 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     // After the mass exchange nobody reads a peer's memory; after a list path peers may still be gathering: wait for them.
     if (done) cluster.sync();
     CI_PROF(9);
+    };  // process_row
+
+    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
+        unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.prof[(size_t)blockIdx.x * 16 + 15] = (long long)gt; a.prof[(size_t)blockIdx.x * 16 + 14] = smid;
+    }
+    int it = 0;
+    for (long long row = blockIdx.x / CS; row < n_rows; row += n_clusters, ++it) {
+        if (it) __syncthreads();                               // every thread is done with the previous row's buffers
+        process_row((int)row, it);
+    }
     if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
         unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
         a.prof[(size_t)blockIdx.x * 16 + 13] = (long long)gt;
+        a.prof[(size_t)blockIdx.x * 16 + 12] = clock64() - prof_t0;
     }
 }
 
@@ -1068,9 +1093,9 @@ extern "C" int colinfer_set_profile_buffer(void* dev, int ctas) {
     return 0;
 }
 
-static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, const colinfer_geometry& g, long long rows, cudaStream_t st) {
+static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, const colinfer_geometry& g, long long clusters, cudaStream_t st) {
     cfg = cudaLaunchConfig_t{};
-    cfg.gridDim = dim3((unsigned)(rows * g.cluster), 1, 1);
+    cfg.gridDim = dim3((unsigned)(clusters * g.cluster), 1, 1);
     cfg.blockDim = dim3(CI_THREADS, 1, 1);
     cfg.dynamicSmemBytes = (size_t)g.smem_bytes;
     cfg.stream = st;
@@ -1082,15 +1107,29 @@ static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, cons
     cfg.numAttrs = 1;
 }
 
-extern "C" int colinfer_max_active_clusters(int V, int dtype) {
-    colinfer_geometry g;
-    if (pick_geometry(V, dtype, nullptr, &g)) return -1;
+// Clusters of this geometry that the current device holds at once (cached per device and geometry): the kernel is
+// persistent, each cluster walks over rows, so the grid never exceeds this.
+static int active_clusters(const colinfer_geometry& g) {
+    struct Entry { int dev, smem, cs, n; };
+    static Entry cache[16];
+    static int used = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    for (int i = 0; i < used; ++i)
+        if (cache[i].dev == dev && cache[i].smem == g.smem_bytes && cache[i].cs == g.cluster) return cache[i].n;
     if (cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes) != cudaSuccess) return -2;
     cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
     fill_launch(cfg, attr, g, 1024, nullptr);
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, k_sample, &cfg) != cudaSuccess) return -3;
+    if (cudaOccupancyMaxActiveClusters(&n, k_sample, &cfg) != cudaSuccess || n <= 0) return -3;
+    if (used < 16) cache[used++] = Entry{dev, g.smem_bytes, g.cluster, n};
     return n;
+}
+
+extern "C" int colinfer_max_active_clusters(int V, int dtype) {
+    colinfer_geometry g;
+    if (pick_geometry(V, dtype, nullptr, &g)) return -1;
+    return active_clusters(g);
 }
 
 extern "C" int colinfer_set_cluster_override(int cluster) {
@@ -1112,7 +1151,10 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     if (mask && (W < (V + 31) / 32 || mask_rows < R)) return (int)cudaErrorInvalidValue;
     colinfer_geometry g;
     if (pick_geometry(V, dtype, logits, &g)) return (int)cudaErrorInvalidValue;
-    if ((long long)B * R * g.cluster > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    if ((long long)B * R > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    const int resident = active_clusters(g);
+    if (resident <= 0) return (int)cudaErrorInvalidConfiguration;
+    const long long clusters = (long long)B * R < resident ? (long long)B * R : resident;
 
     SampleArgs a;
     a.logits = logits; a.dtype = dtype; a.use_bulk = g.bulk_copy;
@@ -1126,7 +1168,7 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     cudaError_t e = cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
-    fill_launch(cfg, attr, g, (long long)B * R, (cudaStream_t)stream);
+    fill_launch(cfg, attr, g, clusters, (cudaStream_t)stream);
     e = cudaLaunchKernelEx(&cfg, k_sample, a);
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();

@@ -122,8 +122,9 @@ int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geom
 /* Test hook: force the cluster size (1, 2, 4 or 8; 0 = automatic) of later colinfer_sample calls of this process. */
 int colinfer_set_cluster_override(int cluster);
 
-/* Profiling hook: when dev is not NULL, the first `ctas` CTAs of later colinfer_sample launches write 16 int64 each
- * (clock64 at phase boundaries, %smid, %globaltimer at entry and exit) to dev[ctas * 16].  NULL switches it off. */
+/* Profiling hook: when dev is not NULL, the first `ctas` CTAs of later colinfer_sample launches add, into 16 int64
+ * each (dev[ctas * 16], zeroed by the caller), the clock cycles spent in each phase summed over the CTA's rows
+ * (slots 0-11), the CTA's total cycles (12), %globaltimer at exit (13) and entry (15), and %smid (14).  NULL = off. */
 int colinfer_set_profile_buffer(void* dev, int ctas);
 
 /* How many clusters of the sampler's geometry for this vocabulary the current device holds at once (occupancy query). */
