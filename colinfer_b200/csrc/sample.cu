@@ -33,9 +33,14 @@
 #define CI_MAX_CHUNKS 16
 #define CI_NB1 4096              // fine buckets over the distance from the row maximum
 #define CI_RANGE 25.0f           // the buckets cover distances up to CI_RANGE * temperature
-#define CI_FASTK 128             // largest top_k handled by the per-slice candidate lists
-#define CI_FASTK_SCALE 128.0f    // buckets per unit logit of the thread-maxima histogram (covers 32 units)
-#define CI_WLIST 64              // list entries per warp
+#define CI_FASTK 100             // largest top_k handled by the per-slice candidate lists
+#define CI_FAST_BINS 512         // bins of the thread-maxima histogram (one per thread)
+#define CI_FAST_SCALE 32.0f      // its bins per unit logit (covers 16 units below the slice maximum)
+#define CI_PCAP 128              // candidates one CTA may push to the CTA that finishes the row
+#define CI_FIN_SCALE 64.0f       // bins per unit logit of the exact selection on the pushed candidates (8 units)
+#define CI_FIN_CAND 64           // candidates of one bin examined pairwise
+#define CI_RETRY 8               // rows a CTA may set aside for the generic path before the fast path is switched off
+#define CI_WLIST 24              // list entries per warp
 #define CI_GLIST 1365            // gathered list entries (16 KB)
 #define CI_SEL_BINS 512          // coarse bins of the exact selection on a gathered list
 #define CI_FB_NB 256             // radix buckets per level of the fallback select (8 bits)
@@ -57,10 +62,14 @@ struct SampleArgs {
 // Profiling hook: thread 0 adds the cycles since its previous marker to the slot's total (summed over the CTA's rows).
 #define CI_PROF(slot) do { if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) { const long long t_ = clock64(); a.prof[(size_t)blockIdx.x * 16 + (slot)] += t_ - prof_last; prof_last = t_; } } while (0)
 
-struct ListEntry { uint32_t idx; float l; uint32_t q; };
+struct ListEntry { uint32_t idx; float l; uint32_t q; };   // gathered list: token, logit, mass
+struct Cand { uint32_t idx; float l; };                      // a warp's list / pushed candidates: token, logit
+
+// A row whose candidates have been pushed to this CTA and that waits for its exact finish.
+struct Pending { int row; float L; int aidx; int status; int count[8]; };
 
 // What every CTA writes into each peer's shared memory before the first cluster barrier.
-struct Hello { float lmax; int lidx; int flags; int pad; };   // flags: 1 = a bounded wait gave up, 2 = list overflow, 4 = slow history path
+struct Hello { float lmax; int lidx; int flags; int pad; };   // flags: 1 = a bounded wait gave up, 4 = slow history path, 8 = stop using the fast path; pad: candidates pushed
 
 // Values one CTA publishes in its own shared memory for its peers to read after a later barrier.
 struct Xch {
@@ -83,6 +92,12 @@ struct Scratch {
     int ncand; float sel_value; int sel_ok;
     int fail;
     int hist_slow;
+    u64 wsum[CI_WARPS], woff[CI_WARPS], wtotal;   // block scan
+    int found_tid; u64 found_excl;
+    float cand_l[CI_FIN_CAND]; u64 cand_w[CI_FIN_CAND]; float res_f;
+    Pending pend;
+    int n_retry_common, n_retry_mine, want_fast_off;
+    int retry_common[CI_RETRY], retry_mine[CI_RETRY], retry_all[CI_RETRY * 9];
     int bcast_i[2];                // written by the cluster's first CTA, per row parity
     u64 mass_in[2][8];             // kept mass of every CTA's slice, written by the peers, per row parity
 };
@@ -281,10 +296,10 @@ __device__ bool radix_select(cg::cluster_group& cluster, const RadixCtx& c, cons
 }
 
 // Gathers the per-warp lists of every CTA of the cluster into glist, in token order (CTA rank, warp, position).
-// Returns the number of entries, or -1 when a list overflowed or the total exceeds the capacity.  with_mass: compute
-// the entries' masses here (lists collected before the row maximum was known carry none).  All threads call.
-__device__ int gather_lists(cg::cluster_group& cluster, int CS, Xch* xch, ListEntry* ownlist, ListEntry* glist, Scratch* sc,
-                            const MassFn* mass) {
+// Returns the number of entries, or -1 when a list overflowed or the total exceeds the capacity.  The entries' masses
+// are computed here (the warps' lists hold token and logit only).  All threads call.
+__device__ int gather_lists(cg::cluster_group& cluster, int CS, Xch* xch, Cand* ownlist, ListEntry* glist, Scratch* sc,
+                            const MassFn& mass) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int np = CS * CI_WARPS;                                          // (CTA, warp) pairs, at most 128
     int overflow = 0;
@@ -309,8 +324,9 @@ __device__ int gather_lists(cg::cluster_group& cluster, int CS, Xch* xch, ListEn
     for (int e = tid; e < n; e += CI_THREADS) {
         int lo = 0, hi = np - 1;                                           // last pair p with poff[p] <= e
         while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sc->poff[mid] <= e) lo = mid; else hi = mid - 1; }
-        ListEntry en = *(cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]));
-        if (mass) en.q = (*mass)(en.l);
+        const Cand c = *(cluster.map_shared_rank(ownlist, lo / CI_WARPS) + (lo % CI_WARPS) * CI_WLIST + (e - sc->poff[lo]));
+        ListEntry en;
+        en.idx = c.idx; en.l = c.l; en.q = mass(c.l);
         glist[e] = en;
     }
     __syncthreads();
@@ -362,8 +378,7 @@ __device__ bool finish_on_list(const ListEntry* glist, int n, float tl, float lc
 
 // Appends the components of one float4 group selected by the 4-bit mask mk to the warp's list, in token order.
 // wn is the warp's running count (uniform over the warp); entries beyond CI_WLIST are dropped and counted.
-__device__ __forceinline__ void warp_append(ListEntry* mylist, int& wn, unsigned mk, const float* e4, const uint32_t* q4,
-                                            uint32_t idx0, int lane) {
+__device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, const float* e4, uint32_t idx0, int lane) {
     const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
     if (!any) return;
     const int c = __popc(mk);
@@ -375,11 +390,167 @@ __device__ __forceinline__ void warp_append(ListEntry* mylist, int& wn, unsigned
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         if (mk & (1u << j)) {
-            if (at < CI_WLIST) { mylist[at].idx = idx0 + j; mylist[at].l = e4[j]; mylist[at].q = q4 ? q4[j] : 0u; }
+            if (at < CI_WLIST) { mylist[at].idx = idx0 + j; mylist[at].l = e4[j]; }
             ++at;
         }
     }
     wn += tot;
+}
+
+// ------------------------------------------------------------------------------------------------ lean block primitives
+// Exclusive prefix of one value per thread over the CTA (thread order), and the total.  Two __syncthreads.
+__device__ __forceinline__ u64 block_excl_scan(u64 v, Scratch* sc, u64& total) {
+    const int lane = lane_id(), warp = warp_id();
+    const u64 incl = warp_incl_scan_u64(v, lane);
+    if (lane == 31) sc->wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const u64 w = lane < CI_WARPS ? sc->wsum[lane] : 0ull;
+        const u64 wi = warp_incl_scan_u64(w, lane);
+        if (lane < CI_WARPS) sc->woff[lane] = wi - w;
+        if (lane == CI_WARPS - 1) sc->wtotal = wi;
+        if (lane == 0) sc->found_tid = -1;
+    }
+    __syncthreads();
+    total = sc->wtotal;
+    return sc->woff[warp] + incl - v;
+}
+// The thread whose [excl, excl + v] interval contains `target` (1 <= target <= total) announces itself.  One __syncthreads.
+__device__ __forceinline__ void block_find_thread(u64 v, u64 excl, u64 target, Scratch* sc, int& ftid, u64& fexcl) {
+    if (excl < target && target <= excl + v) { sc->found_tid = (int)threadIdx.x; sc->found_excl = excl; }
+    __syncthreads();
+    ftid = sc->found_tid;
+    fexcl = sc->found_excl;
+}
+
+// Exact weighted selection among up to two entries per thread: the value v such that W(l > v) < target <= W(l >= v),
+// W summing the weights w.  512 bins over the distance from the row maximum (one per thread), then the pivot bin's
+// entries pairwise.  Returns false when the pivot falls outside the binned range or its bin is too crowded.
+// Seven __syncthreads.  All threads call with the same target.
+__device__ bool lean_select(const float* el, const u64* w, float L, u64 target, u64* bins, Scratch* sc, float& value) {
+    const int tid = threadIdx.x;
+    bins[tid] = 0;
+    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; }
+    __syncthreads();
+    int kb[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        kb[j] = min(CI_FAST_BINS - 1, __float2int_rz((L - el[j]) * CI_FIN_SCALE));
+        if (w[j]) atomicAdd(&bins[kb[j]], w[j]);
+    }
+    __syncthreads();
+    const u64 v = bins[tid];
+    u64 total;
+    const u64 excl = block_excl_scan(v, sc, total);
+    int b_star; u64 before;
+    block_find_thread(v, excl, target, sc, b_star, before);
+    if (b_star < 0 || b_star >= CI_FAST_BINS - 1) return false;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        if (w[j] && kb[j] == b_star) {
+            const int slot = atomicAdd(&sc->ncand, 1);
+            if (slot < CI_FIN_CAND) { sc->cand_l[slot] = el[j]; sc->cand_w[slot] = w[j]; }
+        }
+    }
+    __syncthreads();
+    const int nc = sc->ncand;
+    if (nc > CI_FIN_CAND) return false;
+    if (tid < nc) {
+        const float mine = sc->cand_l[tid];
+        u64 gt = 0, eq = 0;
+        for (int i = 0; i < nc; ++i) {
+            const float o = sc->cand_l[i];
+            if (o > mine) gt += sc->cand_w[i]; else if (o == mine) eq += sc->cand_w[i];
+        }
+        if (before + gt < target && target <= before + gt + eq) { sc->res_f = mine; sc->sel_ok = 1; }
+    }
+    __syncthreads();
+    value = sc->res_f;
+    return sc->sel_ok != 0;
+}
+
+// Exact finish of a row from the candidates its CTAs pushed into this CTA's shared memory: min-p, top-k, top-p and
+// the draw, all inside this CTA (no cluster traffic).  The candidates contain the row's top k logits (and possibly
+// more), in token order: CTA by CTA, each CTA's in token order.  Writes the row's outputs and returns true, or returns
+// false when the row has to take the generic path.  All threads of the CTA call.
+__device__ bool finish_pending(const SampleArgs& a, const Pending& pd, const Cand* plist, int CS, u64* bins, Scratch* sc) {
+    const int tid = threadIdx.x;
+    const int row = pd.row, b = row / a.R, r = row % a.R;
+    const float tc = fmaxf(a.p.temperature[b], 1e-6f);
+    const int kk = a.p.top_k[b];
+    const float topp = a.p.top_p[b];
+    const float L = pd.L;
+    const float m = scale_logit(L, tc);
+    MassFn mass;
+    mass.init(tc, m);
+    const float thr = __fadd_rn(m, a.p.log_min_p[b]);
+    float cut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
+    const float u = row_uniform(a, row, b, r);
+    int pre[9];
+    pre[0] = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) pre[q + 1] = pre[q] + (q < CS ? pd.count[q] : 0);
+    const int n = pre[8];
+    if (n > 2 * CI_THREADS) return false;
+    // thread t holds entries 2t and 2t + 1 of the concatenated lists: thread order is token order
+    float el[2]; uint32_t ei[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int e = 2 * tid + j;
+        el[j] = CI_NEG_INF; ei[j] = 0;
+        if (e < n) {
+            int q = 0;
+#pragma unroll
+            for (int t = 1; t < 8; ++t) q += (pre[t] <= e) ? 1 : 0;
+            const Cand c = plist[q * CI_PCAP + (e - pre[q])];
+            el[j] = c.l; ei[j] = c.idx;
+        }
+    }
+    // ---- top-k: the k-th largest of the candidates that survive min-p
+    u64 w[2];
+    w[0] = (el[0] >= cut && el[0] > CI_NEG_INF) ? 1ull : 0ull;
+    w[1] = (el[1] >= cut && el[1] > CI_NEG_INF) ? 1ull : 0ull;
+    u64 survivors;
+    block_excl_scan(w[0] + w[1], sc, survivors);
+    if (survivors == 0) return false;
+    if ((u64)kk <= survivors) {                               // else fewer than k survive min-p: top-k removes nothing
+        float lk;
+        if (!lean_select(el, w, L, (u64)kk, bins, sc, lk)) return false;
+        cut = fmaxf(cut, lower_logit_for(scale_logit(lk, tc), tc, lk));
+    }
+    // ---- top-p over the kept candidates
+    u64 q2[2];
+    q2[0] = (el[0] >= cut && el[0] > CI_NEG_INF) ? (u64)mass(el[0]) : 0ull;
+    q2[1] = (el[1] >= cut && el[1] > CI_NEG_INF) ? (u64)mass(el[1]) : 0ull;
+    if (topp < 1.0f) {
+        u64 s1;
+        block_excl_scan(q2[0] + q2[1], sc, s1);
+        if (s1 == 0) return false;
+        float lp;
+        if (!lean_select(el, q2, L, ceil_target(topp, s1), bins, sc, lp)) return false;
+        cut = fmaxf(cut, lower_logit_for(scale_logit(lp, tc), tc, lp));
+        if (!(el[0] >= cut)) q2[0] = 0;
+        if (!(el[1] >= cut)) q2[1] = 0;
+    }
+    // ---- the draw: first candidate (token order) whose running kept mass reaches u * total
+    u64 total;
+    const u64 excl = block_excl_scan(q2[0] + q2[1], sc, total);
+    if (total == 0) return false;
+    const u64 target = ceil_target(u, total);
+    int ftid; u64 fexcl;
+    block_find_thread(q2[0] + q2[1], excl, target, sc, ftid, fexcl);
+    if (tid == ftid) {
+        const long long token = (excl + q2[0] >= target) ? (long long)ei[0] : (long long)ei[1];
+        if (a.out) a.out[row] = token;
+        if (a.status) a.status[row] = pd.status;
+        if (a.stats) {
+            colinfer_row_stats st;
+            st.lmax = L; st.lcut = cut; st.tc = tc; st.status = pd.status; st.argmax = pd.aidx; st.mass_q = total;
+            a.stats[row] = st;
+        }
+    }
+    __syncthreads();
+    return ftid >= 0;
 }
 
 extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __grid_constant__ SampleArgs a) {
@@ -407,8 +578,9 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     uint32_t* cand = reinterpret_cast<uint32_t*>(hreg + CI_NB1 * 4 + CI_SEL_BINS * 8);
     u64* fb_hist = reinterpret_cast<u64*>(hreg);                              // fallback radix, over hist1
     u64* fb_seg = fb_hist + CI_FB_NB;
-    ListEntry* ownlist = reinterpret_cast<ListEntry*>(hreg + 24 * 1024);      // [CI_WARPS][CI_WLIST]
-    u64* mbar = reinterpret_cast<u64*>(hreg + 24 * 1024 + CI_WARPS * CI_WLIST * sizeof(ListEntry));
+    Cand* ownlist = reinterpret_cast<Cand*>(hreg + 24 * 1024);                // [CI_WARPS][CI_WLIST] this CTA's lists
+    Cand* plist = ownlist + CI_WARPS * CI_WLIST;                              // [8][CI_PCAP] candidates pushed by the cluster
+    u64* mbar = reinterpret_cast<u64*>(plist + 8 * CI_PCAP);
     Xch* xch = reinterpret_cast<Xch*>(mbar + CI_MAX_CHUNKS);
     Scratch* sc = reinterpret_cast<Scratch*>(xch + 1);
     // penalty tables alias the work area (used before the first histogram)
@@ -428,24 +600,50 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     long long prof_last = clock64();
     const long long prof_t0 = prof_last;
 
+    // Starts the bulk copies of one row's slice (thread 0 only; every thread must be done reading the buffer).
+    auto issue_row = [&](const long long rw) {
+        fence_proxy_async();                                   // earlier reads of the buffer precede these writes
+        const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)rw * V + slice_lo;
+        for (int c = 0; c < nchunks; ++c) {
+            const int len = min(CI_CHUNK, slice_len - c * CI_CHUNK);
+            mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
+            bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
+        }
+    };
+    bool prefetched = false;          // the next row's copies are already in flight
+    bool fast_enabled = true;         // small top-k rows may take the deferred path (identical in every CTA)
+    int fast_seq = 0;                 // deferred rows so far: row j is finished by CTA j % CS
+    int n_set_aside = 0;              // rows set aside for the generic path by every CTA alike
+    if (tid == 0) { sc->pend.row = -1; sc->n_retry_common = 0; sc->n_retry_mine = 0; sc->want_fast_off = 0; }
+
+    // Every CTA that holds a deferred row finishes it; then the cluster meets so that candidates may be pushed again.
+    auto flush = [&]() {
+        __syncthreads();
+        if (sc->pend.row >= 0) {
+            const bool ok = finish_pending(a, sc->pend, plist, CS, reinterpret_cast<u64*>(hreg), sc);
+            if (tid == 0) {
+                if (!ok) {
+                    if (sc->n_retry_mine < CI_RETRY) sc->retry_mine[sc->n_retry_mine++] = sc->pend.row;
+                    if (sc->n_retry_mine >= CI_RETRY - 1) sc->want_fast_off = 1;
+                }
+                sc->pend.row = -1;
+            }
+        }
+        cluster.sync();
+    };
+
     // One row of the batch.  `it` counts this cluster's rows: its parity selects the mbarrier phase and the exchange slots.
-    auto process_row = [&](const int row, const int it) {
+    auto process_row = [&](const int row, const int it, const bool allow_fast, const long long next_row) {
     const int par = it & 1;
     const int b = row / a.R, r = row % a.R;
     // ---------------------------------------------------------------------------------------- start the HBM read
-    // One thread issues every bulk copy of the slice at once, before anything else.
+    // One thread issues every bulk copy of the slice at once, before anything else (unless the previous row already
+    // started this row's copies because it no longer needed the buffer).
     if (tid == 0) {
         sc->fail = 0; sc->hist_slow = 0; xch->list_overflow = 0;
-        if (a.use_bulk) {
-            fence_proxy_async();                               // the previous row's reads of the buffer precede these writes
-            const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)row * V + slice_lo;
-            for (int c = 0; c < nchunks; ++c) {
-                const int len = min(CI_CHUNK, slice_len - c * CI_CHUNK);
-                mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
-                bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
-            }
-        }
+        if (a.use_bulk && !prefetched) issue_row(row);
     }
+    prefetched = false;
     CI_PROF(0);
 
     // ---------------------------------------------------------------------------------------- parameters of the slot
@@ -463,7 +661,8 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     const int kk = a.p.top_k[b];
     const float topp = a.p.top_p[b];
     const float log_min_p = a.p.log_min_p[b];
-    const bool fastk = sampled && kk >= 1 && kk <= CI_FASTK && kk < V;     // identical in every CTA of the cluster
+    const bool fastk = allow_fast && fast_enabled && sampled && kk >= 1 && kk <= CI_FASTK && kk < V &&
+                       !(a.flags & COLINFER_FORCE_DISTRIBUTION);         // identical in every CTA of the cluster
 
     // tail of the slice buffer: -inf (never selected, zero mass); disjoint from the bulk-copy destinations
     for (int i = slice_len + tid; i < n_pad; i += CI_THREADS) rowbuf[i] = CI_NEG_INF;
@@ -601,7 +800,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (om > lmax || (om == lmax && oi < lidx)) { lmax = om; lidx = oi; }
     }
     if (lane == 0) { sc->warp_f[warp] = lmax; sc->warp_i[warp] = lidx; }
-    if (fastk) for (int i = tid; i < CI_NB1; i += CI_THREADS) hist1[i] = 0u;   // (the penalty tables are done with)
+    if (fastk) hist1[tid] = 0u;                                  // CI_FAST_BINS == CI_THREADS (the penalty tables are done with)
     __syncthreads();
     {
         float bm = sc->warp_f[0]; int bi = sc->warp_i[0];
@@ -617,51 +816,69 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     // order inside a region is (step, lane, component).
     const int reg = ((n_pad / 128 + CI_WARPS - 1) / CI_WARPS) * 128;
     const int r_lo = min(warp * reg, n_pad), r_hi = min(r_lo + reg, n_pad);
-    ListEntry* mylist = ownlist + warp * CI_WLIST;
+    Cand* mylist = ownlist + warp * CI_WLIST;
 
     // ---------------------------------------------------------------------------------------- small top-k: candidates of the slice
     // The k-th largest of the threads' maxima bounds the slice's k-th largest logit from below, and every logit of the
     // row's top k is among its own slice's top k: the logits >= that bound, over all slices, contain the row's top k.
     float tl_fast = CI_NEG_INF;
     int my_count = 0;
+    if (it == 0) cluster.barrier_wait();                        // every CTA of the cluster runs: peers' memory may be written
     if (fastk) {
-        if (tmax > CI_NEG_INF) atomicAdd(&hist1[min(CI_NB1 - 1, __float2int_rz((lmax - tmax) * CI_FASTK_SCALE))], 1u);
+        if (tmax > CI_NEG_INF) atomicAdd(&hist1[min(CI_FAST_BINS - 1, __float2int_rz((lmax - tmax) * CI_FAST_SCALE))], 1u);
         __syncthreads();
-        u64 part = 0;
-        for (int i = tid; i < CI_NB1; i += CI_THREADS) part += hist1[i];
-        const u64 have = block_sum_u64(part, sc);
-        if (have >= (u64)kk) {
-            int bk; u64 before;
-            block_find([&](int i) { return (u64)hist1[i]; }, CI_NB1, (u64)kk, sc, bk, before);
-            tl_fast = bk >= CI_NB1 - 1 ? -CI_FLT_MAX : lmax - ((float)(bk + 1) + 0.01f) / CI_FASTK_SCALE - fabsf(lmax) * 1e-6f;
-        } else tl_fast = -CI_FLT_MAX;                           // fewer than k threads saw a finite logit: take them all
+        const u64 v = hist1[tid];
+        u64 have;
+        const u64 excl = block_excl_scan(v, sc, have);
+        int bk; u64 before;
+        block_find_thread(v, excl, (u64)kk, sc, bk, before);
+        if (have >= (u64)kk && bk >= 0 && bk < CI_FAST_BINS - 1)
+            tl_fast = lmax - ((float)(bk + 1) + 0.01f) / CI_FAST_SCALE - fabsf(lmax) * 1e-6f;
+        else tl_fast = -CI_FLT_MAX;                             // fewer than k threads saw a finite logit: take them all
         CI_PROF(10);
         int wn = 0;
         for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
             const int i = i0 + lane * 4;
-            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-            const float e4[4] = {v.x, v.y, v.z, v.w};
-            const unsigned mk = (v.x >= tl_fast ? 1u : 0u) | (v.y >= tl_fast ? 2u : 0u) | (v.z >= tl_fast ? 4u : 0u) | (v.w >= tl_fast ? 8u : 0u);
-            warp_append(mylist, wn, mk, e4, nullptr, (uint32_t)(slice_lo + i), lane);
+            const float4 v4 = *reinterpret_cast<const float4*>(rowbuf + i);
+            const float e4[4] = {v4.x, v4.y, v4.z, v4.w};
+            const unsigned mk = (v4.x >= tl_fast ? 1u : 0u) | (v4.y >= tl_fast ? 2u : 0u) | (v4.z >= tl_fast ? 4u : 0u) | (v4.w >= tl_fast ? 8u : 0u);
+            warp_append(mylist, wn, mk, e4, (uint32_t)(slice_lo + i), lane);
         }
         CI_PROF(11);
-        if (lane == 0) {
-            xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
-            sc->warp_i[warp] = wn;
+        if (lane == 0) sc->warp_i[warp] = wn;
+        __syncthreads();                                        // every thread is done with the row buffer
+        int woff = 0;
+        bool over = false;
+#pragma unroll
+        for (int w = 0; w < CI_WARPS; ++w) {
+            const int c = sc->warp_i[w];
+            if (w < warp) woff += c;
+            my_count += c;
+            over |= c > CI_WLIST;
         }
-        __syncthreads();
-        for (int w = 0; w < CI_WARPS; ++w) my_count += sc->warp_i[w];
-        if (my_count > 0xFFFF) my_count = 0xFFFF;
-        for (int w = 0; w < CI_WARPS; ++w) if (sc->warp_i[w] > CI_WLIST) my_count = 0xFFFF;   // overflow marker
+        if (over || my_count > CI_PCAP) my_count = 0xFFFF;      // overflow marker: the row takes the generic path later
+        else {
+            // push this CTA's candidates, in token order, to the CTA that will finish the row
+            Cand* dst = cluster.map_shared_rank(plist, fast_seq % CS) + rank * CI_PCAP + woff;
+            if (lane < wn) dst[lane] = mylist[lane];
+        }
+        // the row buffer is free: start the next row's copies now
+        if (a.use_bulk && next_row >= 0) {
+            if (tid == 0) issue_row(next_row);
+            prefetched = true;
+        }
+    } else if (!sampled && a.use_bulk && next_row >= 0) {
+        // greedy row: only the maximum is needed from here on
+        if (tid == 0) issue_row(next_row);
+        prefetched = true;
     }
 
     // ---------------------------------------------------------------------------------------- first exchange
     CI_PROF(3);
-    if (it == 0) cluster.barrier_wait();                        // every CTA of the cluster runs: peers' memory may be written
     if (tid < CS) {
         Hello h;
         h.lmax = lmax; h.lidx = lidx;
-        h.flags = (sc->fail ? 1 : 0) | (sc->hist_slow ? 4 : 0);
+        h.flags = (sc->fail ? 1 : 0) | (sc->hist_slow ? 4 : 0) | (sc->want_fast_off ? 8 : 0);
         h.pad = my_count;
         cluster.map_shared_rank(sc, tid)->hello[par][rank] = h;
     }
@@ -676,6 +893,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (h.pad >= 0xFFFF) fast_overflow = true;
     }
     if (aidx == 0x7fffffff) aidx = 0;
+    if (hflags & 8) fast_enabled = false;                       // a CTA ran out of room for set-aside rows
 
     int status = ((hflags & 1) ? COLINFER_ROW_TIMEOUT : 0) | ((hflags & 4) ? COLINFER_ROW_HIST_SLOW : 0);
     const bool finite_max = (L > CI_NEG_INF) && (L < CI_POS_INF);
@@ -700,6 +918,27 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         return;
     }
 
+    // ---------------------------------------------------------------------------------------- small top-k: defer the exact finish
+    if (fastk) {
+        // The candidates of every CTA sit in the shared memory of CTA fast_seq % CS, which finishes the row later, on its
+        // own, while the cluster moves on.  A row whose lists overflowed is set aside for the generic path instead.
+        const bool deferred = !fast_overflow && fast_total >= 1;
+        if (deferred) {
+            if (rank == fast_seq % CS && tid == 0) {
+                Pending pd;
+                pd.row = row; pd.L = L; pd.aidx = aidx; pd.status = status;
+                for (int q = 0; q < 8; ++q) pd.count[q] = q < CS ? sc->hello[par][q].pad : 0;
+                sc->pend = pd;
+            }
+            ++fast_seq;
+            if (fast_seq % CS == 0) flush();                    // every CTA holds a row now
+        } else {
+            if (tid == 0 && sc->n_retry_common < CI_RETRY) sc->retry_common[sc->n_retry_common++] = row;
+            if (++n_set_aside >= CI_RETRY) fast_enabled = false;
+        }
+        return;
+    }
+
     const float m = scale_logit(L, tc);
     MassFn mass;
     mass.init(tc, m);
@@ -710,40 +949,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     const bool need_topp = topp < 1.0f;
     const float u = row_uniform(a, row, b, r);
 
-    // ---------------------------------------------------------------------------------------- small top-k: the first CTA finishes on the list
-    if (fastk) {
-        int ok = 0;
-        if (!fast_overflow && fast_total <= CI_GLIST && fast_total > 0) {
-            if (rank == 0) {
-                const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, &mass);
-                CI_PROF(5);
-                // the list holds every logit of the row's top k; entries below the min-p threshold carry no weight
-                float tl_all = CI_NEG_INF;                      // no lower bound is needed: the pivot is inside the list
-                if (n > 0 && finish_on_list(glist, n, tl_all, lcut, tc, kk, need_topp, topp, u, bins, cand, sc, token, lcut, total_mass)) ok = 1;
-                CI_PROF(6);
-            }
-        }
-        // the first CTA tells the others whether the row is done (they only wait; their lists had to stay readable)
-        if (rank == 0 && tid < CS) cluster.map_shared_rank(sc, tid)->bcast_i[par] = ok;
-        CI_PROF(7);
-        cluster.sync();                                                                // (F) row finished, or not
-        CI_PROF(8);
-        ok = sc->bcast_i[par];
-        if (ok) {
-            if (rank == 0 && tid == 0) {
-                if (a.out) a.out[row] = token;
-                if (a.status) a.status[row] = status;
-                if (a.stats) {
-                    colinfer_row_stats st;
-                    st.lmax = L; st.lcut = lcut; st.tc = tc; st.status = status; st.argmax = aidx; st.mass_q = total_mass;
-                    a.stats[row] = st;
-                }
-            }
-            return;
-        }
-        __syncthreads();
-    }
-
+    // (generic path from here on: the whole cluster works on the row until its token is out)
     enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
     int path = PATH_PURE;
     float t_hi = CI_NEG_INF, t_lo = CI_POS_INF;                 // band thresholds (PATH_BAND), list threshold (PATH_LIST: t_lo)
@@ -850,7 +1056,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
             const float e4[4] = {v.x, v.y, v.z, v.w};
             const unsigned mk = (v.x >= tl ? 1u : 0u) | (v.y >= tl ? 2u : 0u) | (v.z >= tl ? 4u : 0u) | (v.w >= tl ? 8u : 0u);
-            warp_append(mylist, wn, mk, e4, nullptr, (uint32_t)(slice_lo + i), lane);
+            warp_append(mylist, wn, mk, e4, (uint32_t)(slice_lo + i), lane);
         }
         if (lane == 0) {
             xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
@@ -860,7 +1066,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         CI_PROF(6);
         cluster.sync();                                                                // (L) lists published
         // every CTA gathers the lists and finishes alike (identical inputs, identical decisions)
-        const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, &mass);
+        const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, mass);
         if (n > 0 && finish_on_list(glist, n, tl, lcut, tc, kk, need_topp, topp, u, bins, cand, sc, token, lcut, total_mass)) done = true;
         else path = PATH_FALLBACK;
     }
@@ -904,7 +1110,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
                 }
                 acc_above += (u64)a4[0] + a4[1];
                 acc_above += (u64)a4[2] + a4[3];
-                warp_append(mylist, wn, mk, e4, q4, (uint32_t)(slice_lo + i), lane);
+                warp_append(mylist, wn, mk, e4, (uint32_t)(slice_lo + i), lane);
             }
         }
         u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
@@ -929,7 +1135,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
                 const Xch* px = cluster.map_shared_rank(xch, q);
                 s1 += px->s_all; s_above += px->s_above;
             }
-            const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, nullptr);
+            const int n = gather_lists(cluster, CS, xch, ownlist, glist, sc, mass);
             bool ok = n >= 0 && s1 > 0;
             float cut2 = lcut;
             if (ok) {
@@ -952,7 +1158,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
                 // add the kept band entries of this warp's own list to its region's kept mass
                 u64 add = 0;
                 const int mine = min(wn, CI_WLIST);
-                for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mylist[j].q;
+                for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mass(mylist[j].l);
                 wkeep += warp_sum_u64(add);
             } else {
                 // The estimated band missed the pivot (or a list overflowed): every CTA takes the exact radix select
@@ -1045,7 +1251,29 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     int it = 0;
     for (long long row = blockIdx.x / CS; row < n_rows; row += n_clusters, ++it) {
         if (it) __syncthreads();                               // every thread is done with the previous row's buffers
-        process_row((int)row, it);
+        const long long nxt = row + n_clusters < n_rows ? row + n_clusters : -1;
+        process_row((int)row, it, true, nxt);
+    }
+    // Deferred rows still waiting; then the rows that were set aside take the generic path.
+    if (it == 0) cluster.barrier_wait();                       // (a cluster without rows still completes the opening barrier)
+    flush();
+    {
+        int n_all = 0;
+        if (tid == 0) {
+            for (int i = 0; i < sc->n_retry_common; ++i) sc->retry_all[n_all++] = sc->retry_common[i];
+            for (int q = 0; q < CS; ++q) {
+                const Scratch* ps = cluster.map_shared_rank(sc, q);
+                const int nq = ps->n_retry_mine;
+                for (int i = 0; i < nq && i < CI_RETRY; ++i) sc->retry_all[n_all++] = ps->retry_mine[i];
+            }
+            sc->bcast_i[0] = n_all;
+        }
+        cluster.sync();                                        // every CTA has read the peers' lists
+        n_all = sc->bcast_i[0];
+        for (int i = 0; i < n_all; ++i, ++it) {
+            __syncthreads();
+            process_row(sc->retry_all[i], it, false, -1);
+        }
     }
     if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) {
         unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
@@ -1058,7 +1286,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 static int g_cluster_override = 0;
 static long long* g_prof = nullptr;
 static int g_prof_slots = 0;
-static const int kFixedSmem = 24 * 1024 + CI_WARPS * CI_WLIST * (int)sizeof(ListEntry) + CI_MAX_CHUNKS * 8 +
+static const int kFixedSmem = 24 * 1024 + (CI_WARPS * CI_WLIST + 8 * CI_PCAP) * (int)sizeof(Cand) + CI_MAX_CHUNKS * 8 +
                               (int)sizeof(Xch) + (int)sizeof(Scratch) + 64;
 
 static int pick_geometry(int V, int dtype, const void* logits, colinfer_geometry* g) {
