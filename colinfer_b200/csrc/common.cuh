@@ -114,19 +114,27 @@ __device__ __forceinline__ bool mbar_test(void* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(20000u) : "memory");   // may suspend the thread up to ~20 us
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` clock cycles and returns false (the caller records a status and carries on).
+// Bounded wait for a phase of an mbarrier, for a whole warp: one lane waits (suspended by the hardware between tries,
+// so the other warps of the SM keep their issue slots), then the warp reconverges.  Gives up after `limit` clock
+// cycles and returns false (the caller records a status and carries on).
 __device__ __forceinline__ bool mbar_wait_bounded(void* bar, uint32_t parity, long long limit) {
-    if (mbar_test(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_test(bar, parity)) {
-        if (clock64() - t0 > limit) return false;
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        if (!mbar_test(bar, parity)) {
+            const long long t0 = clock64();
+            while (!mbar_test(bar, parity)) {
+                if (clock64() - t0 > limit) { ok = 0; break; }
+                __nanosleep(64);
+            }
+        }
     }
-    return true;
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 // 1-D bulk copy global -> this CTA's shared memory, completion counted on an mbarrier.  dst, src 16-byte aligned,
 // bytes a multiple of 16.  No multicast.

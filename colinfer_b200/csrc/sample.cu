@@ -60,7 +60,7 @@ struct SampleArgs {
     long long* prof; int prof_slots;   // optional per-CTA phase timestamps (profiling hook)
 };
 // Profiling hook: thread 0 adds the cycles since its previous marker to the slot's total (summed over the CTA's rows).
-#define CI_PROF(slot) do { if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots) { const long long t_ = clock64(); a.prof[(size_t)blockIdx.x * 16 + (slot)] += t_ - prof_last; prof_last = t_; } } while (0)
+#define CI_PROF(slot) do { if (a.prof && tid == 0) { const long long t_ = clock64(); sc->prof[slot] += t_ - prof_last; prof_last = t_; } } while (0)
 
 struct ListEntry { uint32_t idx; float l; uint32_t q; };   // gathered list: token, logit, mass
 struct Cand { uint32_t idx; float l; };                      // a warp's list / pushed candidates: token, logit
@@ -98,6 +98,7 @@ struct Scratch {
     Pending pend;
     int n_retry_common, n_retry_mine, want_fast_off;
     int retry_common[CI_RETRY], retry_mine[CI_RETRY], retry_all[CI_RETRY * 9];
+    long long prof[12];            // profiling hook: cycles per phase, summed over the CTA's rows
     int bcast_i[2];                // written by the cluster's first CTA, per row parity
     u64 mass_in[2][8];             // kept mass of every CTA's slice, written by the peers, per row parity
 };
@@ -599,6 +600,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     const long long n_rows = (long long)a.B * a.R;
     long long prof_last = clock64();
     const long long prof_t0 = prof_last;
+    if (a.prof && tid == 0) for (int i = 0; i < 12; ++i) sc->prof[i] = 0;
 
     // Starts the bulk copies of one row's slice (thread 0 only; every thread must be done reading the buffer).
     auto issue_row = [&](const long long rw) {
@@ -716,6 +718,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (c < nchunks) {
             if (a.use_bulk) {
                 if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
+                CI_PROF(5);
             } else {
                 const int valid = min(CI_CHUNK, slice_len - c_lo);
                 const size_t g0 = (size_t)row * V + slice_lo + c_lo;
@@ -789,6 +792,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
                 lidx = g + (v.x == m4 ? 0 : v.y == m4 ? 1 : v.z == m4 ? 2 : 3);
             }
         }
+        CI_PROF(2);
     }
     CI_PROF(2);
     const float tmax = lmax;                                    // this thread's own maximum (used by the top-k bound)
@@ -1279,6 +1283,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
         a.prof[(size_t)blockIdx.x * 16 + 13] = (long long)gt;
         a.prof[(size_t)blockIdx.x * 16 + 12] = clock64() - prof_t0;
+        for (int i = 0; i < 12; ++i) a.prof[(size_t)blockIdx.x * 16 + i] = sc->prof[i];
     }
 }
 
