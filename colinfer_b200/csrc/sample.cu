@@ -27,20 +27,22 @@
 #include "common.cuh"
 #include "../../include/colinfer_b200.h"
 
-#define CI_THREADS 512
+#define CI_THREADS 128
 #define CI_WARPS (CI_THREADS / 32)
 #define CI_CHUNK 4096            // elements per bulk copy
 #define CI_MAX_CHUNKS 16
 #define CI_NB1 4096              // fine buckets over the distance from the row maximum
 #define CI_RANGE 25.0f           // the buckets cover distances up to CI_RANGE * temperature
 #define CI_FASTK 100             // largest top_k handled by the per-slice candidate lists
-#define CI_FAST_BINS 512         // bins of the thread-maxima histogram (one per thread)
+#define CI_FAST_BINS 512         // bins of the thread-maxima histogram and of the exact finish
+#define CI_TGROUPS 4              // maxima each thread keeps (interleaved groups of its elements) for the top-k bound
+#define CI_FIN_MAX 1024          // candidates of one row at the CTA that finishes it (8 x CI_PCAP)
 #define CI_FAST_SCALE 32.0f      // its bins per unit logit (covers 16 units below the slice maximum)
 #define CI_PCAP 128              // candidates one CTA may push to the CTA that finishes the row
 #define CI_FIN_SCALE 64.0f       // bins per unit logit of the exact selection on the pushed candidates (8 units)
 #define CI_FIN_CAND 64           // candidates of one bin examined pairwise
 #define CI_RETRY 8               // rows a CTA may set aside for the generic path before the fast path is switched off
-#define CI_WLIST 24              // list entries per warp
+#define CI_WLIST 64              // list entries per warp
 #define CI_GLIST 1365            // gathered list entries (16 KB)
 #define CI_SEL_BINS 512          // coarse bins of the exact selection on a gathered list
 #define CI_FB_NB 256             // radix buckets per level of the fallback select (8 bits)
@@ -398,6 +400,30 @@ __device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, 
     wn += tot;
 }
 
+// Collects, in token order, the logits >= tl of one warp's region [r_lo, r_hi) of the slice into the warp's list.
+// Four float4 groups per lane and step are loaded together (their latencies overlap); appends are rare.
+__device__ __forceinline__ void collect_region(const float* rowbuf, int r_lo, int r_hi, float tl, Cand* mylist, int& wn,
+                                               uint32_t slice_lo, int lane) {
+    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+        float4 v[4];
+        unsigned mk[4], anym = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * 128 + lane * 4;
+            v[k] = i < r_hi ? *reinterpret_cast<const float4*>(rowbuf + i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+            mk[k] = (v[k].x >= tl ? 1u : 0u) | (v[k].y >= tl ? 2u : 0u) | (v[k].z >= tl ? 4u : 0u) | (v[k].w >= tl ? 8u : 0u);
+            anym |= mk[k];
+        }
+        if (__ballot_sync(0xffffffffu, anym != 0u)) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float e4[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                warp_append(mylist, wn, mk[k], e4, slice_lo + (uint32_t)(i0 + k * 128 + lane * 4), lane);
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ lean block primitives
 // Exclusive prefix of one value per thread over the CTA (thread order), and the total.  Two __syncthreads.
 __device__ __forceinline__ u64 block_excl_scan(u64 v, Scratch* sc, u64& total) {
@@ -416,41 +442,53 @@ __device__ __forceinline__ u64 block_excl_scan(u64 v, Scratch* sc, u64& total) {
     total = sc->wtotal;
     return sc->woff[warp] + incl - v;
 }
-// The thread whose [excl, excl + v] interval contains `target` (1 <= target <= total) announces itself.  One __syncthreads.
-__device__ __forceinline__ void block_find_thread(u64 v, u64 excl, u64 target, Scratch* sc, int& ftid, u64& fexcl) {
-    if (excl < target && target <= excl + v) { sc->found_tid = (int)threadIdx.x; sc->found_excl = excl; }
-    __syncthreads();
-    ftid = sc->found_tid;
-    fexcl = sc->found_excl;
-}
 
-// Exact weighted selection among up to two entries per thread: the value v such that W(l > v) < target <= W(l >= v),
-// W summing the weights w.  512 bins over the distance from the row maximum (one per thread), then the pivot bin's
-// entries pairwise.  Returns false when the pivot falls outside the binned range or its bin is too crowded.
-// Seven __syncthreads.  All threads call with the same target.
-__device__ bool lean_select(const float* el, const u64* w, float L, u64 target, u64* bins, Scratch* sc, float& value) {
+// Where the running sum of CI_FAST_BINS bins (ascending index) first reaches `target`: the bin, the sum before it, and
+// the total.  bin = -1 when target exceeds the total (or is 0).  Three __syncthreads.  All threads call.
+template <class T>
+__device__ void bins_find(const T* bins, u64 target, Scratch* sc, int& bin, u64& before, u64& total) {
+    constexpr int PER = CI_FAST_BINS / CI_THREADS;
     const int tid = threadIdx.x;
-    bins[tid] = 0;
-    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; }
-    __syncthreads();
-    int kb[2];
+    u64 loc[PER], s = 0;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        kb[j] = min(CI_FAST_BINS - 1, __float2int_rz((L - el[j]) * CI_FIN_SCALE));
-        if (w[j]) atomicAdd(&bins[kb[j]], w[j]);
+    for (int j = 0; j < PER; ++j) { loc[j] = (u64)bins[tid * PER + j]; s += loc[j]; }
+    const u64 excl = block_excl_scan(s, sc, total);
+    if (excl < target && target <= excl + s) {
+        u64 run = excl;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            if (run + loc[j] >= target) { sc->found_tid = tid * PER + j; sc->found_excl = run; break; }
+            run += loc[j];
+        }
     }
     __syncthreads();
-    const u64 v = bins[tid];
-    u64 total;
-    const u64 excl = block_excl_scan(v, sc, total);
-    int b_star; u64 before;
-    block_find_thread(v, excl, target, sc, b_star, before);
+    bin = sc->found_tid;
+    before = sc->found_excl;
+}
+
+// Exact weighted selection among n entries (logits fl[0..n) in shared memory, weight wt(i)): the value v such that
+// W(l > v) < target <= W(l >= v).  CI_FAST_BINS bins over the distance from the row maximum, then the pivot bin's
+// entries pairwise.  Returns false when the pivot falls outside the binned range or its bin is too crowded.
+// All threads call with the same arguments.
+template <class W>
+__device__ bool lean_select(const float* fl, int n, W wt, float L, u64 target, u64* bins, Scratch* sc, float& value) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < CI_FAST_BINS; i += CI_THREADS) bins[i] = 0;
+    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; }
+    __syncthreads();
+    for (int i = tid; i < n; i += CI_THREADS) {
+        const u64 w = wt(i);
+        if (w) atomicAdd(&bins[min(CI_FAST_BINS - 1, __float2int_rz((L - fl[i]) * CI_FIN_SCALE))], w);
+    }
+    __syncthreads();
+    int b_star; u64 before, total;
+    bins_find(bins, target, sc, b_star, before, total);
     if (b_star < 0 || b_star >= CI_FAST_BINS - 1) return false;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        if (w[j] && kb[j] == b_star) {
+    for (int i = tid; i < n; i += CI_THREADS) {
+        const u64 w = wt(i);
+        if (w && min(CI_FAST_BINS - 1, __float2int_rz((L - fl[i]) * CI_FIN_SCALE)) == b_star) {
             const int slot = atomicAdd(&sc->ncand, 1);
-            if (slot < CI_FIN_CAND) { sc->cand_l[slot] = el[j]; sc->cand_w[slot] = w[j]; }
+            if (slot < CI_FIN_CAND) { sc->cand_l[slot] = fl[i]; sc->cand_w[slot] = w; }
         }
     }
     __syncthreads();
@@ -473,9 +511,13 @@ __device__ bool lean_select(const float* el, const u64* w, float L, u64 target, 
 // Exact finish of a row from the candidates its CTAs pushed into this CTA's shared memory: min-p, top-k, top-p and
 // the draw, all inside this CTA (no cluster traffic).  The candidates contain the row's top k logits (and possibly
 // more), in token order: CTA by CTA, each CTA's in token order.  Writes the row's outputs and returns true, or returns
-// false when the row has to take the generic path.  All threads of the CTA call.
-__device__ bool finish_pending(const SampleArgs& a, const Pending& pd, const Cand* plist, int CS, u64* bins, Scratch* sc) {
+// false when the row has to take the generic path.  `work` is CI_FAST_BINS * 8 + CI_FIN_MAX * 8 bytes of scratch.
+// All threads of the CTA call.
+__device__ bool finish_pending(const SampleArgs& a, const Pending& pd, const Cand* plist, int CS, unsigned char* work, Scratch* sc) {
     const int tid = threadIdx.x;
+    u64* bins = reinterpret_cast<u64*>(work);
+    float* fl = reinterpret_cast<float*>(work + CI_FAST_BINS * 8);
+    uint32_t* fi = reinterpret_cast<uint32_t*>(fl + CI_FIN_MAX);
     const int row = pd.row, b = row / a.R, r = row % a.R;
     const float tc = fmaxf(a.p.temperature[b], 1e-6f);
     const int kk = a.p.top_k[b];
@@ -492,56 +534,59 @@ __device__ bool finish_pending(const SampleArgs& a, const Pending& pd, const Can
 #pragma unroll
     for (int q = 0; q < 8; ++q) pre[q + 1] = pre[q] + (q < CS ? pd.count[q] : 0);
     const int n = pre[8];
-    if (n > 2 * CI_THREADS) return false;
-    // thread t holds entries 2t and 2t + 1 of the concatenated lists: thread order is token order
-    float el[2]; uint32_t ei[2];
+    if (n > CI_FIN_MAX || n <= 0) return false;
+    // the concatenated lists, contiguous and in token order
+    for (int e = tid; e < n; e += CI_THREADS) {
+        int q = 0;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int e = 2 * tid + j;
-        el[j] = CI_NEG_INF; ei[j] = 0;
-        if (e < n) {
-            int q = 0;
-#pragma unroll
-            for (int t = 1; t < 8; ++t) q += (pre[t] <= e) ? 1 : 0;
-            const Cand c = plist[q * CI_PCAP + (e - pre[q])];
-            el[j] = c.l; ei[j] = c.idx;
-        }
+        for (int t = 1; t < 8; ++t) q += (pre[t] <= e) ? 1 : 0;
+        const Cand c = plist[q * CI_PCAP + (e - pre[q])];
+        fl[e] = c.l; fi[e] = c.idx;
     }
+    __syncthreads();
     // ---- top-k: the k-th largest of the candidates that survive min-p
-    u64 w[2];
-    w[0] = (el[0] >= cut && el[0] > CI_NEG_INF) ? 1ull : 0ull;
-    w[1] = (el[1] >= cut && el[1] > CI_NEG_INF) ? 1ull : 0ull;
+    u64 cnt = 0;
+    for (int i = tid; i < n; i += CI_THREADS) cnt += (fl[i] >= cut && fl[i] > CI_NEG_INF) ? 1 : 0;
     u64 survivors;
-    block_excl_scan(w[0] + w[1], sc, survivors);
+    block_excl_scan(cnt, sc, survivors);
     if (survivors == 0) return false;
     if ((u64)kk <= survivors) {                               // else fewer than k survive min-p: top-k removes nothing
         float lk;
-        if (!lean_select(el, w, L, (u64)kk, bins, sc, lk)) return false;
+        const float c0 = cut;
+        if (!lean_select(fl, n, [&](int i) { return (u64)((fl[i] >= c0 && fl[i] > CI_NEG_INF) ? 1 : 0); }, L, (u64)kk, bins, sc, lk))
+            return false;
         cut = fmaxf(cut, lower_logit_for(scale_logit(lk, tc), tc, lk));
     }
     // ---- top-p over the kept candidates
-    u64 q2[2];
-    q2[0] = (el[0] >= cut && el[0] > CI_NEG_INF) ? (u64)mass(el[0]) : 0ull;
-    q2[1] = (el[1] >= cut && el[1] > CI_NEG_INF) ? (u64)mass(el[1]) : 0ull;
     if (topp < 1.0f) {
+        const float c0 = cut;
+        u64 part = 0;
+        for (int i = tid; i < n; i += CI_THREADS) part += (fl[i] >= c0 && fl[i] > CI_NEG_INF) ? (u64)mass(fl[i]) : 0ull;
         u64 s1;
-        block_excl_scan(q2[0] + q2[1], sc, s1);
+        block_excl_scan(part, sc, s1);
         if (s1 == 0) return false;
         float lp;
-        if (!lean_select(el, q2, L, ceil_target(topp, s1), bins, sc, lp)) return false;
+        if (!lean_select(fl, n, [&](int i) { return (fl[i] >= c0 && fl[i] > CI_NEG_INF) ? (u64)mass(fl[i]) : 0ull; }, L,
+                         ceil_target(topp, s1), bins, sc, lp))
+            return false;
         cut = fmaxf(cut, lower_logit_for(scale_logit(lp, tc), tc, lp));
-        if (!(el[0] >= cut)) q2[0] = 0;
-        if (!(el[1] >= cut)) q2[1] = 0;
     }
     // ---- the draw: first candidate (token order) whose running kept mass reaches u * total
+    const int ept = (n + CI_THREADS - 1) / CI_THREADS;
+    const int e_lo = tid * ept, e_hi = min(e_lo + ept, n);
+    u64 mine = 0;
+    for (int i = e_lo; i < e_hi; ++i) mine += (fl[i] >= cut && fl[i] > CI_NEG_INF) ? (u64)mass(fl[i]) : 0ull;
     u64 total;
-    const u64 excl = block_excl_scan(q2[0] + q2[1], sc, total);
+    const u64 excl = block_excl_scan(mine, sc, total);
     if (total == 0) return false;
     const u64 target = ceil_target(u, total);
-    int ftid; u64 fexcl;
-    block_find_thread(q2[0] + q2[1], excl, target, sc, ftid, fexcl);
-    if (tid == ftid) {
-        const long long token = (excl + q2[0] >= target) ? (long long)ei[0] : (long long)ei[1];
+    if (excl < target && target <= excl + mine) {
+        u64 run = excl;
+        long long token = -1;
+        for (int i = e_lo; i < e_hi; ++i) {
+            run += (fl[i] >= cut && fl[i] > CI_NEG_INF) ? (u64)mass(fl[i]) : 0ull;
+            if (run >= target) { token = (long long)fi[i]; break; }
+        }
         if (a.out) a.out[row] = token;
         if (a.status) a.status[row] = pd.status;
         if (a.stats) {
@@ -551,7 +596,7 @@ __device__ bool finish_pending(const SampleArgs& a, const Pending& pd, const Can
         }
     }
     __syncthreads();
-    return ftid >= 0;
+    return true;
 }
 
 extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __grid_constant__ SampleArgs a) {
@@ -603,7 +648,9 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     if (a.prof && tid == 0) for (int i = 0; i < 12; ++i) sc->prof[i] = 0;
 
     // Starts the bulk copies of one row's slice (thread 0 only; every thread must be done reading the buffer).
+    long long t_issue = 0, t_issue_end = 0;
     auto issue_row = [&](const long long rw) {
+        t_issue = clock64();
         fence_proxy_async();                                   // earlier reads of the buffer precede these writes
         const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)rw * V + slice_lo;
         for (int c = 0; c < nchunks; ++c) {
@@ -611,6 +658,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
             bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
         }
+        t_issue_end = clock64();
     };
     bool prefetched = false;          // the next row's copies are already in flight
     bool fast_enabled = true;         // small top-k rows may take the deferred path (identical in every CTA)
@@ -622,7 +670,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     auto flush = [&]() {
         __syncthreads();
         if (sc->pend.row >= 0) {
-            const bool ok = finish_pending(a, sc->pend, plist, CS, reinterpret_cast<u64*>(hreg), sc);
+            const bool ok = finish_pending(a, sc->pend, plist, CS, hreg, sc);
             if (tid == 0) {
                 if (!ok) {
                     if (sc->n_retry_mine < CI_RETRY) sc->retry_mine[sc->n_retry_mine++] = sc->pend.row;
@@ -711,6 +759,10 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     // ---------------------------------------------------------------------------------------- pass A: land, penalise, mask, maximum
     float lmax = CI_NEG_INF;
     int lidx = 0x7fffffff;
+    int lpos = -1;                                              // float4 group of the slice that holds this thread's maximum
+    float tg[CI_TGROUPS];                                       // maxima of this thread's interleaved element groups
+#pragma unroll
+    for (int j = 0; j < CI_TGROUPS; ++j) tg[j] = CI_NEG_INF;
     const int n_pass_chunks = (n_pad + CI_CHUNK - 1) / CI_CHUNK;
     for (int c = 0; c < n_pass_chunks; ++c) {
         const int c_lo = c * CI_CHUNK;
@@ -719,6 +771,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             if (a.use_bulk) {
                 if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
                 CI_PROF(5);
+                if (a.prof && tid == 0 && c == nchunks - 1) { sc->prof[8] += clock64() - t_issue; sc->prof[9] += t_issue_end - t_issue; }
             } else {
                 const int valid = min(CI_CHUNK, slice_len - c_lo);
                 const size_t g0 = (size_t)row * V + slice_lo + c_lo;
@@ -772,30 +825,49 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             }
             __syncthreads();
         }
+        // four float4 groups per thread and step, loaded together so that their latencies overlap
         float4* row4 = reinterpret_cast<float4*>(rowbuf + c_lo);
-        for (int i = tid; i * 4 < c_len; i += CI_THREADS) {
-            float4 v = row4[i];
-            const int g = slice_lo + c_lo + i * 4;              // global token index of v.x
-            if (mrow != nullptr && g < V) {
-                const uint32_t bits = ((uint32_t)__ldg(mrow + (g >> 5)) >> (g & 31)) & 0xFu;
-                if (bits != 0xFu) {
-                    if (!(bits & 1u)) v.x = CI_NEG_INF;
-                    if (!(bits & 2u)) v.y = CI_NEG_INF;
-                    if (!(bits & 4u)) v.z = CI_NEG_INF;
-                    if (!(bits & 8u)) v.w = CI_NEG_INF;
-                    row4[i] = v;
+        const int n4 = c_len >> 2;
+        for (int i0 = tid; i0 < n4; i0 += CI_TGROUPS * CI_THREADS) {
+            float4 v[CI_TGROUPS];
+#pragma unroll
+            for (int k = 0; k < CI_TGROUPS; ++k) {
+                const int i = i0 + k * CI_THREADS;
+                v[k] = i < n4 ? row4[i] : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+            }
+            if (mrow != nullptr) {
+#pragma unroll
+                for (int k = 0; k < CI_TGROUPS; ++k) {
+                    const int i = i0 + k * CI_THREADS;
+                    const int g = slice_lo + c_lo + i * 4;      // global token index of v[k].x
+                    if (i < n4 && g < V) {
+                        const uint32_t bits = ((uint32_t)__ldg(mrow + (g >> 5)) >> (g & 31)) & 0xFu;
+                        if (bits != 0xFu) {
+                            if (!(bits & 1u)) v[k].x = CI_NEG_INF;
+                            if (!(bits & 2u)) v[k].y = CI_NEG_INF;
+                            if (!(bits & 4u)) v[k].z = CI_NEG_INF;
+                            if (!(bits & 8u)) v[k].w = CI_NEG_INF;
+                            row4[i] = v[k];
+                        }
+                    }
                 }
             }
-            const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-            if (m4 > lmax) {
-                lmax = m4;
-                lidx = g + (v.x == m4 ? 0 : v.y == m4 ? 1 : v.z == m4 ? 2 : 3);
+#pragma unroll
+            for (int k = 0; k < CI_TGROUPS; ++k) {
+                const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
+                tg[k] = fmaxf(tg[k], m4);
+                const bool up = m4 > lmax;                      // strict: the first (lowest) position of the maximum stays
+                lmax = up ? m4 : lmax;
+                lpos = up ? (c_lo >> 2) + i0 + k * CI_THREADS : lpos;
             }
         }
         CI_PROF(2);
     }
     CI_PROF(2);
-    const float tmax = lmax;                                    // this thread's own maximum (used by the top-k bound)
+    if (lpos >= 0) {
+        const float4 v = reinterpret_cast<const float4*>(rowbuf)[lpos];
+        lidx = slice_lo + lpos * 4 + (v.x == lmax ? 0 : v.y == lmax ? 1 : v.z == lmax ? 2 : 3);
+    }
     // block reduce (largest value, lowest index among equals)
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
@@ -804,7 +876,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         if (om > lmax || (om == lmax && oi < lidx)) { lmax = om; lidx = oi; }
     }
     if (lane == 0) { sc->warp_f[warp] = lmax; sc->warp_i[warp] = lidx; }
-    if (fastk) hist1[tid] = 0u;                                  // CI_FAST_BINS == CI_THREADS (the penalty tables are done with)
+    if (fastk) for (int i = tid; i < CI_FAST_BINS; i += CI_THREADS) hist1[i] = 0u;   // (the penalty tables are done with)
     __syncthreads();
     {
         float bm = sc->warp_f[0]; int bi = sc->warp_i[0];
@@ -823,31 +895,24 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     Cand* mylist = ownlist + warp * CI_WLIST;
 
     // ---------------------------------------------------------------------------------------- small top-k: candidates of the slice
-    // The k-th largest of the threads' maxima bounds the slice's k-th largest logit from below, and every logit of the
+    // The k-th largest of the threads' group maxima (CI_TGROUPS disjoint groups per thread) bounds the slice's k-th largest logit from below, and every logit of the
     // row's top k is among its own slice's top k: the logits >= that bound, over all slices, contain the row's top k.
     float tl_fast = CI_NEG_INF;
     int my_count = 0;
     if (it == 0) cluster.barrier_wait();                        // every CTA of the cluster runs: peers' memory may be written
     if (fastk) {
-        if (tmax > CI_NEG_INF) atomicAdd(&hist1[min(CI_FAST_BINS - 1, __float2int_rz((lmax - tmax) * CI_FAST_SCALE))], 1u);
+#pragma unroll
+        for (int j = 0; j < CI_TGROUPS; ++j)
+            if (tg[j] > CI_NEG_INF) atomicAdd(&hist1[min(CI_FAST_BINS - 1, __float2int_rz((lmax - tg[j]) * CI_FAST_SCALE))], 1u);
         __syncthreads();
-        const u64 v = hist1[tid];
-        u64 have;
-        const u64 excl = block_excl_scan(v, sc, have);
-        int bk; u64 before;
-        block_find_thread(v, excl, (u64)kk, sc, bk, before);
+        int bk; u64 before, have;
+        bins_find(hist1, (u64)kk, sc, bk, before, have);
         if (have >= (u64)kk && bk >= 0 && bk < CI_FAST_BINS - 1)
             tl_fast = lmax - ((float)(bk + 1) + 0.01f) / CI_FAST_SCALE - fabsf(lmax) * 1e-6f;
         else tl_fast = -CI_FLT_MAX;                             // fewer than k threads saw a finite logit: take them all
         CI_PROF(10);
         int wn = 0;
-        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-            const int i = i0 + lane * 4;
-            const float4 v4 = *reinterpret_cast<const float4*>(rowbuf + i);
-            const float e4[4] = {v4.x, v4.y, v4.z, v4.w};
-            const unsigned mk = (v4.x >= tl_fast ? 1u : 0u) | (v4.y >= tl_fast ? 2u : 0u) | (v4.z >= tl_fast ? 4u : 0u) | (v4.w >= tl_fast ? 8u : 0u);
-            warp_append(mylist, wn, mk, e4, (uint32_t)(slice_lo + i), lane);
-        }
+        collect_region(rowbuf, r_lo, r_hi, tl_fast, mylist, wn, (uint32_t)slice_lo, lane);
         CI_PROF(11);
         if (lane == 0) sc->warp_i[warp] = wn;
         __syncthreads();                                        // every thread is done with the row buffer
@@ -864,7 +929,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         else {
             // push this CTA's candidates, in token order, to the CTA that will finish the row
             Cand* dst = cluster.map_shared_rank(plist, fast_seq % CS) + rank * CI_PCAP + woff;
-            if (lane < wn) dst[lane] = mylist[lane];
+            for (int j = lane; j < wn; j += 32) dst[j] = mylist[j];
         }
         // the row buffer is free: start the next row's copies now
         if (a.use_bulk && next_row >= 0) {
@@ -967,13 +1032,20 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         __syncthreads();
         {
             const float4* row4 = reinterpret_cast<const float4*>(rowbuf);
-            for (int i = tid; i * 4 < n_pad; i += CI_THREADS) {
-                const float4 v = row4[i];
-                const float e4[4] = {v.x, v.y, v.z, v.w};
+            const int n4 = n_pad >> 2;
+            for (int i0 = tid; i0 < n4; i0 += 4 * CI_THREADS) {
+                float e[16];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (e4[j] >= lk) atomicAdd(&hist1[min(CI_NB1 - 1, __float2int_rz((L - e4[j]) * SC))], 1u);
+                for (int k = 0; k < 4; ++k) {
+                    const int i = i0 + k * CI_THREADS;
+                    const float4 v = i < n4 ? row4[i] : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+                    e[4 * k] = v.x; e[4 * k + 1] = v.y; e[4 * k + 2] = v.z; e[4 * k + 3] = v.w;
                 }
+                int bkt[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) bkt[j] = min(CI_NB1 - 1, __float2int_rz((L - e[j]) * SC));
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (e[j] >= lk) atomicAdd(&hist1[bkt[j]], 1u);
             }
         }
         __syncthreads();
@@ -1055,13 +1127,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     if (path == PATH_LIST) {
         const float tl = fmaxf(fmaxf(t_lo, lcut), -CI_FLT_MAX);
         int wn = 0;
-        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-            const int i = i0 + lane * 4;
-            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-            const float e4[4] = {v.x, v.y, v.z, v.w};
-            const unsigned mk = (v.x >= tl ? 1u : 0u) | (v.y >= tl ? 2u : 0u) | (v.z >= tl ? 4u : 0u) | (v.w >= tl ? 8u : 0u);
-            warp_append(mylist, wn, mk, e4, (uint32_t)(slice_lo + i), lane);
-        }
+        collect_region(rowbuf, r_lo, r_hi, tl, mylist, wn, (uint32_t)slice_lo, lane);
         if (lane == 0) {
             xch->wcount[warp] = (unsigned short)min(wn, CI_WLIST);
             if (wn > CI_WLIST) xch->list_overflow = 1;
@@ -1095,26 +1161,37 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
         const float lk = fmaxf(lcut, -CI_FLT_MAX);
         u64 acc_all = 0, acc_above = 0;
         int wn = 0;
-        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-            const int i = i0 + lane * 4;
-            const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
-            const float e4[4] = {v.x, v.y, v.z, v.w};
-            uint32_t q4[4];
+        for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+            float e[16];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) q4[j] = e4[j] >= lk ? mass(e4[j]) : 0u;
-            acc_all += (u64)q4[0] + q4[1];
-            acc_all += (u64)q4[2] + q4[3];
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * 128 + lane * 4;
+                const float4 v = i < r_hi ? *reinterpret_cast<const float4*>(rowbuf + i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+                e[4 * k] = v.x; e[4 * k + 1] = v.y; e[4 * k + 2] = v.z; e[4 * k + 3] = v.w;
+            }
+            uint32_t q[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) q[j] = e[j] >= lk ? mass(e[j]) : 0u;
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) acc_all += (u64)q[j] + q[j + 1];
             if (band) {
-                uint32_t a4[4];
-                unsigned mk = 0;
+                unsigned mk[4], anym = 0;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    a4[j] = e4[j] > t_hi ? q4[j] : 0u;
-                    if (e4[j] <= t_hi && e4[j] >= t_lo && e4[j] >= lk) mk |= 1u << j;
+                for (int k = 0; k < 4; ++k) {
+                    mk[k] = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float x = e[4 * k + j];
+                        if (x > t_hi) acc_above += q[4 * k + j];
+                        else if (x >= t_lo && x >= lk) mk[k] |= 1u << j;
+                    }
+                    anym |= mk[k];
                 }
-                acc_above += (u64)a4[0] + a4[1];
-                acc_above += (u64)a4[2] + a4[3];
-                warp_append(mylist, wn, mk, e4, (uint32_t)(slice_lo + i), lane);
+                if (__ballot_sync(0xffffffffu, anym != 0u)) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        warp_append(mylist, wn, mk[k], &e[4 * k], (uint32_t)(slice_lo + i0 + k * 128 + lane * 4), lane);
+                }
             }
         }
         u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
