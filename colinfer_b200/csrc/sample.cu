@@ -27,7 +27,7 @@
 #include "common.cuh"
 #include "../../include/colinfer_b200.h"
 
-#define CI_THREADS 128
+#define CI_THREADS 256
 #define CI_WARPS (CI_THREADS / 32)
 #define CI_CHUNK 4096            // elements per bulk copy
 #define CI_MAX_CHUNKS 16
@@ -42,7 +42,7 @@
 #define CI_FIN_SCALE 64.0f       // bins per unit logit of the exact selection on the pushed candidates (8 units)
 #define CI_FIN_CAND 64           // candidates of one bin examined pairwise
 #define CI_RETRY 8               // rows a CTA may set aside for the generic path before the fast path is switched off
-#define CI_WLIST 64              // list entries per warp
+#define CI_WLIST 48              // list entries per warp
 #define CI_GLIST 1365            // gathered list entries (16 KB)
 #define CI_SEL_BINS 512          // coarse bins of the exact selection on a gathered list
 #define CI_FB_NB 256             // radix buckets per level of the fallback select (8 bits)
@@ -379,17 +379,15 @@ __device__ bool finish_on_list(const ListEntry* glist, int n, float tl, float lc
     return true;
 }
 
-// Appends the components of one float4 group selected by the 4-bit mask mk to the warp's list, in token order.
-// wn is the warp's running count (uniform over the warp); entries beyond CI_WLIST are dropped and counted.
+// Appends the components of one float4 group selected by the 4-bit mask mk to the warp's list, in token order
+// (lane, then component).  Positions come from four ballots, no scan.  wn is the warp's running count (uniform over
+// the warp); entries beyond CI_WLIST are dropped and counted.
 __device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, const float* e4, uint32_t idx0, int lane) {
-    const unsigned any = __ballot_sync(0xffffffffu, mk != 0u);
-    if (!any) return;
-    const int c = __popc(mk);
-    int pre = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, pre, o); if (lane >= o) pre += t; }
-    const int tot = __shfl_sync(0xffffffffu, pre, 31);
-    int at = wn + pre - c;
+    const unsigned b0 = __ballot_sync(0xffffffffu, mk & 1u), b1 = __ballot_sync(0xffffffffu, mk & 2u);
+    const unsigned b2 = __ballot_sync(0xffffffffu, mk & 4u), b3 = __ballot_sync(0xffffffffu, mk & 8u);
+    if (!(b0 | b1 | b2 | b3)) return;
+    const unsigned lt = (1u << lane) - 1u;
+    int at = wn + __popc(b0 & lt) + __popc(b1 & lt) + __popc(b2 & lt) + __popc(b3 & lt);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         if (mk & (1u << j)) {
@@ -397,7 +395,7 @@ __device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, 
             ++at;
         }
     }
-    wn += tot;
+    wn += __popc(b0) + __popc(b1) + __popc(b2) + __popc(b3);
 }
 
 // Collects, in token order, the logits >= tl of one warp's region [r_lo, r_hi) of the slice into the warp's list.
