@@ -719,38 +719,48 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     // ---------------------------------------------------------------------------------------- penalty tables
     // bitmap of the slice's tokens that occur in the history, their ranks, and the occurrence count per rank
     if (has_pen) {
+        // this thread's share of the history, loaded once (8 ids per thread cover 2,048 ids; longer histories loop)
+        constexpr int HREG = 8;
+        int hv[HREG];
+#pragma unroll
+        for (int j = 0; j < HREG; ++j) { const int i = tid + j * CI_THREADS; hv[j] = i < hlen ? __ldg(hist + i) - slice_lo : -1; }
         for (int i = tid; i < nw; i += CI_THREADS) pen_bits[i] = 0u;
         for (int i = tid; i < CI_PEN_TABLE; i += CI_THREADS) pen_cnt[i] = 0u;
         __syncthreads();
-        for (int i = tid; i < hlen; i += CI_THREADS) {
-            const int v = hist[i] - slice_lo;
+#pragma unroll
+        for (int j = 0; j < HREG; ++j) if (hv[j] >= 0 && hv[j] < slice_len) atomicOr(&pen_bits[hv[j] >> 5], 1u << (hv[j] & 31));
+        for (int i = tid + HREG * CI_THREADS; i < hlen; i += CI_THREADS) {
+            const int v = __ldg(hist + i) - slice_lo;
             if (v >= 0 && v < slice_len) atomicOr(&pen_bits[v >> 5], 1u << (v & 31));
         }
         __syncthreads();
-        // exclusive prefix of popcounts over the bitmap words (block scan, contiguous words per thread)
-        {
+        if (fp != 0.0f) {
+            // ranks of the set bits (exclusive prefix of popcounts over the bitmap words), then the count per rank
             const int ipt = (nw + CI_THREADS - 1) / CI_THREADS;
             const int lo = tid * ipt;
             u64 local = 0;
             for (int i = lo; i < lo + ipt && i < nw; ++i) local += __popc(pen_bits[i]);
-            const u64 incl = warp_incl_scan_u64(local, lane);
-            if (lane == 31) sc->warp_tot[warp] = incl;
-            __syncthreads();
-            u64 off = 0;
-            for (int w = 0; w < warp; ++w) off += sc->warp_tot[w];
-            uint32_t run = (uint32_t)(off + incl - local);
+            u64 total_bits;
+            uint32_t run = (uint32_t)block_excl_scan(local, sc, total_bits);
             for (int i = lo; i < lo + ipt && i < nw; ++i) { pen_prefix[i] = run; run += __popc(pen_bits[i]); }
             __syncthreads();
-        }
-        for (int i = tid; i < hlen; i += CI_THREADS) {
-            const int v = hist[i] - slice_lo;
-            if (v >= 0 && v < slice_len) {
-                const uint32_t w = pen_bits[v >> 5];
-                const uint32_t rk = pen_prefix[v >> 5] + __popc(w & ((1u << (v & 31)) - 1u));
-                if (rk < CI_PEN_TABLE) atomicAdd(&pen_cnt[rk], 1u);
+#pragma unroll
+            for (int j = 0; j < HREG; ++j) {
+                const int v = hv[j];
+                if (v >= 0 && v < slice_len) {
+                    const uint32_t rk = pen_prefix[v >> 5] + __popc(pen_bits[v >> 5] & ((1u << (v & 31)) - 1u));
+                    if (rk < CI_PEN_TABLE) atomicAdd(&pen_cnt[rk], 1u);
+                }
             }
+            for (int i = tid + HREG * CI_THREADS; i < hlen; i += CI_THREADS) {
+                const int v = __ldg(hist + i) - slice_lo;
+                if (v >= 0 && v < slice_len) {
+                    const uint32_t rk = pen_prefix[v >> 5] + __popc(pen_bits[v >> 5] & ((1u << (v & 31)) - 1u));
+                    if (rk < CI_PEN_TABLE) atomicAdd(&pen_cnt[rk], 1u);
+                }
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
 
     CI_PROF(1);
@@ -761,71 +771,69 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     float tg[CI_TGROUPS];                                       // maxima of this thread's interleaved element groups
 #pragma unroll
     for (int j = 0; j < CI_TGROUPS; ++j) tg[j] = CI_NEG_INF;
-    const int n_pass_chunks = (n_pad + CI_CHUNK - 1) / CI_CHUNK;
-    for (int c = 0; c < n_pass_chunks; ++c) {
-        const int c_lo = c * CI_CHUNK;
-        const int c_len = min(CI_CHUNK, n_pad - c_lo);          // multiple of 128
-        if (c < nchunks) {
-            if (a.use_bulk) {
-                if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
-                CI_PROF(5);
-                if (a.prof && tid == 0 && c == nchunks - 1) { sc->prof[8] += clock64() - t_issue; sc->prof[9] += t_issue_end - t_issue; }
-            } else {
-                const int valid = min(CI_CHUNK, slice_len - c_lo);
-                const size_t g0 = (size_t)row * V + slice_lo + c_lo;
-                if (a.dtype == COLINFER_BF16) {
-                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.logits) + g0;
-                    if ((((uintptr_t)src) & 15) == 0) {
-                        const uint4* s4 = reinterpret_cast<const uint4*>(src);
-                        for (int i = tid; i * 8 < valid; i += CI_THREADS) {
-                            if (i * 8 + 8 <= valid) {
-                                const uint4 q = __ldg(s4 + i);
-                                const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
-                                float* d = rowbuf + c_lo + i * 8;
+    // (1) the slice lands: wait for the bulk copies, or load it with plain loads (unaligned fp32 rows, bf16)
+    if (a.use_bulk) {
+        for (int c = 0; c < nchunks; ++c)
+            if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
+        if (a.prof && tid == 0) { sc->prof[8] += clock64() - t_issue; sc->prof[9] += t_issue_end - t_issue; }
+    } else {
+        const size_t g0 = (size_t)row * V + slice_lo;
+        if (a.dtype == COLINFER_BF16) {
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.logits) + g0;
+            if ((((uintptr_t)src) & 15) == 0) {
+                const uint4* s4 = reinterpret_cast<const uint4*>(src);
+                for (int i = tid; i * 8 < slice_len; i += CI_THREADS) {
+                    if (i * 8 + 8 <= slice_len) {
+                        const uint4 q = __ldg(s4 + i);
+                        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+                        float* d = rowbuf + i * 8;
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    d[2 * j] = __uint_as_float(ww[j] << 16);
-                                    d[2 * j + 1] = __uint_as_float(ww[j] & 0xFFFF0000u);
-                                }
-                            } else {
-                                for (int j = i * 8; j < valid; ++j) rowbuf[c_lo + j] = __bfloat162float(src[j]);
-                            }
+                        for (int j = 0; j < 4; ++j) {
+                            d[2 * j] = __uint_as_float(ww[j] << 16);
+                            d[2 * j + 1] = __uint_as_float(ww[j] & 0xFFFF0000u);
                         }
                     } else {
-                        for (int i = tid; i < valid; i += CI_THREADS) rowbuf[c_lo + i] = __bfloat162float(src[i]);
+                        for (int j = i * 8; j < slice_len; ++j) rowbuf[j] = __bfloat162float(src[j]);
                     }
-                } else {
-                    const float* src = reinterpret_cast<const float*>(a.logits) + g0;
-                    for (int i = tid; i < valid; i += CI_THREADS) rowbuf[c_lo + i] = __ldg(src + i);
                 }
-                __syncthreads();
+            } else {
+                for (int i = tid; i < slice_len; i += CI_THREADS) rowbuf[i] = __bfloat162float(src[i]);
             }
+        } else {
+            const float* src = reinterpret_cast<const float*>(a.logits) + g0;
+            for (int i = tid; i < slice_len; i += CI_THREADS) rowbuf[i] = __ldg(src + i);
         }
-        if (has_pen) {
-            // one bitmap word (32 tokens) per thread
-            const int w0 = c_lo >> 5, wn = c_len >> 5;
-            for (int wi = tid; wi < wn; wi += CI_THREADS) {
-                const uint32_t word = pen_bits[w0 + wi];
-                uint32_t rest = word;
-                while (rest) {
-                    const int bit = __ffs(rest) - 1;
-                    rest &= rest - 1;
-                    const int v = ((w0 + wi) << 5) + bit;
-                    const uint32_t rk = pen_prefix[w0 + wi] + __popc(word & ((1u << bit) - 1u));
-                    int cnt;
+        __syncthreads();
+    }
+    CI_PROF(5);
+    // (2) penalties: one bitmap word (32 tokens) per thread and step
+    if (has_pen) {
+        const int wn = n_pad >> 5;
+        for (int wi = tid; wi < wn; wi += CI_THREADS) {
+            const uint32_t word = pen_bits[wi];
+            uint32_t rest = word;
+            while (rest) {
+                const int bit = __ffs(rest) - 1;
+                rest &= rest - 1;
+                const int v = (wi << 5) + bit;
+                int cnt = 1;
+                if (fp != 0.0f) {
+                    const uint32_t rk = pen_prefix[wi] + __popc(word & ((1u << bit) - 1u));
                     if (rk < CI_PEN_TABLE) cnt = (int)pen_cnt[rk];
                     else {
                         cnt = 0; sc->hist_slow = 1;
                         for (int i = 0; i < hlen; ++i) cnt += (hist[i] == v + slice_lo);
                     }
-                    rowbuf[v] = apply_penalty(rowbuf[v], cnt, rp, pp, fp);
                 }
+                rowbuf[v] = apply_penalty(rowbuf[v], cnt, rp, pp, fp);
             }
-            __syncthreads();
         }
-        // four float4 groups per thread and step, loaded together so that their latencies overlap
-        float4* row4 = reinterpret_cast<float4*>(rowbuf + c_lo);
-        const int n4 = c_len >> 2;
+        __syncthreads();
+    }
+    // (3) mask and maximum: four float4 groups per thread and step, loaded together so that their latencies overlap
+    {
+        float4* row4 = reinterpret_cast<float4*>(rowbuf);
+        const int n4 = n_pad >> 2;
         for (int i0 = tid; i0 < n4; i0 += CI_TGROUPS * CI_THREADS) {
             float4 v[CI_TGROUPS];
 #pragma unroll
@@ -837,7 +845,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 #pragma unroll
                 for (int k = 0; k < CI_TGROUPS; ++k) {
                     const int i = i0 + k * CI_THREADS;
-                    const int g = slice_lo + c_lo + i * 4;      // global token index of v[k].x
+                    const int g = slice_lo + i * 4;             // global token index of v[k].x
                     if (i < n4 && g < V) {
                         const uint32_t bits = ((uint32_t)__ldg(mrow + (g >> 5)) >> (g & 31)) & 0xFu;
                         if (bits != 0xFu) {
@@ -856,10 +864,9 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
                 tg[k] = fmaxf(tg[k], m4);
                 const bool up = m4 > lmax;                      // strict: the first (lowest) position of the maximum stays
                 lmax = up ? m4 : lmax;
-                lpos = up ? (c_lo >> 2) + i0 + k * CI_THREADS : lpos;
+                lpos = up ? i0 + k * CI_THREADS : lpos;
             }
         }
-        CI_PROF(2);
     }
     CI_PROF(2);
     if (lpos >= 0) {
