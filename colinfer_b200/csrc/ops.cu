@@ -116,6 +116,46 @@ extern "C" int colinfer_processed_probs(const float* logits, const float* temper
     return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------ processed_probs without caller scratch
+// For callers that cannot hand over scratch memory: a host that binds this C ABI directly (no torch caching allocator
+// behind it) and replays the call inside a captured CUDA graph, or runs under a fixed memory budget, has nowhere to
+// take the per-row statistics buffer from -- cudaMalloc is illegal during capture and forbidden by such hosts.  This
+// variant keeps the statistics in a fixed array that lives in the library's device image instead.
+#define COLINFER_NOALLOC_MAX_ROWS 4096
+static __device__ __align__(256) colinfer_row_stats g_noalloc_stats[COLINFER_NOALLOC_MAX_ROWS];   // 128 KB per device
+
+// Device address of g_noalloc_stats on the current device.  In host code the array's name is only a handle, never an
+// address a kernel may dereference: the address is asked for once per device, with that device current.
+static int noalloc_stats_ptr(colinfer_row_stats** out) {
+    static colinfer_row_stats* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_stats);
+        if (e != cudaSuccess) return (int)e;
+        cached[dev] = reinterpret_cast<colinfer_row_stats*>(p);
+    }
+    *out = cached[dev];
+    return 0;
+}
+
+extern "C" int colinfer_processed_probs_noalloc(const float* logits, const float* temperature, const int32_t* top_k,
+                                                const float* top_p, const float* log_min_p, float* out, int R, int V,
+                                                void* stream) {
+    if (R > COLINFER_NOALLOC_MAX_ROWS) return (int)cudaErrorInvalidValue;   // more rows than the fixed array holds
+    colinfer_row_stats* stats = nullptr;
+    const int e = noalloc_stats_ptr(&stats);
+    if (e) return e;
+    // Every row's entry is written by the statistics pass before the probability pass reads it: nothing in the array has
+    // to start at zero, and what an earlier call left behind is never read.
+    return colinfer_processed_probs(logits, temperature, top_k, top_p, log_min_p, out, stats, R, V, stream);
+}
+
+extern "C" int colinfer_noalloc_max_rows(void) { return COLINFER_NOALLOC_MAX_ROWS; }
+
 // ------------------------------------------------------------------------------------------------ inverse_cdf
 // One CTA per row.  Sums are float64 (the reference's fp32 scan order is device dependent; float64 is what its CPU
 // cumsum accumulates in).  Warp w owns a contiguous region, lanes interleave, so the index order is (warp, step, lane).

@@ -147,3 +147,24 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
     if status or stats:
         return (out,) + ((st,) if status else ()) + ((rs,) if stats else ())
     return out
+
+
+def processed_probs_noalloc(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                            log_min_p: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """processed_probs into a caller-provided `out` [R, V] without any allocation: the per-row scratch is a fixed array
+    inside the CUDA library (at most 4096 rows; calls that overlap on the GPU race on it).  For hosts that may not
+    allocate at call time; not part of the reference's interface."""
+    check_tensor(logits, torch.float32, "logits")
+    check_tensor(out, torch.float32, "out")
+    if logits.dim() != 2 or out.shape != logits.shape:
+        raise RuntimeError("logits, out [R, V]")
+    for t, dt, name in ((temperature, torch.float32, "temperature"), (top_k, torch.int32, "top_k"),
+                        (top_p, torch.float32, "top_p"), (log_min_p, torch.float32, "log_min_p")):
+        check_tensor(t, dt, name)
+        if t.numel() != 1:
+            raise RuntimeError(f"{name} must have 1 element")
+    R, V = logits.shape
+    _lib.check(_lib.lib().colinfer_processed_probs_noalloc(logits.data_ptr(), temperature.data_ptr(), top_k.data_ptr(),
+                                                           top_p.data_ptr(), log_min_p.data_ptr(), out.data_ptr(), R, V,
+                                                           _stream()), "processed_probs_noalloc")
+    return out

@@ -84,6 +84,21 @@ int colinfer_sample(const void* logits, int dtype, const int32_t* mask, int mask
 int colinfer_processed_probs(const float* logits, const float* temperature, const int32_t* top_k, const float* top_p,
                              const float* log_min_p, float* out, colinfer_row_stats* scratch, int R, int V, void* stream);
 
+/* colinfer_processed_probs for callers that have no scratch to give (no counterpart in the reference; added for hosts
+ * that bind this ABI without an allocator of their own -- e.g. one that replays the call from a captured CUDA graph or
+ * runs under a fixed memory budget, where cudaMalloc is illegal or forbidden).  The per-row statistics live in a
+ * fixed 128 KB array inside the library's device image, held by every GPU that loads the library until the process
+ * exits.  Same arguments and results as colinfer_processed_probs, minus `scratch`.
+ *   - R may not exceed colinfer_noalloc_max_rows() (4096): larger R returns cudaErrorInvalidValue, nothing is launched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call outside any stream capture.  No call allocates or frees device memory.
+ *   - All calls on a device share the one array: two calls that may overlap on the GPU (different streams, no
+ *     dependency between them) race on it.  Serialise them, or use colinfer_processed_probs with separate scratch.
+ *   - Nothing in the array needs clearing between calls: every entry a call reads it has written first. */
+int colinfer_processed_probs_noalloc(const float* logits, const float* temperature, const int32_t* top_k,
+                                     const float* top_p, const float* log_min_p, float* out, int R, int V, void* stream);
+int colinfer_noalloc_max_rows(void);
+
 /* Replaces inverse_cdf (engine/spec/accept.py:36-40): out[r] = #{ j : cumsum(P[r])_j < u[r] * sum(P[r]) }, clamped to
  * V - 1.  P [R, V] fp32, u [R], out [R] int64. */
 int colinfer_inverse_cdf(const float* P, const float* u, int64_t* out, int R, int V, void* stream);
