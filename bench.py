@@ -36,9 +36,9 @@ if ROOT not in sys.path:
 V = 151_936
 HIST = 2048
 CPU_SAMPLE_ROWS = 256
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_sample launch divided by its rows (ncu capture summarised in
-# profiles/k_sample_config3.md); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_ROW = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_sample launch divided by its rows (ncu capture at B = 256,
+# summarised in profiles/k_sample_config3_b256_ncu.md; traffic grows in proportion to the rows).
+NCU_TRAFFIC_BYTES_PER_ROW = 644_400
 
 
 def measured_peak():
@@ -60,7 +60,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
