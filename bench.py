@@ -93,6 +93,10 @@ def cpu_baseline_rows_per_s(w, reps: int, warm: int):
     """The reference's torch path on host cores over the first CPU_SAMPLE_ROWS rows of the batch."""
     import torch
     from oracle import torch_cpu_path as T
+    try:                                                   # every host core this process may use (launchers pin OMP to 1)
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        pass
     n = min(CPU_SAMPLE_ROWS, w["logits"].shape[0])
     sub = {k: (v[:n] if isinstance(v, torch.Tensor) else v) for k, v in w.items() if k != "params"}
     sub["params"] = {k: v[:n] for k, v in w["params"].items()}
