@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libcolinfer_b200.so")
 
 F32, BF16 = 0, 1
 FORCE_DISTRIBUTION = 1
-ROW_DEGENERATE, ROW_TIMEOUT, ROW_HIST_SLOW = 1, 2, 4
+ROW_DEGENERATE, ROW_TIMEOUT, ROW_HIST_SLOW, ROW_SELECT_SLOW = 1, 2, 4, 8
 
 
 class SamplerParamsC(C.Structure):

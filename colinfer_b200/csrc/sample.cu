@@ -1370,6 +1370,9 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 }
 
 // ------------------------------------------------------------------------------------------------ host side
+int colinfer_launch_stream(const void*, int, const int32_t*, int, int, const colinfer_sampler_params*, const void*, int, const float*,
+                           int64_t*, colinfer_row_stats*, int32_t*, int, int, int, int, cudaStream_t);
+
 static int g_cluster_override = 0;
 static long long* g_prof = nullptr;
 static int g_prof_slots = 0;
@@ -1401,6 +1404,8 @@ static int pick_geometry(int V, int dtype, const void* logits, colinfer_geometry
 extern "C" int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geometry* out) {
     return pick_geometry(V, dtype, logits, out) ? (int)cudaErrorInvalidValue : 0;
 }
+
+void colinfer_profile_buffer(long long** buf, int* slots) { *buf = g_prof; *slots = g_prof_slots; }
 
 extern "C" int colinfer_set_profile_buffer(void* dev, int ctas) {
     g_prof = reinterpret_cast<long long*>(dev);
@@ -1464,9 +1469,16 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     if (!params->temperature || !params->top_k || !params->top_p || !params->log_min_p) return (int)cudaErrorInvalidValue;
     if (out_ids && u == nullptr && (pos == nullptr || params->seed == nullptr)) return (int)cudaErrorInvalidValue;
     if (mask && (W < (V + 31) / 32 || mask_rows < R)) return (int)cudaErrorInvalidValue;
+    if ((long long)B * R > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    if (g_cluster_override == 0) {
+        // default: the streaming kernel (one CTA per row, passes over L2); the cluster-resident kernel below runs when
+        // colinfer_set_cluster_override selects a cluster size, or when the row's penalty bitmap would not fit
+        const int rc = colinfer_launch_stream(logits, dtype, mask, mask_rows, W, params, pos, pos_is_i64, u, out_ids, stats, status,
+                                              B, R, V, flags, (cudaStream_t)stream);
+        if (rc != (int)cudaErrorInvalidValue) return rc;
+    }
     colinfer_geometry g;
     if (pick_geometry(V, dtype, logits, &g)) return (int)cudaErrorInvalidValue;
-    if ((long long)B * R > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
     const int resident = active_clusters(g);
     if (resident <= 0) return (int)cudaErrorInvalidConfiguration;
     const long long clusters = (long long)B * R < resident ? (long long)B * R : resident;

@@ -1,0 +1,1136 @@
+// stream.cu -- the streaming form of the fused logits -> token kernel (sm_100a): one CTA per row.
+//
+// A persistent grid of one 1024-thread CTA per SM; each CTA owns one row at a time and streams it from global memory
+// with 128-bit loads in two to three passes: the first pass comes from HBM, the later ones hit the 126 MB L2 (at most
+// one row per SM is in flight: 148 x 608 KB = 90 MB).  No row is ever copied: penalties and the grammar mask are applied
+// on the fly in every pass (a bitmap of the history's tokens in shared memory marks the few logits to penalise).  All
+// reductions stay inside the CTA, so a row costs a handful of __syncthreads and no cluster traffic.
+//
+//   pass 1   maximum / argmax and four group maxima per thread
+//   greedy   done
+//   top_k <= 100   the k-th largest of the 4096 group maxima bounds the k-th largest logit from below; pass 2 collects
+//            the logits above the bound (in token order) and the row is finished exactly on that list
+//   larger top_k / top_p alone   pass 2 builds a 4096-bucket count histogram over the distance from the maximum (exact
+//            bucket of the k-th largest; estimated bucket of the top-p pivot); pass 3 sums the exact masses (top-p:
+//            above a narrow band, whose logits are gathered and resolved exactly); the draw rescans one warp's region
+//   neither  pass 2 sums the masses; the draw rescans one warp's region
+// Masses are exp(z - max) in integer units of 2^-30 and all sums are integer: results do not depend on the batch.
+// If a list overflows or the estimated band misses, an exact radix select over the 32-bit keys runs (4 more passes).
+#include "common.cuh"
+#include "../../include/colinfer_b200.h"
+
+namespace strm {
+
+#define ST_PROF(slot) do { if (a.prof && tid == 0) { const long long t_ = clock64(); sc->prof[slot] += t_ - prof_last; prof_last = t_; } } while (0)
+
+constexpr int NT = 1024;             // threads per CTA
+constexpr int NW = NT / 32;
+constexpr int NWA = 32;              // per-warp exchange arrays are sized (and reduced) for a full warp of warps
+constexpr int NB1 = 4096;            // fine buckets over the distance from the row maximum
+constexpr float RANGE = 25.0f;       // they cover distances up to RANGE * temperature
+constexpr int FASTK = 100;           // largest top_k finished from the group-maxima bound
+constexpr int BINS = 512;            // bins of the sample histogram and of the exact list selection
+constexpr float FAST_SCALE = 32.0f;  // sample-histogram bins per unit logit (16 units below the sample's maximum)
+constexpr float FIN_SCALE = 64.0f;   // list-selection bins per unit logit (8 units below the maximum)
+constexpr int WLIST = 64;            // list entries per warp
+constexpr int FCAP = 128;            // candidates of the one-warp finish
+constexpr int GLIST = 1365;          // gathered list entries
+constexpr int FIN_CAND = 64;         // entries of one bin compared pairwise
+constexpr int FB_NB = 256;           // radix buckets per level of the fallback select
+constexpr int PEN_TABLE = 2048;      // distinct history ids with an O(1) count
+#define ST_FLT_MAX 3.402823466e38f
+#define ST_POS_INF (__int_as_float(0x7f800000))
+
+struct Args {
+    const void* logits; int dtype; int vec;
+    const int32_t* mask; int mask_rows; int W;
+    colinfer_sampler_params p;
+    const void* pos; int pos_i64; const float* u;
+    int64_t* out; colinfer_row_stats* stats; int32_t* status;
+    int B, R, V; int flags;
+    long long* prof; int prof_slots;   // optional cycles per phase (profiling hook)
+};
+
+struct Cand { uint32_t idx; float l; };
+struct Entry { uint32_t idx; float l; uint32_t q; };
+
+struct Sc {
+    u64 wsum[NWA], woff[NWA], wtotal;
+    u64 wmass[NWA];
+    float wf[NWA]; int wi[NWA];
+    int found; u64 found_excl;
+    int ncand; float cand_l[FIN_CAND]; u64 cand_w[FIN_CAND]; float res_f; int sel_ok;
+    int hist_slow, overflow;
+    int wcount[NWA], woffs[NWA + 1];
+    float bc_f; int bc_i;
+    float wtw[NWA], wmin[NWA];     // running top-k: each warp's threshold and smallest list entry
+    float fin_lo; int fin_bstar, fin_n, fin_ok, fin_all;
+    uint32_t fc_idx[FCAP]; float fc_l[FCAP];
+    float fin_cut; u64 fin_total; int fin_token;
+    long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
+};
+
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+__device__ __forceinline__ int warp_id() { return threadIdx.x >> 5; }
+
+// Exclusive prefix of one value per thread (thread order) and the total.  Two __syncthreads.
+__device__ __forceinline__ u64 block_excl_scan(u64 v, Sc* sc, u64& total) {
+    const int lane = lane_id(), warp = warp_id();
+    const u64 incl = warp_incl_scan_u64(v, lane);
+    if (lane == 31) sc->wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const u64 w = sc->wsum[lane];
+        const u64 wi = warp_incl_scan_u64(w, lane);
+        sc->woff[lane] = wi - w;
+        if (lane == 31) sc->wtotal = wi;
+        if (lane == 0) sc->found = -1;
+    }
+    __syncthreads();
+    total = sc->wtotal;
+    return sc->woff[warp] + incl - v;
+}
+
+// Where the running sum of get(0..nbins-1) first reaches target: bin (-1 if never, or target 0), sum before it, total.
+// Three __syncthreads.  All threads call.
+template <class F>
+__device__ void bins_find(F get, int nbins, u64 target, Sc* sc, int& bin, u64& before, u64& total) {
+    const int per = (nbins + NT - 1) / NT;
+    const int lo = min(threadIdx.x * per, nbins), hi = min(lo + per, nbins);
+    u64 s = 0;
+    for (int i = lo; i < hi; ++i) s += (u64)get(i);
+    const u64 excl = block_excl_scan(s, sc, total);
+    if (excl < target && target <= excl + s) {
+        u64 run = excl;
+        for (int i = lo; i < hi; ++i) {
+            const u64 b = (u64)get(i);
+            if (run + b >= target) { sc->found = i; sc->found_excl = run; break; }
+            run += b;
+        }
+    }
+    __syncthreads();
+    bin = sc->found;
+    before = sc->found_excl;
+}
+
+__device__ __forceinline__ u64 ceil_target(float frac, u64 total) {
+    const double t = ceil((double)frac * (double)total);
+    u64 q = t <= 1.0 ? 1ull : (u64)t;
+    return q > total ? total : q;
+}
+
+__device__ __forceinline__ float row_uniform(const Args& a, int row, int b, int r) {
+    if (a.u != nullptr) return a.u[row];
+    if (a.pos != nullptr && a.p.seed != nullptr) {
+        const long long p0 = a.pos_i64 ? reinterpret_cast<const long long*>(a.pos)[b]
+                                       : (long long)reinterpret_cast<const int*>(a.pos)[b];
+        return u32_to_uniform(philox_word(philox_key(a.p.seed[b]), (u64)p0 + (u64)r));
+    }
+    return 1.0f;
+}
+
+__device__ __forceinline__ u64 bucket_mass_est(int b) {
+    return (u64)__float2uint_rn(exp2f(-((float)b + 0.5f) * (RANGE * CI_LOG2E / (float)NB1)) * CI_MASS_SCALE);
+}
+
+// Exact weighted selection among n list entries: the value v with W(l > v) < target <= W(l >= v).  BINS linear bins over
+// (base - l) * scale, then the pivot bin's entries pairwise.  False when the pivot leaves the binned range or its bin
+// is too crowded.  All threads call with the same arguments.
+template <class GL, class W>
+__device__ bool lean_select(GL getl, W wt, int n, float base, float scale, u64 target, u64* bins, Sc* sc, float& value) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < BINS; i += NT) bins[i] = 0;
+    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; }
+    __syncthreads();
+    for (int i = tid; i < n; i += NT) {
+        const u64 w = wt(i);
+        if (w) atomicAdd(&bins[max(0, min(BINS - 1, __float2int_rz((base - getl(i)) * scale)))], w);
+    }
+    __syncthreads();
+    int b_star; u64 before, total;
+    bins_find([&](int i) { return bins[i]; }, BINS, target, sc, b_star, before, total);
+    if (b_star < 0 || b_star >= BINS - 1) return false;
+    for (int i = tid; i < n; i += NT) {
+        const u64 w = wt(i);
+        if (w && max(0, min(BINS - 1, __float2int_rz((base - getl(i)) * scale))) == b_star) {
+            const int slot = atomicAdd(&sc->ncand, 1);
+            if (slot < FIN_CAND) { sc->cand_l[slot] = getl(i); sc->cand_w[slot] = w; }
+        }
+    }
+    __syncthreads();
+    const int nc = sc->ncand;
+    if (nc > FIN_CAND) return false;
+    if (tid < nc) {
+        const float mine = sc->cand_l[tid];
+        u64 gt = 0, eq = 0;
+        for (int i = 0; i < nc; ++i) {
+            const float o = sc->cand_l[i];
+            if (o > mine) gt += sc->cand_w[i]; else if (o == mine) eq += sc->cand_w[i];
+        }
+        if (before + gt < target && target <= before + gt + eq) { sc->res_f = mine; sc->sel_ok = 1; }
+    }
+    __syncthreads();
+    value = sc->res_f;
+    return sc->sel_ok != 0;
+}
+
+__device__ __forceinline__ float apply_penalty(float l, int cnt, float rp, float pp, float fp) {
+    l = l > 0.0f ? __fdiv_rn(l, rp) : __fmul_rn(l, rp);
+    l = __fsub_rn(l, __fmul_rn(fp, (float)cnt));
+    return __fsub_rn(l, pp);
+}
+
+// One row as the passes see it: effective logits (penalties, then mask), four at a time.
+struct Row {
+    const float* p32; const __nv_bfloat16* p16; int V; bool vec;
+    const int32_t* mrow;
+    bool has_pen; const uint32_t* pen_bits; const uint32_t* pen_prefix; const float* pen_val;
+    const int32_t* hist; int hlen; float rp, pp, fp; int* hist_slow;
+
+    // penalised value of a token beyond the table: count its occurrences by scanning the history
+    __device__ float slow_penalty(float l, int tok) const {
+        int cnt = 0;
+        *hist_slow = 1;
+        for (int h = 0; h < hlen; ++h) cnt += (hist[h] == tok);
+        return apply_penalty(l, cnt, rp, pp, fp);
+    }
+    __device__ __forceinline__ float raw(int t) const { return p16 ? __bfloat162float(p16[t]) : __ldg(p32 + t); }
+
+    // elements i .. i+3 (i a multiple of 4) as stored; positions >= V read as -inf.  A pure load: the passes issue
+    // several of these before touching the values, so that their latencies overlap.
+    __device__ __forceinline__ float4 raw4(int i) const {
+        float4 v;
+        if (vec) {
+            v = i < V ? __ldcg(reinterpret_cast<const float4*>(p32 + i)) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+        } else {
+            float e[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int t = i + j;
+                e[j] = t < V ? (p16 ? __bfloat162float(p16[t]) : __ldg(p32 + t)) : CI_NEG_INF;
+            }
+            v = make_float4(e[0], e[1], e[2], e[3]);
+        }
+        return v;
+    }
+    __device__ __forceinline__ float4 load4(int i) const { return fix4(raw4(i), i, V); }
+    // the effective logits of a loaded group: penalties, then mask.  Groups at or beyond lim (the end of the caller's
+    // region; at most V) keep the caller's filler values.
+    __device__ __forceinline__ float4 fix4(float4 v, int i, int lim) const {
+        if (has_pen && i < lim) {
+            // the few penalised logits of the row were computed once (pen_val, by rank of the token in the history bitmap)
+            const uint32_t word = pen_bits[i >> 5];
+            const uint32_t nib = (word >> (i & 31)) & 0xFu;
+            if (nib) {
+                uint32_t rk = pen_prefix[i >> 5] + __popc(word & ((1u << (i & 31)) - 1u));
+                if (nib & 1u) { if (rk < PEN_TABLE) v.x = pen_val[rk]; else v.x = slow_penalty(v.x, i); ++rk; }
+                if (nib & 2u) { if (rk < PEN_TABLE) v.y = pen_val[rk]; else v.y = slow_penalty(v.y, i + 1); ++rk; }
+                if (nib & 4u) { if (rk < PEN_TABLE) v.z = pen_val[rk]; else v.z = slow_penalty(v.z, i + 2); ++rk; }
+                if (nib & 8u) { if (rk < PEN_TABLE) v.w = pen_val[rk]; else v.w = slow_penalty(v.w, i + 3); }
+            }
+        }
+        if (mrow != nullptr && i < lim) {
+            const uint32_t bits = ((uint32_t)__ldg(mrow + (i >> 5)) >> (i & 31)) & 0xFu;
+            if (bits != 0xFu) {
+                if (!(bits & 1u)) v.x = CI_NEG_INF;
+                if (!(bits & 2u)) v.y = CI_NEG_INF;
+                if (!(bits & 4u)) v.z = CI_NEG_INF;
+                if (!(bits & 8u)) v.w = CI_NEG_INF;
+            }
+        }
+        return v;
+    }
+};
+
+// Appends the components of one float4 group selected by mk to the warp's list, in token order (lane, component).
+template <int CAP = WLIST>
+__device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, const float* e4, uint32_t idx0, int lane) {
+    const unsigned b0 = __ballot_sync(0xffffffffu, mk & 1u), b1 = __ballot_sync(0xffffffffu, mk & 2u);
+    const unsigned b2 = __ballot_sync(0xffffffffu, mk & 4u), b3 = __ballot_sync(0xffffffffu, mk & 8u);
+    if (!(b0 | b1 | b2 | b3)) return;
+    const unsigned lt = (1u << lane) - 1u;
+    int at = wn + __popc(b0 & lt) + __popc(b1 & lt) + __popc(b2 & lt) + __popc(b3 & lt);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (mk & (1u << j)) {
+            if (at < CAP) { mylist[at].idx = idx0 + j; mylist[at].l = e4[j]; }
+            ++at;
+        }
+    }
+    wn += __popc(b0) + __popc(b1) + __popc(b2) + __popc(b3);
+}
+
+// Concatenates the warps' lists (token order) into glist with masses; returns n, or -1 on overflow.  All threads call.
+__device__ int gather_lists(const Cand* ownlist, int wn, Entry* glist, const MassFn& mass, Sc* sc) {
+    const int lane = lane_id(), warp = warp_id();
+    if (lane == 0) sc->wcount[warp] = wn;
+    __syncthreads();
+    if (warp == 0) {
+        const int c = sc->wcount[lane];
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+        sc->woffs[lane] = incl - c;
+        if (lane == 31) sc->woffs[NWA] = incl;
+        const unsigned over = __ballot_sync(0xffffffffu, c > WLIST);
+        if (lane == 0) sc->overflow = over != 0u;
+    }
+    __syncthreads();
+    const int n = sc->woffs[NWA];
+    if (sc->overflow || n > GLIST) return -1;
+    const int off = sc->woffs[warp];
+    const Cand* src = ownlist + warp * WLIST;
+    for (int j = lane; j < wn; j += 32) {
+        Entry en;
+        en.idx = src[j].idx; en.l = src[j].l; en.q = mass(src[j].l);
+        glist[off + j] = en;
+    }
+    __syncthreads();
+    return n;
+}
+
+
+// Appends the selected components (mk[k], bit j) of a batch of four float4 groups to the warp's list in token order
+// (group, lane, component).  One packed shuffle scan gives every group's offsets.  The caller guarantees room.
+template <int CAP>
+__device__ __forceinline__ void warp_append_batch(Cand* mylist, int& wn, const unsigned (&mk)[4], const float4 (&v)[4], uint32_t idx0, int lane,
+                                                  unsigned packed_incl, unsigned packed_cnt) {
+    const unsigned tot = __shfl_sync(0xffffffffu, packed_incl, 31);
+    const unsigned excl = packed_incl - packed_cnt;
+    int base = wn;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (mk[k]) {
+            int at = base + (int)((excl >> (8 * k)) & 0xFFu);
+            const float e4[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (mk[k] & (1u << j)) {
+                    if (at < CAP) { mylist[at].idx = idx0 + k * 128 + j; mylist[at].l = e4[j]; }
+                    ++at;
+                }
+            }
+        }
+        base += (int)((tot >> (8 * k)) & 0xFFu);
+    }
+    wn = base;
+}
+
+// Top-k (kk <= FASTK), then top-p and the draw, from the warps' running lists after the single pass over the row.
+// The union of the lists holds every logit >= lo (lo: the largest warp threshold; the smallest listed value when no
+// warp compacted).  BINS linear bins over [lo, L] find the bin of the kk-th largest; the entries down to that bin, at
+// most FCAP and in token order, go to warp 0, which finishes exactly by bisection on the ordered keys.
+// False: the caller takes the general path.  All threads call.
+__device__ bool finish_running_topk(const Cand* ownlist, int wn, float tw, float L, float lcut_in, float tc, const MassFn& mass,
+                                    int kk, bool need_topp, float topp, float u, uint32_t* hist, Sc* sc,
+                                    long long& token, float& lcut, u64& total) {
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    const Cand* mine = ownlist + warp * WLIST;
+    // lo: valid lower bound of the kk-th largest, else the smallest listed value
+    float mn = ST_POS_INF;
+    const bool have_tw = tw > -ST_FLT_MAX;
+    if (!have_tw) for (int j = lane; j < wn; j += 32) mn = fminf(mn, mine[j].l);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    if (lane == 0) { sc->wtw[warp] = tw; sc->wmin[warp] = mn; sc->wcount[warp] = wn; }
+    for (int i = tid; i < BINS; i += NT) hist[i] = 0u;
+    __syncthreads();
+    if (warp == 0) {
+        float t = sc->wtw[lane], m2 = sc->wmin[lane];
+        int c = sc->wcount[lane];
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+            m2 = fminf(m2, __shfl_xor_sync(0xffffffffu, m2, o));
+            c += __shfl_xor_sync(0xffffffffu, c, o);
+        }
+        if (lane == 0) { sc->fin_lo = t > -ST_FLT_MAX ? t : m2; sc->fin_all = !(t > -ST_FLT_MAX); sc->fin_n = c; sc->fin_ok = 0; sc->fin_bstar = -1; }
+    }
+    __syncthreads();
+    const float lo = sc->fin_lo;
+    if (sc->fin_n < 1 || !(lo <= L)) return false;
+    const float scale = L > lo ? (float)(BINS - 2) / (L - lo) : 0.0f;
+    auto bin_of = [&](float l) { return min(BINS - 1, __float2int_rz((L - l) * scale)); };
+    for (int j = lane; j < wn; j += 32) { const float l = mine[j].l; if (l >= lo) atomicAdd(&hist[bin_of(l)], 1u); }
+    __syncthreads();
+    if (warp == 0) {
+        // bin where the running count reaches kk (or the last populated bin when fewer than kk are listed)
+        constexpr int PERB = BINS / 32;
+        uint32_t h[PERB]; uint32_t s = 0;
+#pragma unroll
+        for (int t = 0; t < PERB; ++t) { h[t] = hist[lane * PERB + t]; s += h[t]; }
+        uint32_t incl = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t x = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += x; }
+        const uint32_t all = __shfl_sync(0xffffffffu, incl, 31);
+        const uint32_t want = min((uint32_t)kk, all);
+        const unsigned hit = __ballot_sync(0xffffffffu, incl >= want);
+        if (want > 0 && lane == __ffs(hit) - 1) {
+            uint32_t run = incl - s; int b = lane * PERB;
+#pragma unroll
+            for (int t = 0; t < PERB; ++t) { if (run + h[t] >= want) { b = lane * PERB + t; run += h[t]; break; } run += h[t]; }
+            sc->fin_bstar = b; sc->fin_n = (int)run;                 // run: entries down to and including bin b
+        }
+    }
+    __syncthreads();
+    const int bstar = sc->fin_bstar, nc = sc->fin_n;
+    if (bstar < 0 || nc > FCAP) return false;
+    // every row element in bins <= bstar is a candidate: always when no warp dropped anything, else while bstar stays
+    // clear of the bins around lo
+    const bool complete = bstar <= BINS - 4 || sc->fin_all;
+    // candidates in token order: warps in order, entries in list order
+    {
+        int cnt = 0;
+        for (int j0 = 0; j0 < wn; j0 += 32) {
+            const int j = j0 + lane;
+            const bool is = j < wn && mine[j].l >= lo && bin_of(mine[j].l) <= bstar;
+            cnt += __popc(__ballot_sync(0xffffffffu, is));
+        }
+        if (lane == 0) sc->wcount[warp] = cnt;
+        __syncthreads();
+        int off = 0;
+        for (int w2 = 0; w2 < warp; ++w2) off += sc->wcount[w2];
+        const unsigned lt = (1u << lane) - 1u;
+        for (int j0 = 0; j0 < wn; j0 += 32) {
+            const int j = j0 + lane;
+            const bool is = j < wn && mine[j].l >= lo && bin_of(mine[j].l) <= bstar;
+            const unsigned bal = __ballot_sync(0xffffffffu, is);
+            if (is) { const int at = off + __popc(bal & lt); if (at < FCAP) { sc->fc_idx[at] = mine[j].idx; sc->fc_l[at] = mine[j].l; } }
+            off += __popc(bal);
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        constexpr int PERC = FCAP / 32;
+        float l[PERC]; uint32_t key[PERC], q[PERC];
+        int surv = 0;
+#pragma unroll
+        for (int t = 0; t < PERC; ++t) {
+            const int e = lane * PERC + t;
+            l[t] = e < nc ? sc->fc_l[e] : CI_NEG_INF;
+            key[t] = e < nc ? f2key(l[t]) : 0u;
+            surv += (e < nc && l[t] >= lcut_in) ? 1 : 0;
+        }
+        surv = (int)__reduce_add_sync(0xffffffffu, (unsigned)surv);
+        float cut = lcut_in;
+        bool ok = surv > 0;
+        if (ok && kk <= surv) {                                      // else fewer than k survive min-p: top-k removes nothing
+            uint32_t pre = 0;
+#pragma unroll 1
+            for (int bit = 31; bit >= 0; --bit) {
+                const uint32_t c = pre | (1u << bit);
+                int n = 0;
+#pragma unroll
+                for (int t = 0; t < PERC; ++t) n += key[t] >= c ? 1 : 0;
+                if ((int)__reduce_add_sync(0xffffffffu, (unsigned)n) >= kk) pre = c;
+            }
+            const float lk = key2f(pre);
+            const float ck = lower_logit_for(scale_logit(lk, tc), tc, lk);
+            ok = complete && ck >= lo && bin_of(ck) <= bstar;        // else a tie partner could lie outside the candidates
+            cut = fmaxf(cut, ck);
+        } else {
+            ok = ok && complete;                                     // every logit >= the min-p cut is a candidate
+        }
+#pragma unroll
+        for (int t = 0; t < PERC; ++t) q[t] = l[t] >= cut ? mass(l[t]) : 0u;
+        if (ok && need_topp) {
+            u64 s = 0;
+#pragma unroll
+            for (int t = 0; t < PERC; ++t) s += q[t];
+            const u64 s1 = warp_sum_u64(s);
+            ok = s1 > 0;
+            const u64 target = ceil_target(topp, s1);
+            uint32_t pre = 0;
+#pragma unroll 1
+            for (int bit = 31; bit >= 0; --bit) {
+                const uint32_t c = pre | (1u << bit);
+                u64 w = 0;
+#pragma unroll
+                for (int t = 0; t < PERC; ++t) w += key[t] >= c ? q[t] : 0u;
+                const u64 tot = ((u64)__reduce_add_sync(0xffffffffu, (unsigned)(w >> 24)) << 24) +
+                                __reduce_add_sync(0xffffffffu, (unsigned)(w & 0xFFFFFFu));
+                if (tot >= target) pre = c;
+            }
+            const float lp = key2f(pre);
+            cut = fmaxf(cut, lower_logit_for(scale_logit(lp, tc), tc, lp));
+#pragma unroll
+            for (int t = 0; t < PERC; ++t) q[t] = l[t] >= cut ? q[t] : 0u;
+        }
+        u64 s = 0;
+#pragma unroll
+        for (int t = 0; t < PERC; ++t) s += q[t];
+        const u64 incl = warp_incl_scan_u64(s, lane);
+        const u64 tot = __shfl_sync(0xffffffffu, incl, 31);
+        ok = ok && tot > 0;
+        const u64 target = ceil_target(u, tot);
+        const unsigned hit = __ballot_sync(0xffffffffu, incl >= target);
+        if (ok && lane == __ffs(hit) - 1) {
+            u64 run = incl - s; int e = lane * PERC;
+#pragma unroll
+            for (int t = 0; t < PERC; ++t) { run += q[t]; if (run >= target) { e = lane * PERC + t; break; } }
+            sc->fin_token = (int)sc->fc_idx[e]; sc->fin_cut = cut; sc->fin_total = tot; sc->fin_ok = 1;
+        }
+    }
+    __syncthreads();
+    if (!sc->fin_ok) return false;
+    token = sc->fin_token; lcut = sc->fin_cut; total = sc->fin_total;
+    return true;
+}
+
+}  // namespace strm
+
+namespace strm {
+
+// Top-k, top-p and the draw on a gathered list that holds every logit >= tl of the row (tl below the top-k pivot;
+// -inf when the list is known to contain the row's whole top k).  False: the caller takes another path.
+__device__ bool finish_on_list(const Entry* gl, int n, float tl, float lcut_in, float tc, float L, bool use_topk, int kk,
+                               bool need_topp, float topp, float u, u64* bins, Sc* sc, long long& token, float& lcut, u64& total) {
+    const int tid = threadIdx.x;
+    float cut = lcut_in;
+    const float span = (tl > -1e30f) ? fmaxf(L - tl, 1e-30f) : 0.0f;
+    const float scale = span > 0.0f ? (float)(BINS - 2) / span : FIN_SCALE;
+    auto getl = [&](int i) { return gl[i].l; };
+    u64 cnt = 0;
+    for (int i = tid; i < n; i += NT) cnt += gl[i].l >= cut ? 1 : 0;
+    u64 survivors;
+    block_excl_scan(cnt, sc, survivors);
+    if (survivors == 0) return false;
+    if (use_topk && (u64)kk <= survivors) {                    // else fewer than k survive min-p: top-k removes nothing
+        float lk;
+        const float c0 = cut;
+        if (!lean_select(getl, [&](int i) { return (u64)(gl[i].l >= c0 ? 1 : 0); }, n, L, scale, (u64)kk, bins, sc, lk)) return false;
+        cut = fmaxf(cut, lower_logit_for(scale_logit(lk, tc), tc, lk));
+        if (cut < tl) return false;                            // a tie partner could lie outside the list
+    }
+    if (need_topp) {
+        const float c0 = cut;
+        u64 part = 0;
+        for (int i = tid; i < n; i += NT) part += gl[i].l >= c0 ? (u64)gl[i].q : 0ull;
+        u64 s1;
+        block_excl_scan(part, sc, s1);
+        if (s1 == 0) return false;
+        float lp;
+        if (!lean_select(getl, [&](int i) { return gl[i].l >= c0 ? (u64)gl[i].q : 0ull; }, n, L, scale, ceil_target(topp, s1), bins, sc, lp))
+            return false;
+        cut = fmaxf(cut, lower_logit_for(scale_logit(lp, tc), tc, lp));
+        if (cut < tl) return false;
+    }
+    // the draw: first entry (token order) whose running kept mass reaches u * total
+    const int ept = (n + NT - 1) / NT;
+    const int e_lo = tid * ept, e_hi = min(e_lo + ept, n);
+    u64 mine = 0;
+    for (int i = e_lo; i < e_hi; ++i) mine += gl[i].l >= cut ? (u64)gl[i].q : 0ull;
+    const u64 excl = block_excl_scan(mine, sc, total);
+    if (total == 0) return false;
+    const u64 target = ceil_target(u, total);
+    if (tid == 0) sc->bc_i = -1;
+    __syncthreads();
+    if (excl < target && target <= excl + mine) {
+        u64 run = excl;
+        for (int i = e_lo; i < e_hi; ++i) {
+            run += gl[i].l >= cut ? (u64)gl[i].q : 0ull;
+            if (run >= target) { sc->bc_i = (int)gl[i].idx; break; }
+        }
+    }
+    __syncthreads();
+    token = sc->bc_i;
+    lcut = cut;
+    return token >= 0;
+}
+
+// Exact radix select over the order-preserving keys of the effective logits >= lcut (four 8-bit levels, one streaming
+// pass each).  by_mass: the top-p pivot; else the kk-th largest.  False when the filter removes nothing.
+__device__ bool radix_select(const Row& rw, int r_lo, int r_hi, const MassFn& mass, float lcut, bool by_mass, u64 kk, float topp,
+                             u64* fb_hist, Sc* sc, float& pivot) {
+    const int tid = threadIdx.x, lane = lane_id();
+    const float lk = fmaxf(lcut, -ST_FLT_MAX);
+    uint32_t prefix = 0;
+    u64 target = by_mass ? 0 : kk;
+    for (int lvl = 0; lvl < 4; ++lvl) {
+        const int shift = 24 - 8 * lvl;
+        for (int i = tid; i < FB_NB; i += NT) fb_hist[i] = 0;
+        __syncthreads();
+        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+            const float4 v = rw.load4(i0 + lane * 4);
+            const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float l = e4[j];
+                int bin = -1;
+                if (l >= lk) {
+                    const uint32_t key = f2key(l);
+                    if (lvl == 0 || (key >> (shift + 8)) == prefix) bin = FB_NB - 1 - (int)((key >> shift) & 0xFFu);
+                }
+                // lanes of one bin add once (most keys of a level share a few bins: plain atomics would serialise)
+                const unsigned peers = __match_any_sync(0xffffffffu, bin);
+                const uint32_t w = bin < 0 ? 0u : (by_mass ? mass(l) : 1u);
+                const uint32_t lo = __reduce_add_sync(peers, w & 0xFFFFu), hi = __reduce_add_sync(peers, w >> 16);
+                if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(&fb_hist[bin], ((u64)hi << 16) + lo);
+            }
+        }
+        __syncthreads();
+        int b_star; u64 before, grand;
+        if (lvl == 0) {
+            bins_find([&](int i) { return fb_hist[i]; }, FB_NB, 0, sc, b_star, before, grand);
+            if (by_mass) target = ceil_target(topp, grand);
+            else if (target >= grand) return false;
+            if (grand == 0) return false;
+        }
+        bins_find([&](int i) { return fb_hist[i]; }, FB_NB, target, sc, b_star, before, grand);
+        if (b_star < 0) return false;
+        target -= before;
+        prefix = (prefix << 8) | (uint32_t)(FB_NB - 1 - b_star);
+        __syncthreads();
+    }
+    pivot = key2f(prefix);
+    return true;
+}
+
+}  // namespace strm
+
+namespace strm {
+
+extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__ Args a) {
+    const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
+    const int V = a.V;
+    const int nw = (V + 31) >> 5;                                // bitmap words of a row
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint32_t* hist1 = reinterpret_cast<uint32_t*>(smem_raw);                  // [NB1] counts; [BINS] group-maxima counts
+    Entry* glist = reinterpret_cast<Entry*>(smem_raw);                        // gathered list, over hist1 (16 KB)
+    u64* bins = reinterpret_cast<u64*>(smem_raw + NB1 * 4);                   // [BINS] list-selection bins
+    u64* fb_hist = bins + BINS;                                               // [FB_NB] fallback radix
+    Cand* ownlist = reinterpret_cast<Cand*>(fb_hist + FB_NB);                 // [NW][WLIST]
+    Sc* sc = reinterpret_cast<Sc*>(ownlist + NW * WLIST);
+    uint32_t* pen_bits = reinterpret_cast<uint32_t*>(sc + 1);                 // [nw] tokens of the history
+    uint32_t* pen_prefix = pen_bits + nw;                                     // [nw] rank of each word's first set bit
+    uint32_t* pen_cnt = pen_prefix + nw;                                      // [PEN_TABLE] occurrences per rank
+    float* pen_val = reinterpret_cast<float*>(pen_cnt + PEN_TABLE);            // [PEN_TABLE] penalised logit per rank
+
+    // warp w owns the contiguous region [r_lo, r_hi) of the row; lanes interleave float4 groups: token order inside a
+    // region is (step, lane, component)
+    const int reg = (((V + 127) / 128 + NW - 1) / NW) * 128;
+    const int r_lo = min(warp * reg, V), r_hi = min(r_lo + reg, V);
+    Cand* mylist = ownlist + warp * WLIST;
+    const long long n_rows = (long long)a.B * a.R;
+    long long prof_last = clock64();
+    if (a.prof && tid == 0) for (int i = 0; i < 16; ++i) sc->prof[i] = 0;
+    if (tid < NWA) {                                             // neutral values for the warps a smaller CTA does not have
+        sc->wsum[tid] = 0; sc->wmass[tid] = 0; sc->wf[tid] = CI_NEG_INF; sc->wi[tid] = 0x7fffffff; sc->wcount[tid] = 0;
+        sc->wtw[tid] = -ST_FLT_MAX; sc->wmin[tid] = ST_POS_INF;
+    }
+    __syncthreads();
+    for (long long row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        __syncthreads();                                         // the previous row's shared tables are free
+        ST_PROF(0);
+        const int b = (int)(row / a.R), r = (int)(row % a.R);
+        // ------------------------------------------------------------------------------------ parameters of the slot
+        const float T = a.p.temperature[b];
+        const bool sampled = (T > 0.0f) || (a.flags & COLINFER_FORCE_DISTRIBUTION);
+        const float tc = fmaxf(T, 1e-6f);
+        const int kk = a.p.top_k[b];
+        const float topp = a.p.top_p[b];
+        const float log_min_p = a.p.log_min_p[b];
+        Row rw;
+        rw.V = V; rw.vec = a.vec != 0;
+        rw.p32 = a.dtype == COLINFER_F32 ? reinterpret_cast<const float*>(a.logits) + (size_t)row * V : nullptr;
+        rw.p16 = a.dtype == COLINFER_BF16 ? reinterpret_cast<const __nv_bfloat16*>(a.logits) + (size_t)row * V : nullptr;
+        rw.mrow = a.mask ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
+        rw.rp = a.p.repetition_penalty ? a.p.repetition_penalty[b] : 1.0f;
+        rw.pp = a.p.presence_penalty ? a.p.presence_penalty[b] : 0.0f;
+        rw.fp = a.p.frequency_penalty ? a.p.frequency_penalty[b] : 0.0f;
+        rw.hist = a.p.history ? a.p.history + (size_t)b * a.p.hist_stride : nullptr;
+        int hlen = rw.hist ? (a.p.hist_len ? a.p.hist_len[b] : a.p.hist_stride) : 0;
+        hlen = max(0, min(hlen, a.p.hist_stride));
+        rw.hlen = hlen;
+        rw.has_pen = hlen > 0 && !(rw.rp == 1.0f && rw.pp == 0.0f && rw.fp == 0.0f);
+        rw.pen_bits = pen_bits; rw.pen_prefix = pen_prefix; rw.pen_val = pen_val; rw.hist_slow = &sc->hist_slow;
+        if (tid == 0) sc->hist_slow = 0;
+
+        // ------------------------------------------------------------------------------------ penalty tables (whole row)
+        if (rw.has_pen) {
+            for (int i = tid; i < nw; i += NT) pen_bits[i] = 0u;
+            for (int i = tid; i < PEN_TABLE; i += NT) pen_cnt[i] = 0u;
+            __syncthreads();
+            for (int i = tid; i < hlen; i += NT) {
+                const int v = __ldg(rw.hist + i);
+                if (v >= 0 && v < V) atomicOr(&pen_bits[v >> 5], 1u << (v & 31));
+            }
+            __syncthreads();
+            {
+                // ranks of the set bits (exclusive prefix of popcounts over the bitmap words)
+                const int ipt = (nw + NT - 1) / NT;
+                const int lo = min(tid * ipt, nw), hi = min(lo + ipt, nw);
+                u64 local = 0;
+                for (int i = lo; i < hi; ++i) local += __popc(pen_bits[i]);
+                u64 total_bits;
+                uint32_t run = (uint32_t)block_excl_scan(local, sc, total_bits);
+                for (int i = lo; i < hi; ++i) { pen_prefix[i] = run; run += __popc(pen_bits[i]); }
+                __syncthreads();
+                if (rw.fp != 0.0f) {                              // occurrences per rank
+                    for (int i = tid; i < hlen; i += NT) {
+                        const int v = __ldg(rw.hist + i);
+                        if (v >= 0 && v < V) {
+                            const uint32_t rk = pen_prefix[v >> 5] + __popc(pen_bits[v >> 5] & ((1u << (v & 31)) - 1u));
+                            if (rk < PEN_TABLE) atomicAdd(&pen_cnt[rk], 1u);
+                        }
+                    }
+                    __syncthreads();
+                }
+                // the penalised logit of every marked token, once per row
+                for (int wi = tid; wi < nw; wi += NT) {
+                    uint32_t rest = pen_bits[wi];
+                    uint32_t rk = pen_prefix[wi];
+                    while (rest) {
+                        const int bit = __ffs(rest) - 1;
+                        rest &= rest - 1;
+                        if (rk < PEN_TABLE) {
+                            const int tok = (wi << 5) + bit;
+                            const int cnt = rw.fp != 0.0f ? (int)pen_cnt[rk] : 1;
+                            pen_val[rk] = apply_penalty(rw.raw(tok), cnt, rw.rp, rw.pp, rw.fp);
+                        }
+                        ++rk;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        ST_PROF(1);
+
+        // ------------------------------------------------------------------------------------ pass 1: maximum, argmax; running top-k lists
+        // Small top_k: each warp lists the logits of its region that are >= its own threshold -- the kk-th largest it
+        // has seen, raised whenever the list fills -- so that the lists together always hold the row's top kk.
+        const bool fastk = sampled && kk > 0 && kk <= FASTK && kk < V;
+        float lmax = CI_NEG_INF;
+        int lpos = -1, lidx = 0x7fffffff;
+        float tw = -ST_FLT_MAX;
+        int wn1 = 0, fk_bad = 0;
+#define ST_LOAD_BATCH(v, i0)                                                                                              \
+    _Pragma("unroll") for (int k = 0; k < 4; ++k) {                                                                       \
+        const int i = (i0) + k * 128 + lane * 4;                                                                          \
+        v[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);                       \
+    }                                                                                                                     \
+    _Pragma("unroll") for (int k = 0; k < 4; ++k) v[k] = rw.fix4(v[k], (i0) + k * 128 + lane * 4, r_hi);
+#define ST_TRACK_MAX(v, i0)                                                                                               \
+    _Pragma("unroll") for (int k = 0; k < 4; ++k) {                                                                       \
+        const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));                                             \
+        const bool up = m4 > lmax;               /* strict: the first (lowest) position of the maximum stays */            \
+        lmax = up ? m4 : lmax;                                                                                            \
+        lpos = up ? (i0) + k * 128 + lane * 4 : lpos;                                                                     \
+    }
+        if (!fastk) {
+            for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                float4 v[4];
+                ST_LOAD_BATCH(v, i0)
+                ST_TRACK_MAX(v, i0)
+            }
+        } else {
+            // The first batch of every warp (a tenth of the row at 151,936 logits) bounds the row's kk-th largest logit
+            // from below: the kk-th largest of the sample's float4 maxima.  The pass then lists what reaches the bound.
+            float gm[4];
+            {
+                float4 v[4];
+                ST_LOAD_BATCH(v, r_lo)
+                ST_TRACK_MAX(v, r_lo)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) gm[k] = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
+            }
+            float sm = lmax;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) sm = fmaxf(sm, __shfl_xor_sync(0xffffffffu, sm, o));
+            if (lane == 0) sc->wf[warp] = sm;
+            for (int i = tid; i < BINS; i += NT) hist1[i] = 0u;
+            __syncthreads();
+            float lref = sc->wf[lane];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) lref = fmaxf(lref, __shfl_xor_sync(0xffffffffu, lref, o));
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (gm[k] > CI_NEG_INF && lref < ST_POS_INF) atomicAdd(&hist1[min(BINS - 1, __float2int_rz((lref - gm[k]) * FAST_SCALE))], 1u);
+            __syncthreads();
+            int bk; u64 before, have;
+            bins_find([&](int i) { return (u64)hist1[i]; }, BINS, (u64)kk, sc, bk, before, have);
+            if (have >= (u64)kk && bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
+            for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                float4 v[4];
+                ST_LOAD_BATCH(v, i0)
+                ST_TRACK_MAX(v, i0)
+                unsigned mk[4], anym = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    mk[k] = (v[k].x >= tw ? 1u : 0u) | (v[k].y >= tw ? 2u : 0u) | (v[k].z >= tw ? 4u : 0u) | (v[k].w >= tw ? 8u : 0u);
+                    anym |= mk[k];
+                }
+                if (__ballot_sync(0xffffffffu, anym != 0u)) {
+                    // per-lane counts of the four groups, one byte each (a group holds at most 128: no carry)
+                    const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
+                    unsigned incl = cnt;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+                    warp_append_batch<WLIST>(mylist, wn1, mk, v, (uint32_t)(i0 + lane * 4), lane, incl, cnt);
+                }
+            }
+            if (wn1 > WLIST) fk_bad = 1;                         // a list overflowed (its tail was dropped): general path
+        }
+        ST_PROF(2);
+        if (lpos >= 0) {
+            const float4 v = rw.load4(lpos);
+            lidx = lpos + (v.x == lmax ? 0 : v.y == lmax ? 1 : v.z == lmax ? 2 : 3);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, lmax, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, lidx, o);
+            if (om > lmax || (om == lmax && oi < lidx)) { lmax = om; lidx = oi; }
+        }
+        if (lane == 0) { sc->wf[warp] = lmax; sc->wi[warp] = lidx; }
+        __syncthreads();
+        if (warp == 0) {
+            float bm = sc->wf[lane]; int bi = sc->wi[lane];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                const float om = __shfl_xor_sync(0xffffffffu, bm, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (om > bm || (om == bm && oi < bi)) { bm = om; bi = oi; }
+            }
+            if (lane == 0) { sc->bc_f = bm; sc->bc_i = bi; }
+        }
+        __syncthreads();
+        const float L = sc->bc_f;
+        int aidx = sc->bc_i;
+        if (aidx == 0x7fffffff) aidx = 0;
+        __syncthreads();
+        ST_PROF(3);
+
+        int status = 0;
+        const bool finite_max = (L > CI_NEG_INF) && (L < ST_POS_INF);
+        if (sampled && !finite_max) status |= COLINFER_ROW_DEGENERATE;
+        float lcut = CI_NEG_INF;
+        u64 total_mass = 0;
+        long long token = aidx;
+
+        if (sampled && finite_max) {
+            const float m = scale_logit(L, tc);
+            MassFn mass;
+            mass.init(tc, m);
+            const float thr = __fadd_rn(m, log_min_p);
+            lcut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
+            bool need_topk = kk > 0 && kk < V;
+            const bool need_topp = topp < 1.0f;
+            const float u = row_uniform(a, (int)row, b, r);
+            bool done = false;
+
+            // -------------------------------------------------------------------------------- small top-k: finish from the running lists
+            if (fastk) {
+                ST_PROF(4);
+                if (!__syncthreads_or(fk_bad) &&
+                    finish_running_topk(ownlist, wn1, tw, L, lcut, tc, mass, kk, need_topp, topp, u, hist1, sc, token, lcut, total_mass))
+                    done = true;
+                __syncthreads();
+                ST_PROF(7);
+            }
+
+            if (!done) {
+                enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
+                int path = PATH_PURE;
+                float t_hi = CI_NEG_INF, t_lo = ST_POS_INF;
+                const float SC1 = (float)NB1 / (RANGE * tc);
+                if (need_topk || need_topp) {
+                    // ------------------------------------------------------------------------ pass 2: fine count histogram
+                    const float lk = fmaxf(lcut, -ST_FLT_MAX);
+                    for (int i = tid; i < NB1; i += NT) hist1[i] = 0u;
+                    __syncthreads();
+                    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                        float e[16];
+                        float4 v4[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = i0 + k * 128 + lane * 4;
+                            v4[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float4 v = rw.fix4(v4[k], i0 + k * 128 + lane * 4, r_hi);
+                            e[4 * k] = v.x; e[4 * k + 1] = v.y; e[4 * k + 2] = v.z; e[4 * k + 3] = v.w;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (e[j] >= lk) atomicAdd(&hist1[min(NB1 - 1, __float2int_rz((L - e[j]) * SC1))], 1u);
+                    }
+                    __syncthreads();
+                    ST_PROF(8);
+                    int bsel; u64 before, survivors;
+                    bins_find([&](int i) { return (u64)hist1[i]; }, NB1, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
+                    if (need_topk && (u64)kk >= survivors) need_topk = false;   // fewer survivors than k: top-k removes nothing
+                    if (need_topk) {
+                        const u64 n_upto = bsel >= 0 ? before + hist1[bsel] : (u64)GLIST + 1;
+                        if (bsel < 0 || bsel >= NB1 - 3 || n_upto > GLIST - 64) path = PATH_FALLBACK;
+                        else {
+                            path = PATH_LIST;
+                            t_lo = L - ((float)(bsel + 2) + 0.01f) / SC1 - fabsf(L) * 1e-6f;
+                        }
+                    } else if (need_topp) {
+                        int bp; u64 bef, est_total;
+                        bins_find([&](int i) { return (u64)hist1[i] * bucket_mass_est(i); }, NB1, 0, sc, bp, bef, est_total);
+                        if (est_total == 0) path = PATH_FALLBACK;
+                        else {
+                            bins_find([&](int i) { return (u64)hist1[i] * bucket_mass_est(i); }, NB1, ceil_target(topp, est_total), sc, bp, bef, est_total);
+                            const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
+                            // how far down the list capacity reaches: bucket where the cumulative count gets there
+                            int bcap; u64 bef2, tot2;
+                            bins_find([&](int i) { return (u64)hist1[i]; }, NB1, (u64)768, sc, bcap, bef2, tot2);   // ~24 per warp list of 64
+                            if (bp < 0) path = PATH_FALLBACK;
+                            else if (bcap < 0 || bcap > bp + dn + 1) {
+                                // small nucleus: gather everything down to well below the estimated pivot; nothing is "above"
+                                path = PATH_BAND;
+                                t_hi = ST_POS_INF;
+                                t_lo = bcap < 0 ? -ST_FLT_MAX : L - (float)bcap / SC1;
+                            } else if (bp + dn + 2 >= NB1) path = PATH_FALLBACK;
+                            else {
+                                path = PATH_BAND;
+                                t_hi = bp - up <= 0 ? ST_POS_INF : L - (float)(bp - up) / SC1;
+                                t_lo = L - (float)(bp + dn + 1) / SC1;
+                            }
+                        }
+                    }
+                    __syncthreads();
+                    ST_PROF(9);
+                }
+
+                // ---------------------------------------------------------------------------- large top-k (then top-p) on a gathered list
+                if (path == PATH_LIST) {
+                    const float tl = fmaxf(fmaxf(t_lo, lcut), -ST_FLT_MAX);
+                    int wn = 0;
+                    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                        float4 v[4];
+                        unsigned mk[4], anym = 0;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = i0 + k * 128 + lane * 4;
+                            v[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+                            }
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                            v[k] = rw.fix4(v[k], i0 + k * 128 + lane * 4, r_hi);
+                            mk[k] = (v[k].x >= tl ? 1u : 0u) | (v[k].y >= tl ? 2u : 0u) | (v[k].z >= tl ? 4u : 0u) | (v[k].w >= tl ? 8u : 0u);
+                            anym |= mk[k];
+                        }
+                        if (__ballot_sync(0xffffffffu, anym != 0u)) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float e4[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                                warp_append(mylist, wn, mk[k], e4, (uint32_t)(i0 + k * 128 + lane * 4), lane);
+                            }
+                        }
+                    }
+                    __syncthreads();
+                    const int n = gather_lists(ownlist, wn, glist, mass, sc);
+                    if (n > 0 && finish_on_list(glist, n, tl, lcut, tc, L, true, kk, need_topp, topp, u, bins, sc, token, lcut, total_mass)) done = true;
+                    else path = PATH_FALLBACK;
+                    __syncthreads();
+                    ST_PROF(10);
+                }
+
+                // ---------------------------------------------------------------------------- fallback: exact radix select over the keys
+                if (path == PATH_FALLBACK) {
+                    status |= COLINFER_ROW_SELECT_SLOW;
+                    float lpiv;
+                    if (kk > 0 && kk < V && radix_select(rw, r_lo, r_hi, mass, lcut, false, (u64)kk, topp, fb_hist, sc, lpiv))
+                        lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+                    if (need_topp && radix_select(rw, r_lo, r_hi, mass, lcut, true, 0, topp, fb_hist, sc, lpiv))
+                        lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+                    path = PATH_PURE;
+                    t_hi = CI_NEG_INF; t_lo = ST_POS_INF;
+                }
+
+                // ---------------------------------------------------------------------------- mass pass and inverse CDF over the row
+                if (!done) {
+                    const bool band = path == PATH_BAND;
+                    const float lk = fmaxf(lcut, -ST_FLT_MAX);
+                    u64 acc_all = 0, acc_above = 0;
+                    int wn = 0;
+                    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                        float e[16];
+                        float4 v4[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int i = i0 + k * 128 + lane * 4;
+                            v4[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float4 v = rw.fix4(v4[k], i0 + k * 128 + lane * 4, r_hi);
+                            e[4 * k] = v.x; e[4 * k + 1] = v.y; e[4 * k + 2] = v.z; e[4 * k + 3] = v.w;
+                        }
+                        uint32_t q[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) q[j] = e[j] >= lk ? mass(e[j]) : 0u;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) acc_all += (u64)q[j] + q[j + 1];
+                        if (band) {
+                            unsigned mk[4], anym = 0;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                mk[k] = 0;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float x = e[4 * k + j];
+                                    if (x > t_hi) acc_above += q[4 * k + j];
+                                    else if (x >= t_lo && x >= lk) mk[k] |= 1u << j;
+                                }
+                                anym |= mk[k];
+                            }
+                            if (__ballot_sync(0xffffffffu, anym != 0u)) {
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) warp_append(mylist, wn, mk[k], &e[4 * k], (uint32_t)(i0 + k * 128 + lane * 4), lane);
+                            }
+                        }
+                    }
+                    ST_PROF(11);
+                    u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
+                    if (band) {
+                        const u64 wall = warp_sum_u64(acc_all);
+                        u64 s1, s_above;
+                        block_excl_scan(lane == 0 ? wall : 0ull, sc, s1);
+                        block_excl_scan(lane == 0 ? wkeep : 0ull, sc, s_above);
+                        const int n = gather_lists(ownlist, wn, glist, mass, sc);
+                        bool ok = n >= 0 && s1 > 0;
+                        float cut2 = lcut;
+                        if (ok) {
+                            u64 part = 0;
+                            for (int i = tid; i < n; i += NT) part += glist[i].q;
+                            u64 s_band;
+                            block_excl_scan(part, sc, s_band);
+                            const u64 target = ceil_target(topp, s1);
+                            ok = s_above < target && target <= s_above + s_band;   // the pivot lies inside the band
+                            if (ok) {
+                                const float base = t_hi < ST_POS_INF ? t_hi : L;
+                                const float scale = (float)(BINS - 2) / fmaxf(base - t_lo, 1e-30f);
+                                float lp;
+                                ok = lean_select([&](int i) { return glist[i].l; }, [&](int i) { return (u64)glist[i].q; }, n, base, scale,
+                                                 target - s_above, bins, sc, lp);
+                                if (ok) {
+                                    cut2 = fmaxf(lcut, lower_logit_for(scale_logit(lp, tc), tc, lp));
+                                    if (cut2 < t_lo) ok = false;          // a tie partner could lie below the band
+                                }
+                            }
+                        }
+                        if (ok) {
+                            lcut = cut2;
+                            u64 add = 0;
+                            const int mine = min(wn, WLIST);
+                            for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mass(mylist[j].l);
+                            wkeep += warp_sum_u64(add);
+                        } else {
+                            // the estimated band missed the pivot (or a list overflowed): exact radix select by mass, then the
+                            // regions' kept masses again
+                            float lpiv;
+                            status |= COLINFER_ROW_SELECT_SLOW;
+                            if (radix_select(rw, r_lo, r_hi, mass, lcut, true, 0, topp, fb_hist, sc, lpiv))
+                                lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
+                            const float lk3 = fmaxf(lcut, -ST_FLT_MAX);
+                            u64 acc = 0;
+                            for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                                const float4 v = rw.load4(i0 + lane * 4);
+                                acc += (u64)(v.x >= lk3 ? mass(v.x) : 0u) + (v.y >= lk3 ? mass(v.y) : 0u);
+                                acc += (u64)(v.z >= lk3 ? mass(v.z) : 0u) + (v.w >= lk3 ? mass(v.w) : 0u);
+                            }
+                            wkeep = warp_sum_u64(acc);
+                        }
+                    }
+                    ST_PROF(12);
+                    const u64 woff = __shfl_sync(0xffffffffu, block_excl_scan(lane == 0 ? wkeep : 0ull, sc, total_mass), 0);
+                    const u64 target = ceil_target(u, total_mass);
+                    token = -1;
+                    if (total_mass > 0 && woff < target && target <= woff + wkeep) {
+                        const float lkf = fmaxf(lcut, -ST_FLT_MAX);
+                        u64 run = woff;
+                        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                            const int i = i0 + lane * 4;
+                            const float4 v = rw.load4(i);
+                            u64 q4[4];
+                            q4[0] = v.x >= lkf ? mass(v.x) : 0u; q4[1] = v.y >= lkf ? mass(v.y) : 0u;
+                            q4[2] = v.z >= lkf ? mass(v.z) : 0u; q4[3] = v.w >= lkf ? mass(v.w) : 0u;
+                            const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
+                            const u64 incl = warp_incl_scan_u64(s4, lane);
+                            const u64 grp = __shfl_sync(0xffffffffu, incl, 31);
+                            if (run + grp >= target) {
+                                const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
+                                if (lane == __ffs(hit) - 1) {
+                                    u64 c = run + incl - s4;
+                                    int j = 0;
+                                    for (; j < 3; ++j) { c += q4[j]; if (c >= target) break; }
+                                    if (a.out) a.out[row] = (long long)(i + j);
+                                }
+                                break;
+                            }
+                            run += grp;
+                        }
+                    }
+                    if (total_mass == 0) { status |= COLINFER_ROW_DEGENERATE; token = aidx; }
+                }
+            }
+        }
+        __syncthreads();
+        ST_PROF(13);
+        if (tid == 0) {
+            if (sc->hist_slow) status |= COLINFER_ROW_HIST_SLOW;
+            if (token >= 0 && a.out) a.out[row] = token;          // greedy, list-path or degenerate rows
+            if (a.status) a.status[row] = status;
+            if (a.stats) {
+                colinfer_row_stats st;
+                st.lmax = L; st.lcut = lcut; st.tc = tc; st.status = status; st.argmax = aidx; st.mass_q = total_mass;
+                a.stats[row] = st;
+            }
+        }
+    }
+    if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots)
+        for (int i = 0; i < 16; ++i) a.prof[(size_t)blockIdx.x * 16 + i] = sc->prof[i];
+}
+
+}  // namespace strm
+
+// ------------------------------------------------------------------------------------------------ host side
+static int stream_smem_bytes(int V) {
+    const int nw = (V + 31) / 32;
+    return strm::NB1 * 4 + strm::BINS * 8 + strm::FB_NB * 8 + strm::NW * strm::WLIST * (int)sizeof(strm::Cand) +
+           (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 8 + 256;
+}
+
+void colinfer_profile_buffer(long long** buf, int* slots);   // sample.cu: the buffer colinfer_set_profile_buffer registered
+
+// Launches the streaming kernel; returns cudaErrorInvalidValue when the vocabulary's penalty bitmap does not fit.
+int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, int mask_rows, int W,
+                           const colinfer_sampler_params* params, const void* pos, int pos_is_i64, const float* u,
+                           int64_t* out_ids, colinfer_row_stats* stats, int32_t* status, int B, int R, int V, int flags,
+                           cudaStream_t stream) {
+    const int smem = stream_smem_bytes(V);
+    if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
+    const bool vec = dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)logits) & 15) == 0;
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (sm_count[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        sm_count[dev] = n > 0 ? n : 1;
+    }
+    strm::Args a;
+    a.logits = logits; a.dtype = dtype;
+    a.vec = vec ? 1 : 0;
+    a.mask = mask; a.mask_rows = mask_rows; a.W = W;
+    a.p = *params;
+    a.pos = pos; a.pos_i64 = pos_is_i64; a.u = u;
+    a.out = out_ids; a.stats = stats; a.status = status;
+    a.B = B; a.R = R; a.V = V; a.flags = flags;
+    colinfer_profile_buffer(&a.prof, &a.prof_slots);
+    e = cudaFuncSetAttribute(strm::k_sample_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    const long long rows = (long long)B * R;
+    const int grid = (int)(rows < sm_count[dev] ? rows : sm_count[dev]);
+    strm::k_sample_stream<<<grid, strm::NT, smem, stream>>>(a);
+    return (int)cudaGetLastError();
+}

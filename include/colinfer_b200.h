@@ -48,7 +48,9 @@ typedef struct colinfer_row_stats {
 enum {
     COLINFER_ROW_DEGENERATE = 1,  /* no finite maximum (every token masked, or an infinite logit): argmax emitted */
     COLINFER_ROW_TIMEOUT    = 2,  /* a bounded on-chip wait gave up; the row's outputs are undefined */
-    COLINFER_ROW_HIST_SLOW  = 4   /* more distinct history ids in one vocabulary slice than the fast table holds */
+    COLINFER_ROW_HIST_SLOW  = 4,  /* more distinct history ids than the fast table holds: same result, slower */
+    COLINFER_ROW_SELECT_SLOW = 8  /* a candidate list overflowed or the estimated band missed the pivot: the exact radix
+                                     select ran instead; same result, slower */
 };
 
 enum { COLINFER_F32 = 0, COLINFER_BF16 = 1 };

@@ -76,7 +76,7 @@ def run_workload(w, V, cluster=0, use_philox=False):
                         history=None if hist is None else hist.numpy(),
                         hist_len=None if hist is None else w["params"]["hist_len"].numpy(),
                         u=None if (u is None or use_philox) else u.numpy())
-    assert (st.cpu().numpy() & ~_lib.ROW_HIST_SLOW == 0).all(), st.unique()
+    assert (st.cpu().numpy() & ~(_lib.ROW_HIST_SLOW | _lib.ROW_SELECT_SLOW) == 0).all(), st.unique()
     nb = check_tokens(out.cpu().numpy(), want, info, w.get("name", ""))
     return nb, out
 
@@ -232,11 +232,12 @@ def test_neutral_penalties_are_a_bit_exact_no_op():
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
-def test_many_distinct_history_ids_use_the_slow_count_path():
-    """More than 2048 distinct history ids inside one vocabulary slice: counts come from scanning the history."""
+@pytest.mark.parametrize("cluster", [0, 1])
+def test_many_distinct_history_ids_use_the_slow_count_path(cluster):
+    """More than 2048 distinct history ids in one table: counts come from scanning the history."""
     m = mods()
     V, H = 8192, 6000
-    _lib.lib().colinfer_set_cluster_override(1)
+    _lib.lib().colinfer_set_cluster_override(cluster)
     g = torch.Generator().manual_seed(9)
     logits = torch.randn(1, 1, V, generator=g) * 2
     hist = torch.randint(0, V, (1, H), generator=g, dtype=torch.int32)
@@ -247,6 +248,23 @@ def test_many_distinct_history_ids_use_the_slow_count_path():
     out, st = m["draw"](logits.cuda(), sp, torch.zeros(1, dtype=torch.int32, device="cuda"), status=True)
     want = O.argmax(O.penalties(logits[0, 0].numpy(), hist[0].numpy(), 1.2, 0.3, 0.7))
     assert int(out) == want and int(st) == _lib.ROW_HIST_SLOW
+
+
+@pytest.mark.parametrize("V", [20000, 151936])
+@pytest.mark.parametrize("k,tp", [(0, 0.6), (3000, 1.0), (5000, 0.7), (0, 0.999)])
+def test_heavy_ties_take_the_exact_select(V, k, tp):
+    """Thousands of equal logits around the pivot overflow every candidate list: the radix select must give the same
+    kept set (all ties kept) and the same draw as the oracle."""
+    g = torch.Generator().manual_seed(V + k)
+    B = 6
+    logits = torch.randn(B, 1, V, generator=g)
+    tie = torch.randperm(V, generator=g)[:8000]
+    logits[:, 0, tie] = 3.25                                       # 8000 tokens share the maximum
+    logits[1::2, 0, tie[:10]] = 5.0                                # odd rows: a small head above the plateau
+    params = wl._params(B, V, 0.9, k, tp, 0.0, list(range(11, 11 + B)))
+    w = dict(logits=logits, params=params, pos=torch.arange(B, dtype=torch.int32), u=wl.open_unit(g, B, 1), name="ties")
+    nb, out = run_workload(w, V)
+    assert nb == 0
 
 
 # ------------------------------------------------------------------------------------------------ processed_probs / inverse_cdf
