@@ -38,6 +38,8 @@ constexpr int GLIST = 1365;          // gathered list entries
 constexpr int FIN_CAND = 64;         // entries of one bin compared pairwise
 constexpr int FB_NB = 256;           // radix buckets per level of the fallback select
 constexpr int PEN_TABLE = 2048;      // distinct history ids with an O(1) count
+constexpr int BAL_ROWS = 16384;      // launches up to this many rows deal their rows to the CTAs by cost class
+constexpr int BAL_MINE = BAL_ROWS / 128 + 4;   // rows of one CTA then (the grid has at least 128 CTAs, or one row each)
 #define ST_FLT_MAX 3.402823466e38f
 #define ST_POS_INF (__int_as_float(0x7f800000))
 
@@ -68,6 +70,7 @@ struct Sc {
     uint32_t fc_idx[FCAP]; float fc_l[FCAP];
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
+    int cls_cnt[3]; int my_rows[BAL_MINE];
 };
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
@@ -620,8 +623,52 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         sc->wtw[tid] = -ST_FLT_MAX; sc->wmin[tid] = ST_POS_INF;
     }
     __syncthreads();
-    for (long long row = blockIdx.x; row < n_rows; row += gridDim.x) {
+
+    // ---------------------------------------------------------------------------------------- which rows are this CTA's
+    // Rows differ in cost by a factor of ten (a wide top-p row takes several passes, a greedy row one), so dealing them
+    // out by index would leave some CTAs with most of the expensive ones.  Every CTA orders the rows by cost class
+    // (wide sampled, small top-k, greedy; index order inside a class) -- the same order in all CTAs -- and takes every
+    // gridDim.x-th entry of it.  Launches with at most one row per CTA, or very many rows, keep the index order.
+    const long long my_n = n_rows > blockIdx.x ? (n_rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const bool dealt = n_rows > gridDim.x && n_rows <= BAL_ROWS && gridDim.x >= 128;
+    if (dealt) {
+        auto row_class = [&](int row) {
+            const int b = row / a.R;
+            const float T = a.p.temperature[b];
+            const int k = a.p.top_k[b];
+            if (!((T > 0.0f) || (a.flags & COLINFER_FORCE_DISTRIBUTION))) return 2;
+            return (k > 0 && k <= FASTK && k < V) ? 1 : 0;
+        };
+        if (tid < 3) sc->cls_cnt[tid] = 0;
+        __syncthreads();
+        {
+            int c[3] = {0, 0, 0};
+            for (int row = tid; row < (int)n_rows; row += NT) c[row_class(row)]++;
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const int w = (int)__reduce_add_sync(0xffffffffu, (unsigned)c[j]);
+                if (lane == 0 && w) atomicAdd(&sc->cls_cnt[j], w);
+            }
+        }
+        __syncthreads();
+        long long run[3] = {0, sc->cls_cnt[0], (long long)sc->cls_cnt[0] + sc->cls_cnt[1]};   // next position of each class
+        for (int base = 0; base < (int)n_rows; base += NT) {
+            const int row = base + tid;
+            const int cls = row < (int)n_rows ? row_class(row) : -1;
+            u64 tot;                                             // three 21-bit counters in one scan
+            const u64 ex = block_excl_scan(cls < 0 ? 0ull : 1ull << (21 * cls), sc, tot);
+            if (cls >= 0) {
+                const long long pos = run[cls] + (long long)((ex >> (21 * cls)) & 0x1FFFFFull);
+                if (pos % gridDim.x == blockIdx.x) sc->my_rows[pos / gridDim.x] = row;
+            }
+#pragma unroll
+            for (int j = 0; j < 3; ++j) run[j] += (long long)((tot >> (21 * j)) & 0x1FFFFFull);
+            __syncthreads();
+        }
+    }
+    for (long long it = 0; it < my_n; ++it) {
         __syncthreads();                                         // the previous row's shared tables are free
+        const long long row = dealt ? (long long)sc->my_rows[it] : blockIdx.x + it * gridDim.x;
         ST_PROF(0);
         const int b = (int)(row / a.R), r = (int)(row % a.R);
         // ------------------------------------------------------------------------------------ parameters of the slot
