@@ -188,6 +188,7 @@ struct Row {
     const float* p32; const __nv_bfloat16* p16; int V; bool vec;
     const int32_t* mrow;
     bool has_pen; const uint32_t* pen_bits; const uint32_t* pen_prefix; const float* pen_val;
+    bool pen_inline;                   // the passes apply the penalties element by element (else: raw logits, lists patched afterwards)
     const int32_t* hist; int hlen; float rp, pp, fp; int* hist_slow;
 
     // penalised value of a token beyond the table: count its occurrences by scanning the history
@@ -220,7 +221,7 @@ struct Row {
     // the effective logits of a loaded group: penalties, then mask.  Groups at or beyond lim (the end of the caller's
     // region; at most V) keep the caller's filler values.
     __device__ __forceinline__ float4 fix4(float4 v, int i, int lim) const {
-        if (has_pen && i < lim) {
+        if (pen_inline && i < lim) {
             // the few penalised logits of the row were computed once (pen_val, by rank of the token in the history bitmap)
             const uint32_t word = pen_bits[i >> 5];
             const uint32_t nib = (word >> (i & 31)) & 0xFu;
@@ -366,7 +367,7 @@ __device__ bool finish_running_topk(const Cand* ownlist, int wn, float tw, float
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { const uint32_t x = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += x; }
         const uint32_t all = __shfl_sync(0xffffffffu, incl, 31);
-        const uint32_t want = min((uint32_t)kk, all);
+        const uint32_t want = (all >= (uint32_t)kk || sc->fin_all) ? min((uint32_t)kk, all) : 0u;   // a bound with fewer than kk above it is no bound
         const unsigned hit = __ballot_sync(0xffffffffu, incl >= want);
         if (want > 0 && lane == __ffs(hit) - 1) {
             uint32_t run = incl - s; int b = lane * PERB;
@@ -609,6 +610,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
     uint32_t* pen_prefix = pen_bits + nw;                                     // [nw] rank of each word's first set bit
     uint32_t* pen_cnt = pen_prefix + nw;                                      // [PEN_TABLE] occurrences per rank
     float* pen_val = reinterpret_cast<float*>(pen_cnt + PEN_TABLE);            // [PEN_TABLE] penalised logit per rank
+    float* pen_raw = pen_val + PEN_TABLE;                                      // [PEN_TABLE] stored logit per rank
 
     // warp w owns the contiguous region [r_lo, r_hi) of the row; lanes interleave float4 groups: token order inside a
     // region is (step, lane, component)
@@ -695,6 +697,8 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         if (tid == 0) sc->hist_slow = 0;
 
         // ------------------------------------------------------------------------------------ penalty tables (whole row)
+        int pen_distinct = 0;
+        rw.pen_inline = rw.has_pen;
         if (rw.has_pen) {
             for (int i = tid; i < nw; i += NT) pen_bits[i] = 0u;
             for (int i = tid; i < PEN_TABLE; i += NT) pen_cnt[i] = 0u;
@@ -712,6 +716,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 for (int i = lo; i < hi; ++i) local += __popc(pen_bits[i]);
                 u64 total_bits;
                 uint32_t run = (uint32_t)block_excl_scan(local, sc, total_bits);
+                pen_distinct = (int)total_bits;
                 for (int i = lo; i < hi; ++i) { pen_prefix[i] = run; run += __popc(pen_bits[i]); }
                 __syncthreads();
                 if (rw.fp != 0.0f) {                              // occurrences per rank
@@ -734,7 +739,9 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                         if (rk < PEN_TABLE) {
                             const int tok = (wi << 5) + bit;
                             const int cnt = rw.fp != 0.0f ? (int)pen_cnt[rk] : 1;
-                            pen_val[rk] = apply_penalty(rw.raw(tok), cnt, rw.rp, rw.pp, rw.fp);
+                            const float x = rw.raw(tok);
+                            pen_raw[rk] = x;
+                            pen_val[rk] = apply_penalty(x, cnt, rw.rp, rw.pp, rw.fp);
                         }
                         ++rk;
                     }
@@ -748,6 +755,12 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         // Small top_k: each warp lists the logits of its region that are >= its own threshold -- the kk-th largest it
         // has seen, raised whenever the list fills -- so that the lists together always hold the row's top kk.
         const bool fastk = sampled && kk > 0 && kk <= FASTK && kk < V;
+        // Penalised rows whose few hundred candidates decide everything (small top_k, greedy) read the logits as stored
+        // and patch the listed candidates afterwards: no per-element test of the history bitmap.
+        const bool patch = rw.has_pen && pen_distinct <= PEN_TABLE && (fastk || !sampled);
+        const bool listpass = fastk || patch;                    // greedy patch rows list a handful of top logits
+        const int kq = fastk ? kk : 4;
+        if (patch) rw.pen_inline = false;
         float lmax = CI_NEG_INF;
         int lpos = -1, lidx = 0x7fffffff;
         float tw = -ST_FLT_MAX;
@@ -765,7 +778,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         lmax = up ? m4 : lmax;                                                                                            \
         lpos = up ? (i0) + k * 128 + lane * 4 : lpos;                                                                     \
     }
-        if (!fastk) {
+        if (!listpass) {
             for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
                 float4 v[4];
                 ST_LOAD_BATCH(v, i0)
@@ -796,8 +809,8 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 if (gm[k] > CI_NEG_INF && lref < ST_POS_INF) atomicAdd(&hist1[min(BINS - 1, __float2int_rz((lref - gm[k]) * FAST_SCALE))], 1u);
             __syncthreads();
             int bk; u64 before, have;
-            bins_find([&](int i) { return (u64)hist1[i]; }, BINS, (u64)kk, sc, bk, before, have);
-            if (have >= (u64)kk && bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
+            bins_find([&](int i) { return (u64)hist1[i]; }, BINS, (u64)kq, sc, bk, before, have);
+            if (have >= (u64)kq && bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
             for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
                 float4 v[4];
                 ST_LOAD_BATCH(v, i0)
@@ -820,7 +833,46 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             if (wn1 > WLIST) fk_bad = 1;                         // a list overflowed (its tail was dropped): general path
         }
         ST_PROF(2);
-        if (lpos >= 0) {
+        bool from_lists = false;                                 // the maximum comes from the patched lists
+        if (patch) {
+            // penalised values for the listed tokens; the maximum and argmax of the row are then among the listed ones --
+            // provided no penalised token rose from below the bound to above it, and enough candidates remain
+            int bad = fk_bad;
+            float pm = CI_NEG_INF; int pi = 0x7fffffff, cnt_ok = 0;
+            for (int j = lane; j < min(wn1, WLIST); j += 32) {
+                const uint32_t idx = mylist[j].idx;
+                const uint32_t word = pen_bits[idx >> 5];
+                float l = mylist[j].l;
+                if ((word >> (idx & 31)) & 1u) {
+                    l = pen_val[pen_prefix[idx >> 5] + __popc(word & ((1u << (idx & 31)) - 1u))];
+                    mylist[j].l = l;
+                }
+                if (l >= tw) { ++cnt_ok; if (l > pm) { pm = l; pi = (int)idx; } }   // token order: the first maximum stays
+            }
+            for (int rk = tid; rk < pen_distinct; rk += NT)
+                if (pen_val[rk] >= tw && !(pen_raw[rk] >= tw)) bad = 1;
+            cnt_ok = (int)__reduce_add_sync(0xffffffffu, (unsigned)cnt_ok);
+            if (lane == 0) sc->wcount[warp] = cnt_ok;
+            bad = __syncthreads_or(bad);
+            int have_ok = sc->wcount[lane];
+            have_ok = (int)__reduce_add_sync(0xffffffffu, (unsigned)have_ok);
+            if (!bad && have_ok >= kq && tw > -ST_FLT_MAX) {
+                from_lists = true;
+                lmax = pm; lidx = pi;
+            } else {
+                // the bound does not hold for the penalised values: the element-wise pass after all
+                __syncthreads();
+                fk_bad = 1;
+                rw.pen_inline = true;
+                lmax = CI_NEG_INF; lpos = -1;
+                for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                    float4 v[4];
+                    ST_LOAD_BATCH(v, i0)
+                    ST_TRACK_MAX(v, i0)
+                }
+            }
+        }
+        if (!from_lists && lpos >= 0) {
             const float4 v = rw.load4(lpos);
             lidx = lpos + (v.x == lmax ? 0 : v.y == lmax ? 1 : v.z == lmax ? 2 : 3);
         }
@@ -876,6 +928,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 __syncthreads();
                 ST_PROF(7);
             }
+            if (!done) rw.pen_inline = rw.has_pen;               // the general path applies penalties element by element
 
             if (!done) {
                 enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
@@ -1141,7 +1194,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
 static int stream_smem_bytes(int V) {
     const int nw = (V + 31) / 32;
     return strm::NB1 * 4 + strm::BINS * 8 + strm::FB_NB * 8 + strm::NW * strm::WLIST * (int)sizeof(strm::Cand) +
-           (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 8 + 256;
+           (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 12 + 256;
 }
 
 void colinfer_profile_buffer(long long** buf, int* slots);   // sample.cu: the buffer colinfer_set_profile_buffer registered
