@@ -71,6 +71,7 @@ struct Sc {
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
     int cls_cnt[3]; int my_rows[BAL_MINE];
+    int glist_n;
 };
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
@@ -262,6 +263,25 @@ __device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, 
         }
     }
     wn += __popc(b0) + __popc(b1) + __popc(b2) + __popc(b3);
+}
+
+// Removes the entries of penalised tokens from a warp's list (token order kept); an overflowed list stays overflowed.
+__device__ __forceinline__ int warp_drop_penalised(Cand* mylist, int wn, const uint32_t* pen_bits, int lane) {
+    if (wn > WLIST) return wn;
+    const unsigned lt = (1u << lane) - 1u;
+    int out = 0;
+    for (int j0 = 0; j0 < wn; j0 += 32) {
+        const int j = j0 + lane;
+        Cand c; c.idx = 0; c.l = 0.0f;
+        bool keep = false;
+        if (j < wn) { c = mylist[j]; keep = !((pen_bits[c.idx >> 5] >> (c.idx & 31)) & 1u); }
+        const unsigned bal = __ballot_sync(0xffffffffu, keep);
+        __syncwarp();
+        if (keep) mylist[out + __popc(bal & lt)] = c;
+        out += __popc(bal);
+    }
+    __syncwarp();
+    return out;
 }
 
 // Concatenates the warps' lists (token order) into glist with masses; returns n, or -1 on overflow.  All threads call.
@@ -739,9 +759,10 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                         if (rk < PEN_TABLE) {
                             const int tok = (wi << 5) + bit;
                             const int cnt = rw.fp != 0.0f ? (int)pen_cnt[rk] : 1;
-                            const float x = rw.raw(tok);
+                            const bool masked = rw.mrow != nullptr && !((__ldg(rw.mrow + wi) >> bit) & 1);
+                            const float x = masked ? CI_NEG_INF : rw.raw(tok);
                             pen_raw[rk] = x;
-                            pen_val[rk] = apply_penalty(x, cnt, rw.rp, rw.pp, rw.fp);
+                            pen_val[rk] = masked ? CI_NEG_INF : apply_penalty(x, cnt, rw.rp, rw.pp, rw.fp);
                         }
                         ++rk;
                     }
@@ -755,10 +776,11 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         // Small top_k: each warp lists the logits of its region that are >= its own threshold -- the kk-th largest it
         // has seen, raised whenever the list fills -- so that the lists together always hold the row's top kk.
         const bool fastk = sampled && kk > 0 && kk <= FASTK && kk < V;
-        // Penalised rows whose few hundred candidates decide everything (small top_k, greedy) read the logits as stored
-        // and patch the listed candidates afterwards: no per-element test of the history bitmap.
-        const bool patch = rw.has_pen && pen_distinct <= PEN_TABLE && (fastk || !sampled);
-        const bool listpass = fastk || patch;                    // greedy patch rows list a handful of top logits
+        // Penalised rows read the logits as stored -- no per-element test of the history bitmap -- and patch afterwards:
+        // the listed candidates (which give the penalised maximum, and decide small-top-k and greedy rows), and for
+        // wide rows every count and sum, by the difference the few penalised tokens make.
+        const bool patch = rw.has_pen && pen_distinct <= PEN_TABLE;
+        const bool listpass = fastk || patch;                    // rows without a small top_k list a handful of top logits
         const int kq = fastk ? kk : 4;
         if (patch) rw.pen_inline = false;
         float lmax = CI_NEG_INF;
@@ -928,13 +950,31 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 __syncthreads();
                 ST_PROF(7);
             }
-            if (!done) rw.pen_inline = rw.has_pen;               // the general path applies penalties element by element
+            // Wide rows of a penalised slot keep reading the stored logits: every count and sum is corrected afterwards by
+            // the difference the (at most PEN_TABLE) penalised tokens make.  Without the patched maximum: element by element.
+            bool corr = !done && from_lists;
+            rw.pen_inline = rw.has_pen && !corr;
+            // the penalised tokens of this warp's own region (corrections of the warp's own sums need no atomics)
+            auto for_my_pen = [&](auto f) {
+                for (int wi = (r_lo >> 5) + lane; wi < ((r_hi + 31) >> 5); wi += 32) {
+                    uint32_t rest = pen_bits[wi], rk = pen_prefix[wi];
+                    while (rest) { const int bit = __ffs(rest) - 1; rest &= rest - 1; f((wi << 5) + bit, pen_raw[rk], pen_val[rk]); ++rk; }
+                }
+            };
+            auto for_each_pen = [&](auto f) {
+                for (int wi = tid; wi < nw; wi += NT) {
+                    uint32_t rest = pen_bits[wi], rk = pen_prefix[wi];
+                    while (rest) { const int bit = __ffs(rest) - 1; rest &= rest - 1; f((wi << 5) + bit, pen_raw[rk], pen_val[rk]); ++rk; }
+                }
+            };
 
             if (!done) {
                 enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
                 int path = PATH_PURE;
                 float t_hi = CI_NEG_INF, t_lo = ST_POS_INF;
                 const float SC1 = (float)NB1 / (RANGE * tc);
+                // a stored logit of a penalised token may lie above the row's (penalised) maximum: bucket 0
+                auto bucket1 = [&](float x) { return max(0, min(NB1 - 1, __float2int_rz((L - x) * SC1))); };
                 if (need_topk || need_topp) {
                     // ------------------------------------------------------------------------ pass 2: fine count histogram
                     const float lk = fmaxf(lcut, -ST_FLT_MAX);
@@ -955,9 +995,16 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                         }
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (e[j] >= lk) atomicAdd(&hist1[min(NB1 - 1, __float2int_rz((L - e[j]) * SC1))], 1u);
+                            if (e[j] >= lk) atomicAdd(&hist1[bucket1(e[j])], 1u);
                     }
                     __syncthreads();
+                    if (corr) {
+                        for_each_pen([&](int, float r, float e) {
+                            if (r >= lk) atomicSub(&hist1[bucket1(r)], 1u);
+                            if (e >= lk) atomicAdd(&hist1[bucket1(e)], 1u);
+                        });
+                        __syncthreads();
+                    }
                     ST_PROF(8);
                     int bsel; u64 before, survivors;
                     bins_find([&](int i) { return (u64)hist1[i]; }, NB1, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
@@ -1023,9 +1070,22 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                             }
                         }
                     }
-                    __syncthreads();
-                    const int n = gather_lists(ownlist, wn, glist, mass, sc);
-                    if (n > 0 && finish_on_list(glist, n, tl, lcut, tc, L, true, kk, need_topp, topp, u, bins, sc, token, lcut, total_mass)) done = true;
+                    int raised = 0;
+                    if (corr) {
+                        // listed penalised tokens take their penalised value in place (below tl: -inf, never kept); one
+                        // that rises from below tl to above it is not listed: the element-wise fallback
+                        for (int j = lane; j < min(wn, WLIST); j += 32) {
+                            const uint32_t idx = mylist[j].idx, word = pen_bits[idx >> 5];
+                            if ((word >> (idx & 31)) & 1u) {
+                                const float e = pen_val[pen_prefix[idx >> 5] + __popc(word & ((1u << (idx & 31)) - 1u))];
+                                mylist[j].l = e >= tl ? e : CI_NEG_INF;
+                            }
+                        }
+                        for_each_pen([&](int, float r, float e) { if (e >= tl && !(r >= tl)) raised = 1; });
+                    }
+                    raised = __syncthreads_or(raised);
+                    const int n = raised ? -1 : gather_lists(ownlist, wn, glist, mass, sc);
+                    if (n > 0 && finish_on_list(glist, n, tl, fmaxf(lcut, -ST_FLT_MAX), tc, L, true, kk, need_topp, topp, u, bins, sc, token, lcut, total_mass)) done = true;
                     else path = PATH_FALLBACK;
                     __syncthreads();
                     ST_PROF(10);
@@ -1034,6 +1094,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 // ---------------------------------------------------------------------------- fallback: exact radix select over the keys
                 if (path == PATH_FALLBACK) {
                     status |= COLINFER_ROW_SELECT_SLOW;
+                    corr = false; rw.pen_inline = rw.has_pen;
                     float lpiv;
                     if (kk > 0 && kk < V && radix_select(rw, r_lo, r_hi, mass, lcut, false, (u64)kk, topp, fb_hist, sc, lpiv))
                         lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
@@ -1050,50 +1111,65 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                     u64 acc_all = 0, acc_above = 0;
                     int wn = 0;
                     for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
-                        float e[16];
-                        float4 v4[4];
+                        float4 v[4];
+                        ST_LOAD_BATCH(v, i0)
+                        unsigned mk[4], anym = 0;
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const int i = i0 + k * 128 + lane * 4;
-                            v4[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
-                        }
+                            const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                            mk[k] = 0;
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const float4 v = rw.fix4(v4[k], i0 + k * 128 + lane * 4, r_hi);
-                            e[4 * k] = v.x; e[4 * k + 1] = v.y; e[4 * k + 2] = v.z; e[4 * k + 3] = v.w;
-                        }
-                        uint32_t q[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) q[j] = e[j] >= lk ? mass(e[j]) : 0u;
-#pragma unroll
-                        for (int j = 0; j < 16; j += 2) acc_all += (u64)q[j] + q[j + 1];
-                        if (band) {
-                            unsigned mk[4], anym = 0;
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                mk[k] = 0;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float x = e[4 * k + j];
-                                    if (x > t_hi) acc_above += q[4 * k + j];
-                                    else if (x >= t_lo && x >= lk) mk[k] |= 1u << j;
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t q = e[j] >= lk ? mass(e[j]) : 0u;
+                                acc_all += q;
+                                if (band) {
+                                    if (e[j] > t_hi) acc_above += q;
+                                    else if (e[j] >= t_lo && e[j] >= lk) mk[k] |= 1u << j;
                                 }
-                                anym |= mk[k];
                             }
-                            if (__ballot_sync(0xffffffffu, anym != 0u)) {
+                            anym |= mk[k];
+                        }
+                        if (band && __ballot_sync(0xffffffffu, anym != 0u)) {
+                            const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
+                            unsigned incl = cnt;
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) warp_append(mylist, wn, mk[k], &e[4 * k], (uint32_t)(i0 + k * 128 + lane * 4), lane);
-                            }
+                            for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+                            warp_append_batch<WLIST>(mylist, wn, mk, v, (uint32_t)(i0 + lane * 4), lane, incl, cnt);
                         }
                     }
                     ST_PROF(11);
                     u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
+                    u64 wall_corr = 0;
+                    if (corr) {
+                        // what the penalised tokens change: their stored logits were summed, their penalised ones count
+                        u64 d_all = 0, d_ab = 0;
+                        for_my_pen([&](int, float r, float e) {
+                            const u64 qr = r >= lk ? mass(r) : 0u, qe = e >= lk ? mass(e) : 0u;
+                            d_all += qe - qr;
+                            if (band) d_ab += (e > t_hi ? qe : 0ull) - (r > t_hi ? qr : 0ull);
+                        });
+                        wall_corr = warp_sum_u64(d_all);
+                        wkeep += band ? warp_sum_u64(d_ab) : wall_corr;
+                        if (band) wn = warp_drop_penalised(mylist, wn, pen_bits, lane);   // their penalised values join the band below
+                    }
                     if (band) {
-                        const u64 wall = warp_sum_u64(acc_all);
+                        const u64 wall = warp_sum_u64(acc_all) + wall_corr;
                         u64 s1, s_above;
                         block_excl_scan(lane == 0 ? wall : 0ull, sc, s1);
                         block_excl_scan(lane == 0 ? wkeep : 0ull, sc, s_above);
-                        const int n = gather_lists(ownlist, wn, glist, mass, sc);
+                        int n = gather_lists(ownlist, wn, glist, mass, sc);
+                        if (corr && n >= 0) {
+                            if (tid == 0) sc->glist_n = n;
+                            __syncthreads();
+                            for_each_pen([&](int tok, float, float e) {
+                                if (e >= lk && e >= t_lo && !(e > t_hi)) {
+                                    const int slot = atomicAdd(&sc->glist_n, 1);
+                                    if (slot < GLIST) { Entry en; en.idx = (uint32_t)tok; en.l = e; en.q = mass(e); glist[slot] = en; }
+                                }
+                            });
+                            __syncthreads();
+                            n = sc->glist_n <= GLIST ? sc->glist_n : -1;
+                        }
                         bool ok = n >= 0 && s1 > 0;
                         float cut2 = lcut;
                         if (ok) {
@@ -1121,11 +1197,18 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                             const int mine = min(wn, WLIST);
                             for (int j = lane; j < mine; j += 32) if (mylist[j].l >= lcut) add += mass(mylist[j].l);
                             wkeep += warp_sum_u64(add);
+                            if (corr) {
+                                // penalised tokens whose penalised value lies in the band (those above it are in wkeep already)
+                                u64 d = 0;
+                                for_my_pen([&](int, float, float e) { if (e >= lcut && e >= lk && !(e > t_hi)) d += mass(e); });
+                                wkeep += warp_sum_u64(d);
+                            }
                         } else {
                             // the estimated band missed the pivot (or a list overflowed): exact radix select by mass, then the
                             // regions' kept masses again
                             float lpiv;
                             status |= COLINFER_ROW_SELECT_SLOW;
+                            corr = false; rw.pen_inline = rw.has_pen;
                             if (radix_select(rw, r_lo, r_hi, mass, lcut, true, 0, topp, fb_hist, sc, lpiv))
                                 lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
                             const float lk3 = fmaxf(lcut, -ST_FLT_MAX);
@@ -1138,6 +1221,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                             wkeep = warp_sum_u64(acc);
                         }
                     }
+                    rw.pen_inline = rw.has_pen;                 // the rescan of one region applies penalties in place
                     ST_PROF(12);
                     const u64 woff = __shfl_sync(0xffffffffu, block_excl_scan(lane == 0 ? wkeep : 0ull, sc, total_mass), 0);
                     const u64 target = ceil_target(u, total_mass);
