@@ -26,8 +26,9 @@ namespace strm {
 constexpr int NT = 1024;             // threads per CTA
 constexpr int NW = NT / 32;
 constexpr int NWA = 32;              // per-warp exchange arrays are sized (and reduced) for a full warp of warps
-constexpr int NB1 = 4096;            // fine buckets over the distance from the row maximum
-constexpr float RANGE = 25.0f;       // they cover distances up to RANGE * temperature
+constexpr int NB1 = 8192;            // fine buckets over the distance from the row maximum (or from the sample's)
+constexpr int HOFF = 4096;           // buckets kept above the sample's maximum when the histogram is built in pass 1
+constexpr float RANGE = 50.0f;       // they cover distances up to RANGE * temperature (RANGE / 2 above a sample's maximum)
 constexpr int FASTK = 100;           // largest top_k finished from the group-maxima bound
 constexpr int BINS = 512;            // bins of the sample histogram and of the exact list selection
 constexpr float FAST_SCALE = 32.0f;  // sample-histogram bins per unit logit (16 units below the sample's maximum)
@@ -133,9 +134,6 @@ __device__ __forceinline__ float row_uniform(const Args& a, int row, int b, int 
     return 1.0f;
 }
 
-__device__ __forceinline__ u64 bucket_mass_est(int b) {
-    return (u64)__float2uint_rn(exp2f(-((float)b + 0.5f) * (RANGE * CI_LOG2E / (float)NB1)) * CI_MASS_SCALE);
-}
 
 // Exact weighted selection among n list entries: the value v with W(l > v) < target <= W(l >= v).  BINS linear bins over
 // (base - l) * scale, then the pivot bin's entries pairwise.  False when the pivot leaves the binned range or its bin
@@ -720,10 +718,30 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         int pen_distinct = 0;
         rw.pen_inline = rw.has_pen;
         if (rw.has_pen) {
+            // Each thread keeps its first HP history entries and their stored logits in registers: the two dependent loads
+            // (id, then logit) run under the bitmap and rank steps.  Longer histories re-read the rest.
+            constexpr int HP = 2;
+            int ht[HP]; float hx[HP];
             for (int i = tid; i < nw; i += NT) pen_bits[i] = 0u;
             for (int i = tid; i < PEN_TABLE; i += NT) pen_cnt[i] = 0u;
+#pragma unroll
+            for (int j = 0; j < HP; ++j) {
+                const int i = tid + j * NT;
+                ht[j] = i < hlen ? __ldg(rw.hist + i) : -1;
+                if (ht[j] >= V) ht[j] = -1;
+            }
+#pragma unroll
+            for (int j = 0; j < HP; ++j) {
+                hx[j] = CI_NEG_INF;
+                if (ht[j] >= 0) {
+                    const bool masked = rw.mrow != nullptr && !((__ldg(rw.mrow + (ht[j] >> 5)) >> (ht[j] & 31)) & 1);
+                    if (!masked) hx[j] = rw.raw(ht[j]);
+                }
+            }
             __syncthreads();
-            for (int i = tid; i < hlen; i += NT) {
+#pragma unroll
+            for (int j = 0; j < HP; ++j) if (ht[j] >= 0) atomicOr(&pen_bits[ht[j] >> 5], 1u << (ht[j] & 31));
+            for (int i = tid + HP * NT; i < hlen; i += NT) {
                 const int v = __ldg(rw.hist + i);
                 if (v >= 0 && v < V) atomicOr(&pen_bits[v >> 5], 1u << (v & 31));
             }
@@ -739,32 +757,34 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 pen_distinct = (int)total_bits;
                 for (int i = lo; i < hi; ++i) { pen_prefix[i] = run; run += __popc(pen_bits[i]); }
                 __syncthreads();
+                auto rank_of = [&](int v) { return pen_prefix[v >> 5] + __popc(pen_bits[v >> 5] & ((1u << (v & 31)) - 1u)); };
+                uint32_t hr[HP];
+#pragma unroll
+                for (int j = 0; j < HP; ++j) hr[j] = ht[j] >= 0 ? rank_of(ht[j]) : 0xFFFFFFFFu;
                 if (rw.fp != 0.0f) {                              // occurrences per rank
-                    for (int i = tid; i < hlen; i += NT) {
+#pragma unroll
+                    for (int j = 0; j < HP; ++j) if (hr[j] < PEN_TABLE) atomicAdd(&pen_cnt[hr[j]], 1u);
+                    for (int i = tid + HP * NT; i < hlen; i += NT) {
                         const int v = __ldg(rw.hist + i);
-                        if (v >= 0 && v < V) {
-                            const uint32_t rk = pen_prefix[v >> 5] + __popc(pen_bits[v >> 5] & ((1u << (v & 31)) - 1u));
-                            if (rk < PEN_TABLE) atomicAdd(&pen_cnt[rk], 1u);
-                        }
+                        if (v >= 0 && v < V) { const uint32_t rk = rank_of(v); if (rk < PEN_TABLE) atomicAdd(&pen_cnt[rk], 1u); }
                     }
                     __syncthreads();
                 }
-                // the penalised logit of every marked token, once per row
-                for (int wi = tid; wi < nw; wi += NT) {
-                    uint32_t rest = pen_bits[wi];
-                    uint32_t rk = pen_prefix[wi];
-                    while (rest) {
-                        const int bit = __ffs(rest) - 1;
-                        rest &= rest - 1;
-                        if (rk < PEN_TABLE) {
-                            const int tok = (wi << 5) + bit;
-                            const int cnt = rw.fp != 0.0f ? (int)pen_cnt[rk] : 1;
-                            const bool masked = rw.mrow != nullptr && !((__ldg(rw.mrow + wi) >> bit) & 1);
-                            const float x = masked ? CI_NEG_INF : rw.raw(tok);
-                            pen_raw[rk] = x;
-                            pen_val[rk] = masked ? CI_NEG_INF : apply_penalty(x, cnt, rw.rp, rw.pp, rw.fp);
-                        }
-                        ++rk;
+                // the stored and the penalised logit of every marked token (equal tokens write equal values)
+                auto put = [&](uint32_t rk, float x) {
+                    if (rk < PEN_TABLE) {
+                        const int cnt = rw.fp != 0.0f ? (int)pen_cnt[rk] : 1;
+                        pen_raw[rk] = x;
+                        pen_val[rk] = x > CI_NEG_INF ? apply_penalty(x, cnt, rw.rp, rw.pp, rw.fp) : CI_NEG_INF;
+                    }
+                };
+#pragma unroll
+                for (int j = 0; j < HP; ++j) put(hr[j], hx[j]);
+                for (int i = tid + HP * NT; i < hlen; i += NT) {
+                    const int v = __ldg(rw.hist + i);
+                    if (v >= 0 && v < V) {
+                        const bool masked = rw.mrow != nullptr && !((__ldg(rw.mrow + (v >> 5)) >> (v & 31)) & 1);
+                        put(rank_of(v), masked ? CI_NEG_INF : rw.raw(v));
                     }
                 }
             }
@@ -780,8 +800,14 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         // the listed candidates (which give the penalised maximum, and decide small-top-k and greedy rows), and for
         // wide rows every count and sum, by the difference the few penalised tokens make.
         const bool patch = rw.has_pen && pen_distinct <= PEN_TABLE;
-        const bool listpass = fastk || patch;                    // rows without a small top_k list a handful of top logits
+        const bool do_lists = fastk || patch;                    // rows without a small top_k list a handful of top logits
+        // Wide rows that need a pivot (large top_k, top_p) count the fine histogram in this pass too, in buckets laid
+        // out from the sample's maximum (the row's is not known yet), HOFF of them above it.
+        const bool wide_hist = sampled && !fastk && ((kk > 0 && kk < V) || topp < 1.0f);
+        const bool listpass = do_lists || wide_hist;
         const int kq = fastk ? kk : 4;
+        const float SCW = (float)NB1 / (RANGE * tc);
+        float lref = CI_NEG_INF;
         if (patch) rw.pen_inline = false;
         float lmax = CI_NEG_INF;
         int lpos = -1, lidx = 0x7fffffff;
@@ -823,20 +849,41 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             if (lane == 0) sc->wf[warp] = sm;
             for (int i = tid; i < BINS; i += NT) hist1[i] = 0u;
             __syncthreads();
-            float lref = sc->wf[lane];
+            lref = sc->wf[lane];
 #pragma unroll
             for (int o = 16; o; o >>= 1) lref = fmaxf(lref, __shfl_xor_sync(0xffffffffu, lref, o));
+            if (do_lists) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (gm[k] > CI_NEG_INF && lref < ST_POS_INF) atomicAdd(&hist1[min(BINS - 1, __float2int_rz((lref - gm[k]) * FAST_SCALE))], 1u);
-            __syncthreads();
-            int bk; u64 before, have;
-            bins_find([&](int i) { return (u64)hist1[i]; }, BINS, (u64)kq, sc, bk, before, have);
-            if (have >= (u64)kq && bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
+                for (int k = 0; k < 4; ++k)
+                    if (gm[k] > CI_NEG_INF && lref < ST_POS_INF) atomicAdd(&hist1[min(BINS - 1, __float2int_rz((lref - gm[k]) * FAST_SCALE))], 1u);
+                __syncthreads();
+                int bk; u64 before, have;
+                bins_find([&](int i) { return (u64)hist1[i]; }, BINS, (u64)kq, sc, bk, before, have);
+                if (have >= (u64)kq && bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
+            } else {
+                tw = ST_POS_INF;                                 // nothing to list
+            }
+            const bool count_hist = wide_hist && lref > CI_NEG_INF && lref < ST_POS_INF;
+            if (count_hist) {
+                __syncthreads();
+                for (int i = tid; i < NB1; i += NT) hist1[i] = 0u;
+                __syncthreads();
+            } else {
+                lref = CI_NEG_INF;                               // marks: no histogram from this pass
+            }
             for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
                 float4 v[4];
                 ST_LOAD_BATCH(v, i0)
                 ST_TRACK_MAX(v, i0)
+                if (count_hist) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (e[j] > CI_NEG_INF) atomicAdd(&hist1[max(0, min(NB1 - 1, HOFF + __float2int_rd((lref - e[j]) * SCW)))], 1u);
+                    }
+                }
                 unsigned mk[4], anym = 0;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -853,6 +900,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 }
             }
             if (wn1 > WLIST) fk_bad = 1;                         // a list overflowed (its tail was dropped): general path
+            if (!do_lists) { tw = -ST_FLT_MAX; wn1 = 0; }
         }
         ST_PROF(2);
         bool from_lists = false;                                 // the maximum comes from the patched lists
@@ -894,6 +942,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 }
             }
         }
+        if (patch && !from_lists) lref = CI_NEG_INF;             // the histogram of this pass counted stored logits: void
         if (!from_lists && lpos >= 0) {
             const float4 v = rw.load4(lpos);
             lidx = lpos + (v.x == lmax ? 0 : v.y == lmax ? 1 : v.z == lmax ? 2 : 3);
@@ -972,71 +1021,78 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
                 int path = PATH_PURE;
                 float t_hi = CI_NEG_INF, t_lo = ST_POS_INF;
-                const float SC1 = (float)NB1 / (RANGE * tc);
-                // a stored logit of a penalised token may lie above the row's (penalised) maximum: bucket 0
-                auto bucket1 = [&](float x) { return max(0, min(NB1 - 1, __float2int_rz((L - x) * SC1))); };
+                const float SC1 = SCW;
+                // The fine buckets: from pass 1 (laid out from the sample's maximum, HOFF of them above it) or counted now
+                // (from the row's maximum).  Bucket b holds the logits in (edge(b + 1), edge(b)].  A stored logit of a
+                // penalised token may lie above every bucket: bucket 0.
+                const bool hist_ready = lref > CI_NEG_INF;
+                const float href = hist_ready ? lref : L;
+                const int hoff = hist_ready ? HOFF : 0;
+                auto bucket1 = [&](float x) { return max(0, min(NB1 - 1, hoff + __float2int_rd((href - x) * SC1))); };
+                auto edge = [&](int b) { return href - (float)(b - hoff) / SC1; };
                 if (need_topk || need_topp) {
-                    // ------------------------------------------------------------------------ pass 2: fine count histogram
-                    const float lk = fmaxf(lcut, -ST_FLT_MAX);
-                    for (int i = tid; i < NB1; i += NT) hist1[i] = 0u;
-                    __syncthreads();
-                    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
-                        float e[16];
-                        float4 v4[4];
+                    if (!hist_ready) {
+                        // -------------------------------------------------------------------- pass 2: fine count histogram
+                        for (int i = tid; i < NB1; i += NT) hist1[i] = 0u;
+                        __syncthreads();
+                        for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                            float4 v[4];
+                            ST_LOAD_BATCH(v, i0)
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int i = i0 + k * 128 + lane * 4;
-                            v4[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+                            for (int k = 0; k < 4; ++k) {
+                                const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) if (e[j] > CI_NEG_INF) atomicAdd(&hist1[bucket1(e[j])], 1u);
+                            }
                         }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const float4 v = rw.fix4(v4[k], i0 + k * 128 + lane * 4, r_hi);
-                            e[4 * k] = v.x; e[4 * k + 1] = v.y; e[4 * k + 2] = v.z; e[4 * k + 3] = v.w;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (e[j] >= lk) atomicAdd(&hist1[bucket1(e[j])], 1u);
                     }
                     __syncthreads();
                     if (corr) {
                         for_each_pen([&](int, float r, float e) {
-                            if (r >= lk) atomicSub(&hist1[bucket1(r)], 1u);
-                            if (e >= lk) atomicAdd(&hist1[bucket1(e)], 1u);
+                            if (r > CI_NEG_INF) atomicSub(&hist1[bucket1(r)], 1u);
+                            if (e > CI_NEG_INF) atomicAdd(&hist1[bucket1(e)], 1u);
                         });
                         __syncthreads();
                     }
                     ST_PROF(8);
+                    // the histogram counts every finite logit; buckets wholly below the min-p cut are left out of the scans
+                    const int b_cut = lcut > CI_NEG_INF ? bucket1(lcut) : NB1 - 1;
+                    auto cnt_of = [&](int i) { return i <= b_cut ? (u64)hist1[i] : 0ull; };
+                    const float dL = (L - href) / tc;
+                    auto mass_est = [&](int i) {
+                        return (u64)__float2uint_rn(exp2f(fminf(0.0f, -(((float)(i - hoff) + 0.5f) * (RANGE / (float)NB1) + dL) * CI_LOG2E)) * CI_MASS_SCALE);
+                    };
                     int bsel; u64 before, survivors;
-                    bins_find([&](int i) { return (u64)hist1[i]; }, NB1, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
-                    if (need_topk && (u64)kk >= survivors) need_topk = false;   // fewer survivors than k: top-k removes nothing
+                    bins_find(cnt_of, NB1, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
+                    if (need_topk && (u64)kk >= survivors) need_topk = false;   // at most k reach the min-p cut's bucket: top-k removes nothing
                     if (need_topk) {
                         const u64 n_upto = bsel >= 0 ? before + hist1[bsel] : (u64)GLIST + 1;
-                        if (bsel < 0 || bsel >= NB1 - 3 || n_upto > GLIST - 64) path = PATH_FALLBACK;
+                        if (bsel < (hist_ready ? 1 : 0) || bsel >= NB1 - 3 || n_upto > GLIST - 64) path = PATH_FALLBACK;   // bucket 0 of a pass-1 histogram may mix logits from far above the sample's maximum
                         else {
                             path = PATH_LIST;
-                            t_lo = L - ((float)(bsel + 2) + 0.01f) / SC1 - fabsf(L) * 1e-6f;
+                            t_lo = edge(bsel + 2) - 0.01f / SC1 - fabsf(href) * 1e-6f;
                         }
                     } else if (need_topp) {
                         int bp; u64 bef, est_total;
-                        bins_find([&](int i) { return (u64)hist1[i] * bucket_mass_est(i); }, NB1, 0, sc, bp, bef, est_total);
+                        bins_find([&](int i) { return cnt_of(i) * mass_est(i); }, NB1, 0, sc, bp, bef, est_total);
                         if (est_total == 0) path = PATH_FALLBACK;
                         else {
-                            bins_find([&](int i) { return (u64)hist1[i] * bucket_mass_est(i); }, NB1, ceil_target(topp, est_total), sc, bp, bef, est_total);
+                            bins_find([&](int i) { return cnt_of(i) * mass_est(i); }, NB1, ceil_target(topp, est_total), sc, bp, bef, est_total);
                             const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
                             // how far down the list capacity reaches: bucket where the cumulative count gets there
                             int bcap; u64 bef2, tot2;
-                            bins_find([&](int i) { return (u64)hist1[i]; }, NB1, (u64)768, sc, bcap, bef2, tot2);   // ~24 per warp list of 64
-                            if (bp < 0) path = PATH_FALLBACK;
+                            bins_find(cnt_of, NB1, (u64)768, sc, bcap, bef2, tot2);   // ~24 per warp list of 64
+                            if (bp < (hist_ready ? 1 : 0)) path = PATH_FALLBACK;
                             else if (bcap < 0 || bcap > bp + dn + 1) {
                                 // small nucleus: gather everything down to well below the estimated pivot; nothing is "above"
                                 path = PATH_BAND;
                                 t_hi = ST_POS_INF;
-                                t_lo = bcap < 0 ? -ST_FLT_MAX : L - (float)bcap / SC1;
+                                t_lo = bcap < 0 ? -ST_FLT_MAX : edge(bcap);
                             } else if (bp + dn + 2 >= NB1) path = PATH_FALLBACK;
                             else {
                                 path = PATH_BAND;
-                                t_hi = bp - up <= 0 ? ST_POS_INF : L - (float)(bp - up) / SC1;
-                                t_lo = L - (float)(bp + dn + 1) / SC1;
+                                t_hi = bp - up <= 0 ? ST_POS_INF : edge(bp - up);
+                                t_lo = edge(bp + dn + 1);
                             }
                         }
                     }
