@@ -245,6 +245,31 @@ struct Row {
     }
 };
 
+// Pass 1 of rows that list nothing: maximum of the warp's region and the float4 group it was first seen in.  Its own
+// function (and register allocation): the loop must keep four 128-bit loads per thread in flight.
+__device__ __noinline__ float2 pass1_lean(const Row rw, int r_lo, int r_hi, int lane) {
+    float lmax = CI_NEG_INF;
+    int lpos = -1;
+    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * 128 + lane * 4;
+            v[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = rw.fix4(v[k], i0 + k * 128 + lane * 4, r_hi);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
+            const bool up = m4 > lmax;                           // strict: the first (lowest) position of the maximum stays
+            lmax = up ? m4 : lmax;
+            lpos = up ? i0 + k * 128 + lane * 4 : lpos;
+        }
+    }
+    return make_float2(lmax, __int_as_float(lpos));
+}
+
 // Appends the components of one float4 group selected by mk to the warp's list, in token order (lane, component).
 template <int CAP = WLIST>
 __device__ __forceinline__ void warp_append(Cand* mylist, int& wn, unsigned mk, const float* e4, uint32_t idx0, int lane) {
@@ -827,11 +852,8 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         lpos = up ? (i0) + k * 128 + lane * 4 : lpos;                                                                     \
     }
         if (!listpass) {
-            for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
-                float4 v[4];
-                ST_LOAD_BATCH(v, i0)
-                ST_TRACK_MAX(v, i0)
-            }
+            const float2 mp = pass1_lean(rw, r_lo, r_hi, lane);
+            lmax = mp.x; lpos = __float_as_int(mp.y);
         } else {
             // The first batch of every warp (a tenth of the row at 151,936 logits) bounds the row's kk-th largest logit
             // from below: the kk-th largest of the sample's float4 maxima.  The pass then lists what reaches the bound.
