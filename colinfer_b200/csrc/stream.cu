@@ -71,7 +71,7 @@ struct Sc {
     uint32_t fc_idx[FCAP]; float fc_l[FCAP];
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
-    int cls_cnt[3]; int my_rows[BAL_MINE];
+    int my_rows[BAL_MINE];
     int glist_n;
 };
 
@@ -684,32 +684,30 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             if (!((T > 0.0f) || (a.flags & COLINFER_FORCE_DISTRIBUTION))) return 2;
             return (k > 0 && k <= FASTK && k < V) ? 1 : 0;
         };
-        if (tid < 3) sc->cls_cnt[tid] = 0;
-        __syncthreads();
-        {
-            int c[3] = {0, 0, 0};
-            for (int row = tid; row < (int)n_rows; row += NT) c[row_class(row)]++;
+        // one scan over the threads' per-class counts (three 21-bit counters in a word) orders the rows by (class, thread,
+        // chunk): any order will do as long as every CTA computes the same one
+        constexpr int CH = BAL_ROWS / NT;
+        int cls[CH];
+        u64 packed = 0;
 #pragma unroll
-            for (int j = 0; j < 3; ++j) {
-                const int w = (int)__reduce_add_sync(0xffffffffu, (unsigned)c[j]);
-                if (lane == 0 && w) atomicAdd(&sc->cls_cnt[j], w);
+        for (int c = 0; c < CH; ++c) {
+            const int row = c * NT + tid;
+            cls[c] = row < (int)n_rows ? row_class(row) : -1;
+            if (cls[c] >= 0) packed += 1ull << (21 * cls[c]);
+        }
+        u64 tot;
+        u64 ex = block_excl_scan(packed, sc, tot);
+        const u64 n0 = tot & 0x1FFFFFull, n1 = (tot >> 21) & 0x1FFFFFull;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            if (cls[c] >= 0) {
+                const int j = cls[c];
+                const long long pos = (long long)((j == 0 ? 0ull : j == 1 ? n0 : n0 + n1) + ((ex >> (21 * j)) & 0x1FFFFFull));
+                ex += 1ull << (21 * j);
+                if (pos % gridDim.x == blockIdx.x) sc->my_rows[pos / gridDim.x] = c * NT + tid;
             }
         }
         __syncthreads();
-        long long run[3] = {0, sc->cls_cnt[0], (long long)sc->cls_cnt[0] + sc->cls_cnt[1]};   // next position of each class
-        for (int base = 0; base < (int)n_rows; base += NT) {
-            const int row = base + tid;
-            const int cls = row < (int)n_rows ? row_class(row) : -1;
-            u64 tot;                                             // three 21-bit counters in one scan
-            const u64 ex = block_excl_scan(cls < 0 ? 0ull : 1ull << (21 * cls), sc, tot);
-            if (cls >= 0) {
-                const long long pos = run[cls] + (long long)((ex >> (21 * cls)) & 0x1FFFFFull);
-                if (pos % gridDim.x == blockIdx.x) sc->my_rows[pos / gridDim.x] = row;
-            }
-#pragma unroll
-            for (int j = 0; j < 3; ++j) run[j] += (long long)((tot >> (21 * j)) & 0x1FFFFFull);
-            __syncthreads();
-        }
     }
     for (long long it = 0; it < my_n; ++it) {
         __syncthreads();                                         // the previous row's shared tables are free
