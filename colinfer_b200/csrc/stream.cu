@@ -39,6 +39,7 @@ constexpr int GLIST = 1365;          // gathered list entries
 constexpr int FIN_CAND = 64;         // entries of one bin compared pairwise
 constexpr int FB_NB = 256;           // radix buckets per level of the fallback select
 constexpr int PEN_TABLE = 2048;      // distinct history ids with an O(1) count
+constexpr int XSTEPS = 128;           // 128-logit steps of one warp's region, at most (vocabularies up to 32 x 128 x 128)
 constexpr int BAL_ROWS = 16384;      // launches up to this many rows deal their rows to the CTAs by cost class
 constexpr int BAL_MINE = BAL_ROWS / 128 + 4;   // rows of one CTA then (the grid has at least 128 CTAs, or one row each)
 #define ST_FLT_MAX 3.402823466e38f
@@ -72,6 +73,7 @@ struct Sc {
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
     int my_rows[BAL_MINE];
+    int x_warp; u64 x_off; u64 step_sum[XSTEPS];   // the draw's region, walked by all warps
     int glist_n;
 };
 
@@ -1302,29 +1304,57 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                     const u64 woff = __shfl_sync(0xffffffffu, block_excl_scan(lane == 0 ? wkeep : 0ull, sc, total_mass), 0);
                     const u64 target = ceil_target(u, total_mass);
                     token = -1;
-                    if (total_mass > 0 && woff < target && target <= woff + wkeep) {
+                    // The draw falls into one warp's region; all warps walk that region together, one 128-logit step each.
+                    if (lane == 0 && total_mass > 0 && woff < target && target <= woff + wkeep) { sc->x_warp = warp; sc->x_off = woff; }
+                    __syncthreads();
+                    if (total_mass > 0) {
                         const float lkf = fmaxf(lcut, -ST_FLT_MAX);
-                        u64 run = woff;
-                        for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
-                            const int i = i0 + lane * 4;
-                            const float4 v = rw.load4(i);
-                            u64 q4[4];
+                        const int x_lo = min(sc->x_warp * reg, V), x_hi = min(x_lo + reg, V);
+                        const int nsteps = (x_hi - x_lo + 127) >> 7;        // at most XSTEPS
+                        const u64 t2 = target - sc->x_off;                  // the crossing inside the region
+                        auto step_masses = [&](int st, u64 (&q4)[4]) {
+                            const int i = x_lo + st * 128 + lane * 4;
+                            const float4 v = i < x_hi ? rw.load4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
                             q4[0] = v.x >= lkf ? mass(v.x) : 0u; q4[1] = v.y >= lkf ? mass(v.y) : 0u;
                             q4[2] = v.z >= lkf ? mass(v.z) : 0u; q4[3] = v.w >= lkf ? mass(v.w) : 0u;
-                            const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
-                            const u64 incl = warp_incl_scan_u64(s4, lane);
-                            const u64 grp = __shfl_sync(0xffffffffu, incl, 31);
-                            if (run + grp >= target) {
-                                const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
-                                if (lane == __ffs(hit) - 1) {
-                                    u64 c = run + incl - s4;
-                                    int j = 0;
-                                    for (; j < 3; ++j) { c += q4[j]; if (c >= target) break; }
-                                    if (a.out) a.out[row] = (long long)(i + j);
-                                }
-                                break;
+                        };
+                        for (int st = warp; st < nsteps; st += NW) {
+                            u64 q4[4];
+                            step_masses(st, q4);
+                            const u64 ws = warp_sum_u64(q4[0] + q4[1] + q4[2] + q4[3]);
+                            if (lane == 0) sc->step_sum[st] = ws;
+                        }
+                        __syncthreads();
+                        if (warp == 0) {
+                            // the step in which the running kept mass reaches t2 (four steps per lane), then its lane and logit
+                            constexpr int PS = XSTEPS / 32;
+                            u64 mine[PS], s = 0;
+#pragma unroll
+                            for (int t = 0; t < PS; ++t) { const int st = lane * PS + t; mine[t] = st < nsteps ? sc->step_sum[st] : 0ull; s += mine[t]; }
+                            const u64 incl = warp_incl_scan_u64(s, lane);
+                            const unsigned hit = __ballot_sync(0xffffffffu, incl >= t2);
+                            int sx = -1; u64 before = 0;
+                            if (hit) {
+                                const int hl = __ffs(hit) - 1;
+                                u64 run = incl - s; int st = lane * PS;
+#pragma unroll
+                                for (int t = 0; t < PS; ++t) { if (run + mine[t] >= t2) { st = lane * PS + t; break; } run += mine[t]; }
+                                sx = __shfl_sync(0xffffffffu, st, hl);
+                                before = __shfl_sync(0xffffffffu, run, hl);
                             }
-                            run += grp;
+                            if (sx >= 0) {
+                                u64 q4[4];
+                                step_masses(sx, q4);
+                                const u64 s4 = q4[0] + q4[1] + q4[2] + q4[3];
+                                const u64 inc2 = warp_incl_scan_u64(s4, lane);
+                                const unsigned h2 = __ballot_sync(0xffffffffu, before + inc2 >= t2);
+                                if (h2 && lane == __ffs(h2) - 1) {
+                                    u64 c = before + inc2 - s4;
+                                    int j = 0;
+                                    for (; j < 3; ++j) { c += q4[j]; if (c >= t2) break; }
+                                    if (a.out) a.out[row] = (long long)(x_lo + sx * 128 + lane * 4 + j);
+                                }
+                            }
                         }
                     }
                     if (total_mass == 0) { status |= COLINFER_ROW_DEGENERATE; token = aidx; }
@@ -1365,7 +1395,7 @@ int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, i
                            int64_t* out_ids, colinfer_row_stats* stats, int32_t* status, int B, int R, int V, int flags,
                            cudaStream_t stream) {
     const int smem = stream_smem_bytes(V);
-    if (smem > 226 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 226 * 1024 || V > 32 * 128 * strm::XSTEPS) return (int)cudaErrorInvalidValue;
     const bool vec = dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)logits) & 15) == 0;
     static int sm_count[64] = {};
     int dev = 0;
