@@ -120,6 +120,45 @@ __device__ void bins_find(F get, int nbins, u64 target, Sc* sc, int& bin, u64& b
     before = sc->found_excl;
 }
 
+// bins_find over the NB1 fine buckets with weights: value(i) = hist[i] * w(i) for i <= last, 0 beyond.  Each thread owns
+// NB1 / NT consecutive buckets and reads them with 128-bit loads (scalar loads at that stride conflict eightfold).
+template <class W>
+__device__ void fine_find(const uint32_t* hist, W w, int last, u64 target, Sc* sc, int& bin, u64& before, u64& total) {
+    constexpr int PER = NB1 / NT;
+    static_assert(PER % 4 == 0, "128-bit loads");
+    const int lo = threadIdx.x * PER;
+    uint32_t c[PER];
+#pragma unroll
+    for (int t = 0; t < PER; t += 4) {
+        const uint4 x = *reinterpret_cast<const uint4*>(hist + lo + t);
+        c[t] = x.x; c[t + 1] = x.y; c[t + 2] = x.z; c[t + 3] = x.w;
+    }
+    u64 s = 0;
+#pragma unroll
+    for (int t = 0; t < PER; ++t) s += (lo + t <= last && c[t]) ? (u64)c[t] * w(lo + t) : 0ull;
+    const u64 excl = block_excl_scan(s, sc, total);
+    if (excl < target && target <= excl + s) {
+        u64 run = excl;
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+            const u64 b = (lo + t <= last && c[t]) ? (u64)c[t] * w(lo + t) : 0ull;
+            if (run + b >= target) { sc->found = lo + t; sc->found_excl = run; break; }
+            run += b;
+        }
+    }
+    __syncthreads();
+    bin = sc->found;
+    before = sc->found_excl;
+}
+
+// Fine bucket of a logit: floor((href - x) * sc) + hoff clamped to [0, NB1), computed as a rounding float add (no
+// conversion instruction: that pipe is the exponentials').  A logit exactly on an edge may land in either neighbour;
+// every user keeps a whole bucket of margin.  One function for counting, corrections and thresholds.
+__device__ __forceinline__ int fine_bucket(float x, float href, float sc1, float hoff_minus_half) {
+    const float t = fminf(fmaxf(fmaf(href - x, sc1, hoff_minus_half), 0.0f), (float)(NB1 - 1));
+    return __float_as_int(t + 8388608.0f) - 0x4B000000;
+}
+
 __device__ __forceinline__ u64 ceil_target(float frac, u64 total) {
     const double t = ceil((double)frac * (double)total);
     u64 q = t <= 1.0 ? 1ull : (u64)t;
@@ -903,7 +942,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                         const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            if (e[j] > CI_NEG_INF) atomicAdd(&hist1[max(0, min(NB1 - 1, HOFF + __float2int_rd((lref - e[j]) * SCW)))], 1u);
+                            if (e[j] > CI_NEG_INF) atomicAdd(&hist1[fine_bucket(e[j], lref, SCW, (float)HOFF - 0.5f)], 1u);
                     }
                 }
                 unsigned mk[4], anym = 0;
@@ -1043,6 +1082,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 enum { PATH_PURE = 0, PATH_LIST = 1, PATH_BAND = 2, PATH_FALLBACK = 3 };
                 int path = PATH_PURE;
                 float t_hi = CI_NEG_INF, t_lo = ST_POS_INF;
+                int band_top = 0, band_bot = 0;                  // fine buckets the band covers (from, to)
                 const float SC1 = SCW;
                 // The fine buckets: from pass 1 (laid out from the sample's maximum, HOFF of them above it) or counted now
                 // (from the row's maximum).  Bucket b holds the logits in (edge(b + 1), edge(b)].  A stored logit of a
@@ -1050,7 +1090,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 const bool hist_ready = lref > CI_NEG_INF;
                 const float href = hist_ready ? lref : L;
                 const int hoff = hist_ready ? HOFF : 0;
-                auto bucket1 = [&](float x) { return max(0, min(NB1 - 1, hoff + __float2int_rd((href - x) * SC1))); };
+                auto bucket1 = [&](float x) { return fine_bucket(x, href, SC1, (float)hoff - 0.5f); };
                 auto edge = [&](int b) { return href - (float)(b - hoff) / SC1; };
                 if (need_topk || need_topp) {
                     if (!hist_ready) {
@@ -1079,13 +1119,13 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                     ST_PROF(8);
                     // the histogram counts every finite logit; buckets wholly below the min-p cut are left out of the scans
                     const int b_cut = lcut > CI_NEG_INF ? bucket1(lcut) : NB1 - 1;
-                    auto cnt_of = [&](int i) { return i <= b_cut ? (u64)hist1[i] : 0ull; };
+                    auto one = [](int) { return 1ull; };
                     const float dL = (L - href) / tc;
                     auto mass_est = [&](int i) {
                         return (u64)__float2uint_rn(exp2f(fminf(0.0f, -(((float)(i - hoff) + 0.5f) * (RANGE / (float)NB1) + dL) * CI_LOG2E)) * CI_MASS_SCALE);
                     };
                     int bsel; u64 before, survivors;
-                    bins_find(cnt_of, NB1, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
+                    fine_find(hist1, one, b_cut, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
                     if (need_topk && (u64)kk >= survivors) need_topk = false;   // at most k reach the min-p cut's bucket: top-k removes nothing
                     if (need_topk) {
                         const u64 n_upto = bsel >= 0 ? before + hist1[bsel] : (u64)GLIST + 1;
@@ -1096,25 +1136,27 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                         }
                     } else if (need_topp) {
                         int bp; u64 bef, est_total;
-                        bins_find([&](int i) { return cnt_of(i) * mass_est(i); }, NB1, 0, sc, bp, bef, est_total);
+                        fine_find(hist1, mass_est, b_cut, 0, sc, bp, bef, est_total);
                         if (est_total == 0) path = PATH_FALLBACK;
                         else {
-                            bins_find([&](int i) { return cnt_of(i) * mass_est(i); }, NB1, ceil_target(topp, est_total), sc, bp, bef, est_total);
+                            fine_find(hist1, mass_est, b_cut, ceil_target(topp, est_total), sc, bp, bef, est_total);
                             const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
                             // how far down the list capacity reaches: bucket where the cumulative count gets there
                             int bcap; u64 bef2, tot2;
-                            bins_find(cnt_of, NB1, (u64)768, sc, bcap, bef2, tot2);   // ~24 per warp list of 64
+                            fine_find(hist1, one, b_cut, (u64)768, sc, bcap, bef2, tot2);   // ~24 per warp list of 64
                             if (bp < (hist_ready ? 1 : 0)) path = PATH_FALLBACK;
                             else if (bcap < 0 || bcap > bp + dn + 1) {
                                 // small nucleus: gather everything down to well below the estimated pivot; nothing is "above"
                                 path = PATH_BAND;
                                 t_hi = ST_POS_INF;
                                 t_lo = bcap < 0 ? -ST_FLT_MAX : edge(bcap);
+                                band_top = 0; band_bot = bcap < 0 ? NB1 - 1 : bcap;
                             } else if (bp + dn + 2 >= NB1) path = PATH_FALLBACK;
                             else {
                                 path = PATH_BAND;
                                 t_hi = bp - up <= 0 ? ST_POS_INF : edge(bp - up);
                                 t_lo = edge(bp + dn + 1);
+                                band_top = max(0, bp - up); band_bot = bp + dn;
                             }
                         }
                     }
@@ -1186,6 +1228,8 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 if (!done) {
                     const bool band = path == PATH_BAND;
                     const float lk = fmaxf(lcut, -ST_FLT_MAX);
+                    u64 wkeep = 0;
+                    for (int attempt = 0; attempt < 2; ++attempt) {
                     u64 acc_all = 0, acc_above = 0;
                     int wn = 0;
                     for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
@@ -1195,13 +1239,14 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                            uint32_t q[4];
+                            mass.four(e, lk, q);
+                            acc_all += ((u64)q[0] + q[1]) + ((u64)q[2] + q[3]);   // 64-bit adds: a stored logit of a penalised token may exceed the maximum
                             mk[k] = 0;
+                            if (band) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t q = e[j] >= lk ? mass(e[j]) : 0u;
-                                acc_all += q;
-                                if (band) {
-                                    if (e[j] > t_hi) acc_above += q;
+                                for (int j = 0; j < 4; ++j) {
+                                    if (e[j] > t_hi) acc_above += q[j];
                                     else if (e[j] >= t_lo && e[j] >= lk) mk[k] |= 1u << j;
                                 }
                             }
@@ -1216,7 +1261,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                         }
                     }
                     ST_PROF(11);
-                    u64 wkeep = warp_sum_u64(band ? acc_above : acc_all);   // kept mass of the region known so far
+                    wkeep = warp_sum_u64(band ? acc_above : acc_all);       // kept mass of the region known so far
                     u64 wall_corr = 0;
                     if (corr) {
                         // what the penalised tokens change: their stored logits were summed, their penalised ones count
@@ -1282,10 +1327,45 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                                 wkeep += warp_sum_u64(d);
                             }
                         } else {
-                            // the estimated band missed the pivot (or a list overflowed): exact radix select by mass, then the
+                            status |= COLINFER_ROW_SELECT_SLOW;
+                            if (attempt == 0 && n >= 0 && s1 > 0) {
+                                // The estimated band missed the pivot.  Exact masses of the WIN fine buckets next to the band,
+                                // on the side the pivot lies, give its bucket; the mass pass then runs again around it.
+                                constexpr int WIN = BINS + FB_NB;
+                                u64* win = bins;                             // bins and fb_hist are contiguous
+                                const u64 target = ceil_target(topp, s1);
+                                const int w0 = target <= s_above ? max(0, band_top - WIN + 1) : max(0, band_bot);
+                                for (int i = tid; i < WIN; i += NT) win[i] = 0;
+                                __syncthreads();
+                                u64 hi = 0;
+                                auto put = [&](float x, bool add) {
+                                    if (x >= lk) {
+                                        const u64 q = add ? (u64)mass(x) : 0ull - (u64)mass(x);
+                                        const int b = bucket1(x);
+                                        if (b < w0) hi += q;
+                                        else if (b < w0 + WIN) atomicAdd(reinterpret_cast<unsigned long long*>(&win[b - w0]), (unsigned long long)q);
+                                    }
+                                };
+                                for (int i0 = r_lo; i0 < r_hi; i0 += 128) {
+                                    const float4 v = rw.load4(i0 + lane * 4);
+                                    put(v.x, true); put(v.y, true); put(v.z, true); put(v.w, true);
+                                }
+                                if (corr) for_each_pen([&](int, float r, float e) { put(r, false); put(e, true); });
+                                u64 s_hi;
+                                block_excl_scan(hi, sc, s_hi);
+                                int bw = -1; u64 bef_w = 0, tot_w = 0;
+                                if (target > s_hi) bins_find([&](int i) { return win[i]; }, WIN, target - s_hi, sc, bw, bef_w, tot_w);
+                                __syncthreads();
+                                if (bw >= 0) {
+                                    const int bstar = w0 + bw;
+                                    t_hi = bstar - 1 <= 0 ? ST_POS_INF : edge(bstar - 1);
+                                    t_lo = edge(bstar + 2);
+                                    continue;                                // the mass pass again, around the pivot's bucket
+                                }
+                            }
+                            // a list overflowed, or the pivot lies far from the estimate: exact radix select by mass, then the
                             // regions' kept masses again
                             float lpiv;
-                            status |= COLINFER_ROW_SELECT_SLOW;
                             corr = false; rw.pen_inline = rw.has_pen;
                             if (radix_select(rw, r_lo, r_hi, mass, lcut, true, 0, topp, fb_hist, sc, lpiv))
                                 lcut = fmaxf(lcut, lower_logit_for(scale_logit(lpiv, tc), tc, lpiv));
@@ -1298,6 +1378,8 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                             }
                             wkeep = warp_sum_u64(acc);
                         }
+                    }
+                    break;
                     }
                     rw.pen_inline = rw.has_pen;                 // the rescan of one region applies penalties in place
                     ST_PROF(12);

@@ -490,7 +490,11 @@ def test_config3_full_batch_properties():
     a = m["draw"](logits, sp, pos)
     b = m["draw"](logits, sp, pos)
     assert torch.equal(a, b)
-    rows = [0, 1, 17, 333, 512, 1023]
+    a, st = m["draw"](logits, sp, pos, status=True)
+    assert torch.equal(a, b)
+    # the oracle sample: fixed rows plus every row that took a slower exact path (a missed band estimate, a full list)
+    slow = torch.nonzero(st.reshape(-1) != 0).reshape(-1).tolist()
+    rows = sorted(set([0, 1, 17, 333, 512, 1023] + slow[:10]))
     for r in rows:
         one = m["draw"](logits[r:r + 1].contiguous(), sp.view(r, r + 1), pos[r:r + 1].contiguous())
         assert torch.equal(one[0], a[r])
