@@ -36,9 +36,9 @@ if ROOT not in sys.path:
 V = 151_936
 HIST = 2048
 CPU_SAMPLE_ROWS = 256
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_sample launch divided by its rows (ncu capture at B = 256,
-# summarised in profiles/k_sample_config3_b256_ncu.md; traffic grows in proportion to the rows).
-NCU_TRAFFIC_BYTES_PER_ROW = 644_400
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_sample_stream launch divided by its rows (ncu capture at
+# B = 256, summarised in profiles/k_sample_stream_config3_b256_ncu.md; traffic grows in proportion to the rows).
+NCU_TRAFFIC_BYTES_PER_ROW = 854_600
 
 
 def measured_peak():
@@ -250,7 +250,7 @@ def main():
                        "sharding": f"rows x{world}, ids all-gathered" if world > 1 else "single GPU"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind} copy rate", "frac_of_nominal_8000": achieved / 8000.0,
-                         "bytes_per_row": bytes_row, "kernel": "k_sample", "kernel_ms": kernel_ms,
+                         "bytes_per_row": bytes_row, "kernel": "k_sample_stream", "kernel_ms": kernel_ms,
                          "traffic": None if NCU_TRAFFIC_BYTES_PER_ROW is None else NCU_TRAFFIC_BYTES_PER_ROW * B},
             "e2e": {"value": n_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "steps": e2e_steps,
                     "h2d_bytes_per_step": int(h_logits.numel() * 4 + h_hist.numel() * 4 + h_pos.numel() * 4),

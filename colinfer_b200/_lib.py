@@ -11,8 +11,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libcolinfer_b200.so")
 
 F32, BF16 = 0, 1
-FORCE_DISTRIBUTION = 1
 ROW_DEGENERATE, ROW_TIMEOUT, ROW_HIST_SLOW, ROW_SELECT_SLOW = 1, 2, 4, 8
+FORCE_DISTRIBUTION, TEST_MISS_BAND = 1, 0x4000
 
 
 class SamplerParamsC(C.Structure):

@@ -1157,6 +1157,13 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                                 t_hi = bp - up <= 0 ? ST_POS_INF : edge(bp - up);
                                 t_lo = edge(bp + dn + 1);
                                 band_top = max(0, bp - up); band_bot = bp + dn;
+                                if (a.flags & COLINFER_TEST_MISS_BAND) {     // test hook: a band eight buckets off (above or below by row parity)
+                                    const int sh = (row & 1) ? 8 : -8;
+                                    if (bp - up + sh > 0 && bp + dn + sh + 2 < NB1) {
+                                        t_hi = edge(bp - up + sh); t_lo = edge(bp + dn + 1 + sh);
+                                        band_top = bp - up + sh; band_bot = bp + dn + sh;
+                                    }
+                                }
                             }
                         }
                     }

@@ -101,14 +101,15 @@ def inverse_cdf(P: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
 
 
 def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | None = None,
-         u: torch.Tensor | None = None, status: bool = False, stats: bool = False):
+         u: torch.Tensor | None = None, status: bool = False, stats: bool = False, flags: int = 0):
     """logits [B, R, V] fp32 (or bf16): row r of slot b predicts the token at position pos[b] + r.
     p: SamplerParams for the B slots.  Returns the sampled tokens [B, R] int64 (argmax for slots with temperature 0).
     (engine/spec/accept.py:43-52)
 
     mask [B, R, W] int32: grammar bitmask applied inside the same pass (what apply_mask would do first).
     u [B, R] fp32: explicit uniforms in (0, 1] instead of Philox(seed, pos).
-    status / stats: also return the per-row status words int32 [B, R] / the raw row statistics uint8 [B, R, 32]."""
+    status / stats: also return the per-row status words int32 [B, R] / the raw row statistics uint8 [B, R, 32].
+    flags: COLINFER_* flag bits of colinfer_sample (test hooks)."""
     if logits.dim() != 3:
         raise RuntimeError("logits [B, R, V]")
     check_tensor(logits, None, "logits")
@@ -143,7 +144,7 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
     rs = torch.empty(B, R, _lib.ROW_STATS_BYTES, dtype=torch.uint8, device=logits.device) if stats else None
     _lib.check(_lib.lib().colinfer_sample(logits.data_ptr(), dt, mask_ptr, mask_rows, W, C.byref(ps), pos_ptr, pos_i64,
                                           u_ptr, out.data_ptr(), rs.data_ptr() if stats else None,
-                                          st.data_ptr() if status else None, B, R, V, 0, _stream()), "draw")
+                                          st.data_ptr() if status else None, B, R, V, int(flags), _stream()), "draw")
     if status or stats:
         return (out,) + ((st,) if status else ()) + ((rs,) if stats else ())
     return out

@@ -57,7 +57,9 @@ enum { COLINFER_F32 = 0, COLINFER_BF16 = 1 };
 
 /* Flags of colinfer_sample. */
 enum {
-    COLINFER_FORCE_DISTRIBUTION = 1  /* build the distribution even for temperature <= 0 (processed_probs does) */
+    COLINFER_FORCE_DISTRIBUTION = 1, /* build the distribution even for temperature <= 0 (processed_probs does) */
+    COLINFER_TEST_MISS_BAND = 0x4000 /* test hook: misplace the estimated top-p band so that the exact retry paths run;
+                                        results are unchanged, rows report COLINFER_ROW_SELECT_SLOW */
 };
 
 /* Replaces ops().philox_uniform (csrc/sampling.cu:25-35, csrc/bindings.cpp:538-544):

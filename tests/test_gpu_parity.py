@@ -511,6 +511,33 @@ def test_config3_full_batch_properties():
     assert int(a.min()) >= 0 and int(a.max()) < V
 
 
+def test_missed_band_estimate_retries_exactly():
+    """The top-p band is an estimate; with the test hook it is misplaced (above the pivot on odd rows, below on even
+    ones): the exact window pass must find the pivot's bucket and the tokens must not change."""
+    m = mods()
+    V = wl.V_QWEN
+    w = wl.config3(32)
+    w["params"]["top_k"][:] = V                                     # top-p rows only
+    dev = "cuda"
+    logits, pos = w["logits"].to(dev), w["pos"].to(dev)
+    for strip in (False, True):
+        pr = dict(w["params"])
+        if strip:
+            for k in ("history", "hist_len", "repetition_penalty", "presence_penalty", "frequency_penalty"):
+                pr.pop(k)
+        sp = wl.sampler_params(pr, V, dev)
+        a, sa = m["draw"](logits, sp, pos, status=True)
+        b, sb = m["draw"](logits, sp, pos, status=True, flags=_lib.TEST_MISS_BAND)
+        assert torch.equal(a, b)
+        assert int((sb & _lib.ROW_SELECT_SLOW).ne(0).sum()) >= 24   # the hook took effect
+        assert int((sa & _lib.ROW_SELECT_SLOW).ne(0).sum()) <= 2
+    want, info = O.draw(w["logits"].numpy(), np_params(w["params"]), w["pos"].numpy(),
+                        history=w["params"]["history"].numpy(), hist_len=w["params"]["hist_len"].numpy())
+    sp = wl.sampler_params(w["params"], V, dev)
+    got = m["draw"](logits, sp, pos, flags=_lib.TEST_MISS_BAND)
+    check_tokens(got.cpu().numpy(), want, info, "missed band")
+
+
 def test_config4_bf16_large_vocab():
     w = wl.config4(B=6)
     nb, out = run_workload(w, wl.V_LARGE, use_philox=True)
