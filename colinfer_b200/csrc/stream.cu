@@ -73,6 +73,7 @@ struct Sc {
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
     int my_rows[BAL_MINE];
+    u64 wsum2[NWA], woff2[NWA], wtotal2; int fb[3]; u64 fe[3];   // second scan and the three finds of fine_decide
     int x_warp; u64 x_off; u64 step_sum[XSTEPS];   // the draw's region, walked by all warps
     int glist_n;
 };
@@ -120,37 +121,6 @@ __device__ void bins_find(F get, int nbins, u64 target, Sc* sc, int& bin, u64& b
     before = sc->found_excl;
 }
 
-// bins_find over the NB1 fine buckets with weights: value(i) = hist[i] * w(i) for i <= last, 0 beyond.  Each thread owns
-// NB1 / NT consecutive buckets and reads them with 128-bit loads (scalar loads at that stride conflict eightfold).
-template <class W>
-__device__ void fine_find(const uint32_t* hist, W w, int last, u64 target, Sc* sc, int& bin, u64& before, u64& total) {
-    constexpr int PER = NB1 / NT;
-    static_assert(PER % 4 == 0, "128-bit loads");
-    const int lo = threadIdx.x * PER;
-    uint32_t c[PER];
-#pragma unroll
-    for (int t = 0; t < PER; t += 4) {
-        const uint4 x = *reinterpret_cast<const uint4*>(hist + lo + t);
-        c[t] = x.x; c[t + 1] = x.y; c[t + 2] = x.z; c[t + 3] = x.w;
-    }
-    u64 s = 0;
-#pragma unroll
-    for (int t = 0; t < PER; ++t) s += (lo + t <= last && c[t]) ? (u64)c[t] * w(lo + t) : 0ull;
-    const u64 excl = block_excl_scan(s, sc, total);
-    if (excl < target && target <= excl + s) {
-        u64 run = excl;
-#pragma unroll
-        for (int t = 0; t < PER; ++t) {
-            const u64 b = (lo + t <= last && c[t]) ? (u64)c[t] * w(lo + t) : 0ull;
-            if (run + b >= target) { sc->found = lo + t; sc->found_excl = run; break; }
-            run += b;
-        }
-    }
-    __syncthreads();
-    bin = sc->found;
-    before = sc->found_excl;
-}
-
 // Fine bucket of a logit: floor((href - x) * sc) + hoff clamped to [0, NB1), computed as a rounding float add (no
 // conversion instruction: that pipe is the exponentials').  A logit exactly on an edge may land in either neighbour;
 // every user keeps a whole bucket of margin.  One function for counting, corrections and thresholds.
@@ -163,6 +133,65 @@ __device__ __forceinline__ u64 ceil_target(float frac, u64 total) {
     const double t = ceil((double)frac * (double)total);
     u64 q = t <= 1.0 ? 1ull : (u64)t;
     return q > total ? total : q;
+}
+
+// One pass over the fine histogram for everything the path decision needs: the bucket of the kk-th largest count, the
+// bucket where the running count reaches cap, and the bucket where the running estimated mass reaches topp of its
+// total.  Two prefix scans share the two block barriers.  Buckets beyond `last` count nothing.
+struct FineDecision { int b_k; u64 before_k; u64 total_cnt; int b_cap; int b_p; u64 est_total; };
+template <class W>
+__device__ FineDecision fine_decide(const uint32_t* hist, W west, int last, u64 kk_target, u64 cap_target, float topp, bool want_p, Sc* sc) {
+    constexpr int PER = NB1 / NT;
+    const int lane = lane_id(), warp = warp_id();
+    const int lo = threadIdx.x * PER;
+    uint32_t c[PER];
+#pragma unroll
+    for (int t = 0; t < PER; t += 4) {
+        const uint4 x = *reinterpret_cast<const uint4*>(hist + lo + t);
+        c[t] = x.x; c[t + 1] = x.y; c[t + 2] = x.z; c[t + 3] = x.w;
+    }
+    u64 sc_c = 0, sc_e = 0;
+#pragma unroll
+    for (int t = 0; t < PER; ++t) {
+        if (lo + t <= last && c[t]) { sc_c += c[t]; if (want_p) sc_e += (u64)c[t] * west(lo + t); } else c[t] = 0;
+    }
+    const u64 in_c = warp_incl_scan_u64(sc_c, lane), in_e = warp_incl_scan_u64(sc_e, lane);
+    if (lane == 31) { sc->wsum[warp] = in_c; sc->wsum2[warp] = in_e; }
+    __syncthreads();
+    if (warp == 0) {
+        const u64 w1 = sc->wsum[lane], w2 = sc->wsum2[lane];
+        const u64 i1 = warp_incl_scan_u64(w1, lane), i2 = warp_incl_scan_u64(w2, lane);
+        sc->woff[lane] = i1 - w1; sc->woff2[lane] = i2 - w2;
+        if (lane == 31) { sc->wtotal = i1; sc->wtotal2 = i2; }
+        if (lane < 3) sc->fb[lane] = -1;
+    }
+    __syncthreads();
+    FineDecision o;
+    o.total_cnt = sc->wtotal; o.est_total = sc->wtotal2;
+    const u64 ex_c = sc->woff[warp] + in_c - sc_c, ex_e = sc->woff2[warp] + in_e - sc_e;
+    const u64 t_p = (want_p && o.est_total > 0) ? ceil_target(topp, o.est_total) : 0ull;
+    if (kk_target && ex_c < kk_target && kk_target <= ex_c + sc_c) {
+        u64 run = ex_c;
+#pragma unroll
+        for (int t = 0; t < PER; ++t) { if (run + c[t] >= kk_target) { sc->fb[0] = lo + t; sc->fe[0] = run; break; } run += c[t]; }
+    }
+    if (cap_target && ex_c < cap_target && cap_target <= ex_c + sc_c) {
+        u64 run = ex_c;
+#pragma unroll
+        for (int t = 0; t < PER; ++t) { if (run + c[t] >= cap_target) { sc->fb[1] = lo + t; break; } run += c[t]; }
+    }
+    if (t_p && ex_e < t_p && t_p <= ex_e + sc_e) {
+        u64 run = ex_e;
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+            const u64 b = c[t] ? (u64)c[t] * west(lo + t) : 0ull;
+            if (run + b >= t_p) { sc->fb[2] = lo + t; break; }
+            run += b;
+        }
+    }
+    __syncthreads();
+    o.b_k = sc->fb[0]; o.before_k = sc->fe[0]; o.b_cap = sc->fb[1]; o.b_p = sc->fb[2];
+    return o;
 }
 
 __device__ __forceinline__ float row_uniform(const Args& a, int row, int b, int r) {
@@ -705,7 +734,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
     long long prof_last = clock64();
     if (a.prof && tid == 0) for (int i = 0; i < 16; ++i) sc->prof[i] = 0;
     if (tid < NWA) {                                             // neutral values for the warps a smaller CTA does not have
-        sc->wsum[tid] = 0; sc->wmass[tid] = 0; sc->wf[tid] = CI_NEG_INF; sc->wi[tid] = 0x7fffffff; sc->wcount[tid] = 0;
+        sc->wsum[tid] = 0; sc->wsum2[tid] = 0; sc->wmass[tid] = 0; sc->wf[tid] = CI_NEG_INF; sc->wi[tid] = 0x7fffffff; sc->wcount[tid] = 0;
         sc->wtw[tid] = -ST_FLT_MAX; sc->wmin[tid] = ST_POS_INF;
     }
     __syncthreads();
@@ -1119,31 +1148,26 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                     ST_PROF(8);
                     // the histogram counts every finite logit; buckets wholly below the min-p cut are left out of the scans
                     const int b_cut = lcut > CI_NEG_INF ? bucket1(lcut) : NB1 - 1;
-                    auto one = [](int) { return 1ull; };
                     const float dL = (L - href) / tc;
                     auto mass_est = [&](int i) {
                         return (u64)__float2uint_rn(exp2f(fminf(0.0f, -(((float)(i - hoff) + 0.5f) * (RANGE / (float)NB1) + dL) * CI_LOG2E)) * CI_MASS_SCALE);
                     };
-                    int bsel; u64 before, survivors;
-                    fine_find(hist1, one, b_cut, need_topk ? (u64)kk : 0ull, sc, bsel, before, survivors);
-                    if (need_topk && (u64)kk >= survivors) need_topk = false;   // at most k reach the min-p cut's bucket: top-k removes nothing
+                    // 768: how far down the list capacity reaches (~24 per warp list of 64)
+                    const FineDecision fd = fine_decide(hist1, mass_est, b_cut, need_topk ? (u64)kk : 0ull, 768ull, topp, need_topp, sc);
+                    const int bsel = fd.b_k;
+                    if (need_topk && (u64)kk >= fd.total_cnt) need_topk = false;   // at most k reach the min-p cut's bucket: top-k removes nothing
                     if (need_topk) {
-                        const u64 n_upto = bsel >= 0 ? before + hist1[bsel] : (u64)GLIST + 1;
+                        const u64 n_upto = bsel >= 0 ? fd.before_k + hist1[bsel] : (u64)GLIST + 1;
                         if (bsel < (hist_ready ? 1 : 0) || bsel >= NB1 - 3 || n_upto > GLIST - 64) path = PATH_FALLBACK;   // bucket 0 of a pass-1 histogram may mix logits from far above the sample's maximum
                         else {
                             path = PATH_LIST;
                             t_lo = edge(bsel + 2) - 0.01f / SC1 - fabsf(href) * 1e-6f;
                         }
                     } else if (need_topp) {
-                        int bp; u64 bef, est_total;
-                        fine_find(hist1, mass_est, b_cut, 0, sc, bp, bef, est_total);
-                        if (est_total == 0) path = PATH_FALLBACK;
+                        const int bp = fd.b_p, bcap = fd.b_cap;
+                        if (fd.est_total == 0) path = PATH_FALLBACK;
                         else {
-                            fine_find(hist1, mass_est, b_cut, ceil_target(topp, est_total), sc, bp, bef, est_total);
                             const int up = a.dtype == COLINFER_BF16 ? 3 : 1, dn = a.dtype == COLINFER_BF16 ? 4 : 2;
-                            // how far down the list capacity reaches: bucket where the cumulative count gets there
-                            int bcap; u64 bef2, tot2;
-                            fine_find(hist1, one, b_cut, (u64)768, sc, bcap, bef2, tot2);   // ~24 per warp list of 64
                             if (bp < (hist_ready ? 1 : 0)) path = PATH_FALLBACK;
                             else if (bcap < 0 || bcap > bp + dn + 1) {
                                 // small nucleus: gather everything down to well below the estimated pivot; nothing is "above"
