@@ -68,7 +68,7 @@ struct Sc {
     int wcount[NWA], woffs[NWA + 1];
     float bc_f; int bc_i;
     float wtw[NWA], wmin[NWA];     // running top-k: each warp's threshold and smallest list entry
-    float fin_lo; int fin_bstar, fin_n, fin_ok, fin_all;
+    int fin_ok;
     uint32_t fc_idx[FCAP]; float fc_l[FCAP];
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
@@ -433,68 +433,55 @@ __device__ __forceinline__ void warp_append_batch(Cand* mylist, int& wn, const u
     wn = base;
 }
 
+// Bin of a BINS-bin count histogram in which the running count reaches kk, or -1; computed by the calling warp alone
+// (every warp of the block gets the same answer, so no broadcast and no barrier follow).  `run`: count down to and
+// including that bin.
+__device__ __forceinline__ int warp_count_bin(const uint32_t* hist, uint32_t kk, int lane, uint32_t& run_out) {
+    constexpr int PERB = BINS / 32;
+    uint32_t h[PERB]; uint32_t s = 0;
+#pragma unroll
+    for (int t = 0; t < PERB; t += 4) {
+        const uint4 x = *reinterpret_cast<const uint4*>(hist + lane * PERB + t);
+        h[t] = x.x; h[t + 1] = x.y; h[t + 2] = x.z; h[t + 3] = x.w;
+        s += x.x + x.y + x.z + x.w;
+    }
+    uint32_t incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t x = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += x; }
+    const uint32_t all = __shfl_sync(0xffffffffu, incl, 31);
+    if (all < kk) { run_out = all; return -1; }
+    const unsigned hit = __ballot_sync(0xffffffffu, incl >= kk);
+    const int hl = __ffs(hit) - 1;
+    uint32_t run = incl - s; int b = lane * PERB;
+#pragma unroll
+    for (int t = 0; t < PERB; ++t) { if (run + h[t] >= kk) { b = lane * PERB + t; run += h[t]; break; } run += h[t]; }
+    run_out = __shfl_sync(0xffffffffu, run, hl);
+    return __shfl_sync(0xffffffffu, b, hl);
+}
+
 // Top-k (kk <= FASTK), then top-p and the draw, from the warps' running lists after the single pass over the row.
 // The union of the lists holds every logit >= lo (lo: the largest warp threshold; the smallest listed value when no
 // warp compacted).  BINS linear bins over [lo, L] find the bin of the kk-th largest; the entries down to that bin, at
 // most FCAP and in token order, go to warp 0, which finishes exactly by bisection on the ordered keys.
 // False: the caller takes the general path.  All threads call.
-__device__ bool finish_running_topk(const Cand* ownlist, int wn, float tw, float L, float lcut_in, float tc, const MassFn& mass,
+__device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo, float L, float lcut_in, float tc, const MassFn& mass,
                                     int kk, bool need_topp, float topp, float u, uint32_t* hist, Sc* sc,
                                     long long& token, float& lcut, u64& total) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const Cand* mine = ownlist + warp * WLIST;
-    // lo: valid lower bound of the kk-th largest, else the smallest listed value
-    float mn = ST_POS_INF;
-    const bool have_tw = tw > -ST_FLT_MAX;
-    if (!have_tw) for (int j = lane; j < wn; j += 32) mn = fminf(mn, mine[j].l);
-#pragma unroll
-    for (int o = 16; o; o >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-    if (lane == 0) { sc->wtw[warp] = tw; sc->wmin[warp] = mn; sc->wcount[warp] = wn; }
-    for (int i = tid; i < BINS; i += NT) hist[i] = 0u;
-    __syncthreads();
-    if (warp == 0) {
-        float t = sc->wtw[lane], m2 = sc->wmin[lane];
-        int c = sc->wcount[lane];
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
-            m2 = fminf(m2, __shfl_xor_sync(0xffffffffu, m2, o));
-            c += __shfl_xor_sync(0xffffffffu, c, o);
-        }
-        if (lane == 0) { sc->fin_lo = t > -ST_FLT_MAX ? t : m2; sc->fin_all = !(t > -ST_FLT_MAX); sc->fin_n = c; sc->fin_ok = 0; sc->fin_bstar = -1; }
-    }
-    __syncthreads();
-    const float lo = sc->fin_lo;
-    if (sc->fin_n < 1 || !(lo <= L)) return false;
+    if (!(lo <= L)) return false;
     const float scale = L > lo ? (float)(BINS - 2) / (L - lo) : 0.0f;
     auto bin_of = [&](float l) { return min(BINS - 1, __float2int_rz((L - l) * scale)); };
     for (int j = lane; j < wn; j += 32) { const float l = mine[j].l; if (l >= lo) atomicAdd(&hist[bin_of(l)], 1u); }
+    if (tid == 0) sc->fin_ok = 0;
     __syncthreads();
-    if (warp == 0) {
-        // bin where the running count reaches kk (or the last populated bin when fewer than kk are listed)
-        constexpr int PERB = BINS / 32;
-        uint32_t h[PERB]; uint32_t s = 0;
-#pragma unroll
-        for (int t = 0; t < PERB; ++t) { h[t] = hist[lane * PERB + t]; s += h[t]; }
-        uint32_t incl = s;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const uint32_t x = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += x; }
-        const uint32_t all = __shfl_sync(0xffffffffu, incl, 31);
-        const uint32_t want = (all >= (uint32_t)kk || sc->fin_all) ? min((uint32_t)kk, all) : 0u;   // a bound with fewer than kk above it is no bound
-        const unsigned hit = __ballot_sync(0xffffffffu, incl >= want);
-        if (want > 0 && lane == __ffs(hit) - 1) {
-            uint32_t run = incl - s; int b = lane * PERB;
-#pragma unroll
-            for (int t = 0; t < PERB; ++t) { if (run + h[t] >= want) { b = lane * PERB + t; run += h[t]; break; } run += h[t]; }
-            sc->fin_bstar = b; sc->fin_n = (int)run;                 // run: entries down to and including bin b
-        }
-    }
-    __syncthreads();
-    const int bstar = sc->fin_bstar, nc = sc->fin_n;
-    if (bstar < 0 || nc > FCAP) return false;
-    // every row element in bins <= bstar is a candidate: always when no warp dropped anything, else while bstar stays
-    // clear of the bins around lo
-    const bool complete = bstar <= BINS - 4 || sc->fin_all;
+    uint32_t run_b;
+    const int bstar = warp_count_bin(hist, (uint32_t)kk, lane, run_b);   // every warp scans the bins itself
+    if (bstar < 0) return false;                                     // a bound with fewer than kk above it is no bound
+    const int nc = (int)run_b;                                       // entries down to and including bin bstar
+    if (nc > FCAP) return false;
+    // every row element in bins <= bstar is a candidate while bstar stays clear of the bins around lo
+    const bool complete = bstar <= BINS - 4;
     // candidates in token order: warps in order, entries in list order
     {
         int cnt = 0;
@@ -520,6 +507,10 @@ __device__ bool finish_running_topk(const Cand* ownlist, int wn, float tw, float
     if (warp == 0) {
         constexpr int PERC = FCAP / 32;
         float l[PERC]; uint32_t key[PERC], q[PERC];
+        // the candidates' ordered keys share the bits above the highest one in which key(lo) and key(L) differ
+        const uint32_t kd = f2key(L) ^ f2key(lo);
+        const int top = kd ? 31 - __clz(kd) : -1;
+        const uint32_t pre0 = top >= 0 ? (f2key(L) & ~((2u << top) - 1u)) : f2key(L);
         int surv = 0;
 #pragma unroll
         for (int t = 0; t < PERC; ++t) {
@@ -532,9 +523,9 @@ __device__ bool finish_running_topk(const Cand* ownlist, int wn, float tw, float
         float cut = lcut_in;
         bool ok = surv > 0;
         if (ok && kk <= surv) {                                      // else fewer than k survive min-p: top-k removes nothing
-            uint32_t pre = 0;
+            uint32_t pre = pre0;
 #pragma unroll 1
-            for (int bit = 31; bit >= 0; --bit) {
+            for (int bit = top; bit >= 0; --bit) {
                 const uint32_t c = pre | (1u << bit);
                 int n = 0;
 #pragma unroll
@@ -557,9 +548,9 @@ __device__ bool finish_running_topk(const Cand* ownlist, int wn, float tw, float
             const u64 s1 = warp_sum_u64(s);
             ok = s1 > 0;
             const u64 target = ceil_target(topp, s1);
-            uint32_t pre = 0;
+            uint32_t pre = pre0;
 #pragma unroll 1
-            for (int bit = 31; bit >= 0; --bit) {
+            for (int bit = top; bit >= 0; --bit) {
                 const uint32_t c = pre | (1u << bit);
                 u64 w = 0;
 #pragma unroll
@@ -947,9 +938,9 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 for (int k = 0; k < 4; ++k)
                     if (gm[k] > CI_NEG_INF && lref < ST_POS_INF) atomicAdd(&hist1[min(BINS - 1, __float2int_rz((lref - gm[k]) * FAST_SCALE))], 1u);
                 __syncthreads();
-                int bk; u64 before, have;
-                bins_find([&](int i) { return (u64)hist1[i]; }, BINS, (u64)kq, sc, bk, before, have);
-                if (have >= (u64)kq && bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
+                uint32_t have;
+                const int bk = warp_count_bin(hist1, (uint32_t)kq, lane, have);
+                if (bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
             } else {
                 tw = ST_POS_INF;                                 // nothing to list
             }
@@ -1033,6 +1024,10 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             }
         }
         if (patch && !from_lists) lref = CI_NEG_INF;             // the histogram of this pass counted stored logits: void
+        if (fastk) {                                             // bins of the finish (the reduce below has the barriers after)
+            __syncthreads();                                     // every warp has read the sample's bins
+            for (int i = tid; i < BINS; i += NT) hist1[i] = 0u;
+        }
         if (!from_lists && lpos >= 0) {
             const float4 v = rw.load4(lpos);
             lidx = lpos + (v.x == lmax ? 0 : v.y == lmax ? 1 : v.z == lmax ? 2 : 3);
@@ -1083,7 +1078,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             // -------------------------------------------------------------------------------- small top-k: finish from the running lists
             if (fastk) {
                 ST_PROF(4);
-                if (!__syncthreads_or(fk_bad) &&
+                if (!__syncthreads_or(fk_bad || !(tw > -ST_FLT_MAX)) &&
                     finish_running_topk(ownlist, wn1, tw, L, lcut, tc, mass, kk, need_topp, topp, u, hist1, sc, token, lcut, total_mass))
                     done = true;
                 __syncthreads();
