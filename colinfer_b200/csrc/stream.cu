@@ -1503,7 +1503,7 @@ int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, i
                            int64_t* out_ids, colinfer_row_stats* stats, int32_t* status, int B, int R, int V, int flags,
                            cudaStream_t stream) {
     const int smem = stream_smem_bytes(V);
-    if (smem > 226 * 1024 || V > 32 * 128 * strm::XSTEPS) return (int)cudaErrorInvalidValue;
+    if (smem > 226 * 1024 || V > strm::NW * 128 * strm::XSTEPS) return (int)cudaErrorInvalidValue;
     const bool vec = dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)logits) & 15) == 0;
     static int sm_count[64] = {};
     int dev = 0;
