@@ -38,7 +38,7 @@ HIST = 2048
 CPU_SAMPLE_ROWS = 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_sample_stream launch divided by its rows (ncu capture at
 # B = 256, summarised in profiles/k_sample_stream_config3_b256_ncu.md; traffic grows in proportion to the rows).
-NCU_TRAFFIC_BYTES_PER_ROW = 854_600
+NCU_TRAFFIC_BYTES_PER_ROW = 703_100
 
 
 def measured_peak():
@@ -138,6 +138,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1024, help="rows per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cluster", type=int, default=0,
+                    help="0: the default streaming kernel; 1/2/4/8: the cluster-resident kernel with that cluster size")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -150,6 +152,7 @@ def main():
     from colinfer_b200.spec.accept import draw
 
     _lib.lib()                                             # fail loudly if the CUDA library is missing
+    _lib.lib().colinfer_set_cluster_override(args.cluster)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -250,8 +253,8 @@ def main():
                        "sharding": f"rows x{world}, ids all-gathered" if world > 1 else "single GPU"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind} copy rate", "frac_of_nominal_8000": achieved / 8000.0,
-                         "bytes_per_row": bytes_row, "kernel": "k_sample_stream", "kernel_ms": kernel_ms,
-                         "traffic": None if NCU_TRAFFIC_BYTES_PER_ROW is None else NCU_TRAFFIC_BYTES_PER_ROW * B},
+                         "bytes_per_row": bytes_row, "kernel": "k_sample" if args.cluster else "k_sample_stream", "kernel_ms": kernel_ms,
+                         "traffic": None if args.cluster else NCU_TRAFFIC_BYTES_PER_ROW * B},
             "e2e": {"value": n_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "steps": e2e_steps,
                     "h2d_bytes_per_step": int(h_logits.numel() * 4 + h_hist.numel() * 4 + h_pos.numel() * 4),
                     "d2h_bytes_per_step": int(h_ids.numel() * 8)},
