@@ -46,6 +46,8 @@ SIGNATURES = {
     "colinfer_spec_verify": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.POINTER(SamplerParamsC),
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_logprobs": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_int, C.c_int, C.c_void_p]),
     "colinfer_spec_verify_stats_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_spec_verify_ids_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.POINTER(Geometry)]),

@@ -149,6 +149,13 @@ int colinfer_set_profile_buffer(void* dev, int ctas);
 /* How many clusters of the sampler's geometry for this vocabulary the current device holds at once (occupancy query). */
 int colinfer_max_active_clusters(int V, int dtype);
 
+/* Replaces Scheduler._logprobs (engine/runtime/scheduler.py:714-722: log_softmax + gather + topk on the RAW logits of
+ * the positions that produced the emitted tokens).  logits [rows, V] fp32 or bf16; toks [rows] int64 (NULL: no chosen
+ * logprob); chosen [rows] fp32 = log_softmax(row)[tok]; top_ids / top_lp [rows, n_top]: the n_top (0 .. 32) most likely
+ * tokens in descending order (equal logits: lower token first) with their logprobs.  One pass over each row. */
+int colinfer_logprobs(const void* logits, int dtype, const int64_t* toks, int n_top, float* chosen, int64_t* top_ids,
+                      float* top_lp, int rows, int V, void* stream);
+
 /* Library version (major * 100 + minor). */
 int colinfer_version(void);
 

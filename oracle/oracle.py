@@ -339,3 +339,26 @@ def spec_verify_reject(target_logits, draft_logits, draft_ids, temperature, top_
             res = p
         tok, margin = inverse_cdf_row(res, us[j])
         return dict(n_accept=j, token=tok, margin=margin, accept_margin=accept_margin)
+
+
+# ------------------------------------------------------------------------------------------------ logprobs
+def logprobs(rows, toks, n_top):
+    """Logprob of each emitted token and the n_top most likely alternatives, from the RAW logits of the positions that
+    produced them (engine/runtime/scheduler.py:714-722: log_softmax, gather, topk).
+
+    rows [r, V], toks [r], n_top >= 0.  Returns (chosen float64 [r], top_ids int64 [r, n_top], top_lp float64
+    [r, n_top]); alternatives in descending order, equal values in ascending token order (torch.topk leaves the order
+    of ties open; the tests compare tie groups as sets).  log-sum-exp in float64."""
+    x = np.asarray(rows, dtype=np.float64)
+    r, V = x.shape
+    m = np.max(x, axis=1, keepdims=True)
+    m = np.where(np.isfinite(m), m, 0.0)
+    lse = m[:, 0] + np.log(np.sum(np.exp(x - m), axis=1))
+    lsm = x - lse[:, None]
+    chosen = lsm[np.arange(r), np.asarray(toks, dtype=np.int64)]
+    top_ids = np.zeros((r, n_top), dtype=np.int64)
+    top_lp = np.zeros((r, n_top), dtype=np.float64)
+    for i in range(r):
+        order = np.lexsort((np.arange(V), -x[i]))[:n_top]           # value descending, then index ascending
+        top_ids[i], top_lp[i] = order, lsm[i, order]
+    return chosen, top_ids, top_lp

@@ -7,6 +7,7 @@ colinfer checkout (default /root/reference; nothing is written there and engine.
 The .npz holds the inputs and the reference's outputs; the tests compare the oracle and the CUDA kernels with them.
 processed_probs / draw cannot run without a GPU (FlashInfer) and are pinned by the reference's known-answer vectors
 instead (tests/test_spec_accept.py:39-48 of the reference, restated in tests/test_oracle.py).
+Also writes tests/golden/ref_logprobs.npz from engine.runtime.scheduler.Scheduler._logprobs.
 """
 import math
 import os
@@ -80,3 +81,32 @@ out["view_top_k"] = v.top_k.numpy()
 dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_cpu_vectors.npz")
 np.savez_compressed(dst, **out)
 print("wrote", dst, {k: v.shape for k, v in out.items()})
+
+# Logprobs of emitted tokens: Scheduler._logprobs (engine/runtime/scheduler.py:714-722) is a pure torch function of
+# its arguments and runs on a CPU.  Small rows are stored; the full-vocabulary rows are regenerated from their seed.
+from engine.runtime.scheduler import Scheduler  # noqa: E402
+lp = {}
+g2 = torch.Generator().manual_seed(99)
+rows = torch.randn(5, 1000, generator=g2) * 4
+rows[1, 10:14] = rows[1].max() + 1.0            # a four-way tie at the top
+rows[2, ::3] = -math.inf                        # masked-out logits
+toks = [3, 11, 4, 999, 0]
+res = Scheduler._logprobs(None, rows, toks, 5)
+lp["small_rows"], lp["small_toks"] = rows.numpy(), np.array(toks)
+lp["small_chosen"] = np.array([r[0] for r in res], dtype=np.float64)
+lp["small_top_ids"] = np.array([[t[0] for t in r[1]] for r in res], dtype=np.int64)
+lp["small_top_lp"] = np.array([[t[1] for t in r[1]] for r in res], dtype=np.float64)
+g3 = torch.Generator().manual_seed(2024)
+big = torch.randn(3, 151936, generator=g3) * 2.5
+btoks = [151935, 0, 77777]
+res = Scheduler._logprobs(None, big, btoks, 20)
+lp["big_seed"], lp["big_toks"] = np.array([2024]), np.array(btoks)
+lp["big_chosen"] = np.array([r[0] for r in res], dtype=np.float64)
+lp["big_top_ids"] = np.array([[t[0] for t in r[1]] for r in res], dtype=np.int64)
+lp["big_top_lp"] = np.array([[t[1] for t in r[1]] for r in res], dtype=np.float64)
+res0 = Scheduler._logprobs(None, rows, toks, 0)
+lp["small_chosen_n0"] = np.array([r[0] for r in res0], dtype=np.float64)
+assert all(r[1] == [] for r in res0)
+dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_logprobs.npz")
+np.savez_compressed(dst, **lp)
+print("wrote", dst, {k: v.shape for k, v in lp.items()})

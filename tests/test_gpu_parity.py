@@ -646,3 +646,65 @@ def test_spec_verify_preserves_the_target_distribution():
     emp = torch.bincount(out[:, 0], minlength=V).double().cpu() / B
     p = torch.softmax(tl[0, 0].double(), -1)
     assert 0.5 * (emp - p).abs().sum().item() < 0.02
+
+
+# ------------------------------------------------------------------------------------------------ logprobs of emitted tokens
+def _check_logprobs(rows, toks, n_top, tol=2e-5):
+    from colinfer_b200.runtime.logprobs import logprobs_tensors
+    from test_oracle import _tie_groups_equal
+    chosen, ids, lps = logprobs_tensors(rows.cuda().contiguous(), torch.tensor(toks, dtype=torch.int64, device="cuda"), n_top)
+    wc, wi, wl_ = O.logprobs(rows.float().numpy(), np.asarray(toks), n_top)
+    got_c = chosen.cpu().numpy().astype(np.float64)
+    both_inf = np.isinf(got_c) & np.isinf(wc)
+    with np.errstate(invalid="ignore"):
+        assert np.all(both_inf | (np.abs(got_c - wc) <= tol)), (got_c, wc)
+    for r in range(rows.size(0)):
+        _tie_groups_equal(ids[r].cpu().numpy(), lps[r].cpu().numpy(), wi[r], wl_[r], tol)
+    return chosen, ids, lps
+
+
+def test_logprobs_match_reference_vectors_on_gpu():
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_logprobs.npz"))
+    from colinfer_b200.runtime.logprobs import logprobs
+    from test_oracle import _tie_groups_equal
+    res = logprobs(torch.from_numpy(g["small_rows"]).cuda(), g["small_toks"].tolist(), 5)
+    for r, (lp, alts) in enumerate(res):
+        assert abs(lp - g["small_chosen"][r]) <= 2e-5
+        _tie_groups_equal([a[0] for a in alts], [a[1] for a in alts], g["small_top_ids"][r], g["small_top_lp"][r], 2e-5)
+    assert [x[1] for x in logprobs(torch.from_numpy(g["small_rows"]).cuda(), g["small_toks"].tolist(), 0)] == [[]] * 5
+    big = torch.randn(3, 151936, generator=torch.Generator().manual_seed(int(g["big_seed"][0]))) * 2.5
+    res = logprobs(big.cuda(), g["big_toks"].tolist(), 20)
+    for r, (lp, alts) in enumerate(res):
+        assert abs(lp - g["big_chosen"][r]) <= 2e-5
+        _tie_groups_equal([a[0] for a in alts], [a[1] for a in alts], g["big_top_ids"][r], g["big_top_lp"][r], 2e-5)
+
+
+@pytest.mark.parametrize("V", [1, 31, 33, 1000, 4099, 151936])
+@pytest.mark.parametrize("n_top", [0, 1, 5, 20])
+def test_logprobs_vs_oracle(V, n_top):
+    if n_top > V:
+        pytest.skip("n_top <= V")
+    g = torch.Generator().manual_seed(V * 31 + n_top)
+    rows = torch.randn(5, V, generator=g) * 3
+    if V > 40:
+        rows[1, 5:9] = rows[1].max() + 2.0                          # ties at the top
+        rows[2, ::2] = -math.inf                                    # half masked
+        rows[3] = rows[3].sort().values                             # ascending: every batch raises the bound
+    toks = [int(t) for t in torch.randint(0, V, (5,), generator=g)]
+    _check_logprobs(rows, toks, n_top)
+
+
+def test_logprobs_long_ties_take_the_slow_path_and_bf16():
+    V = 151936
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randn(3, V, generator=g)
+    rows[0, torch.randperm(V, generator=g)[:9000]] = 4.5            # 9000 equal maxima: every list overflows
+    rows[1] = 0.0                                                   # a constant row
+    toks = [7, 0, V - 1]
+    _, ids, _ = _check_logprobs(rows, toks, 20)
+    assert ids[1].tolist() == list(range(20))                       # equal logits: lower token first
+    _check_logprobs(rows.bfloat16().float(), toks, 20)              # same values through the bf16 loader
+    from colinfer_b200.runtime.logprobs import logprobs_tensors
+    c16, i16, l16 = logprobs_tensors(rows.bfloat16().cuda(), torch.tensor(toks, device="cuda"), 20)
+    c32, i32, l32 = logprobs_tensors(rows.bfloat16().float().cuda(), torch.tensor(toks, device="cuda"), 20)
+    assert torch.equal(i16, i32) and torch.allclose(l16, l32, atol=1e-6) and torch.allclose(c16, c32, atol=1e-6)

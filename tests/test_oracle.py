@@ -203,3 +203,39 @@ def test_verify_reject_keeps_target_distribution():
                                  np.maximum(rng.random(2), 1e-7).astype(np.float32))
         counts[d if r["n_accept"] == 1 else r["token"]] += 1
     assert 0.5 * np.abs(counts / trials - p).sum() < 0.03
+
+
+# ------------------------------------------------------------------------------------------------ logprobs (reference vectors)
+def _tie_groups_equal(ids_a, lp_a, ids_b, lp_b, tol):
+    """Same values position by position; ids equal as sets inside every run of equal values (topk leaves ties open),
+    except a run cut off by the end of the list, where either choice of tied tokens is a valid top-n."""
+    ids_a, ids_b = np.asarray(ids_a), np.asarray(ids_b)
+    lp_a, lp_b = np.asarray(lp_a, dtype=np.float64), np.asarray(lp_b, dtype=np.float64)
+    both_inf = np.isinf(lp_a) & np.isinf(lp_b)
+    with np.errstate(invalid="ignore"):
+        assert np.all(both_inf | (np.abs(lp_a - lp_b) <= tol)), (lp_a, lp_b)
+    i, n = 0, len(ids_a)
+    while i < n:
+        j = i
+        while j + 1 < n and lp_b[j + 1] == lp_b[i]:
+            j += 1
+        if j + 1 < n:
+            assert set(ids_a[i:j + 1].tolist()) == set(ids_b[i:j + 1].tolist()), (ids_a, ids_b)
+        i = j + 1
+
+
+def test_logprobs_match_reference_vectors():
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_logprobs.npz"))
+    chosen, ids, lp = O.logprobs(g["small_rows"], g["small_toks"], 5)
+    assert np.allclose(chosen, g["small_chosen"], atol=2e-6)
+    for r in range(len(chosen)):
+        _tie_groups_equal(ids[r], lp[r], g["small_top_ids"][r], g["small_top_lp"][r], 2e-6)
+    c0, i0, l0 = O.logprobs(g["small_rows"], g["small_toks"], 0)
+    assert np.allclose(c0, g["small_chosen_n0"], atol=2e-6) and i0.shape == (5, 0)
+    import torch
+    big = (torch.randn(3, 151936, generator=torch.Generator().manual_seed(int(g["big_seed"][0]))) * 2.5).numpy()
+    chosen, ids, lp = O.logprobs(big, g["big_toks"], 20)
+    assert np.allclose(chosen, g["big_chosen"], atol=5e-6)
+    for r in range(3):
+        _tie_groups_equal(ids[r], lp[r], g["big_top_ids"][r], g["big_top_lp"][r], 5e-6)
