@@ -130,6 +130,77 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_logprobs(args):
+    """Logprobs of emitted tokens (the first row after the headline path): one GPU, rows resident, 20 alternatives.
+    --impl reference times the reference's own expression (log_softmax + gather + topk, torch) on the host cores."""
+    import torch
+    n_top, B = 20, args.batch
+    g = torch.Generator().manual_seed(11)
+    rows = torch.randn(B if args.impl == "ours" else min(B, 256), V, generator=g) * 2.5
+    toks = torch.randint(0, V, (rows.size(0),), generator=g)
+    cfg = {"workload": f"logprobs of emitted tokens: fp32 raw logits [{rows.size(0)}, {V}], 20 alternatives"}
+    if args.impl == "reference":
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+        def ref():
+            lsm = torch.log_softmax(rows.float(), -1)                # engine/runtime/scheduler.py:716-720
+            c = lsm.gather(1, toks[:, None])[:, 0].tolist()
+            tv, ti = lsm.topk(n_top, -1)
+            return c, tv.tolist(), ti.tolist()
+        for _ in range(args.warmup):
+            ref()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            ref()
+        dt = (time.perf_counter() - t0) / args.steps
+        v = rows.size(0) / dt
+        print(json.dumps({"impl": "reference", "metric": "logprob rows/s", "value": v, "unit": "rows/s", "n_gpus": 1,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                          "config": cfg, "cpu_baseline": {"value": v, "unit": "rows/s", "cores": torch.get_num_threads(),
+                                                          "kind": "reference", "sample": f"{rows.size(0)} rows per step"},
+                          "e2e": {"value": v, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
+    from colinfer_b200 import _lib
+    from colinfer_b200.runtime.logprobs import logprobs_tensors
+    _lib.lib()
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    dev = torch.device("cuda", 0)
+    d_rows, d_toks = rows.to(dev), toks.to(dev)
+    for _ in range(args.warmup):
+        logprobs_tensors(d_rows, d_toks, n_top)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            logprobs_tensors(d_rows, d_toks, n_top)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # end to end: rows from pinned host memory, results read back
+    h_rows = rows.pin_memory()
+    h_out = torch.empty(B, dtype=torch.float32).pin_memory()
+    t0 = time.perf_counter()
+    n_e2e = max(3, min(args.steps, 10))
+    for _ in range(n_e2e):
+        d_rows.copy_(h_rows, non_blocking=True)
+        c, ids, lps = logprobs_tensors(d_rows, d_toks, n_top)
+        h_out.copy_(c, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
+    peak, kind = measured_peak()
+    bytes_row = V * 4 + 8 + 4 + n_top * 12
+    ach = bytes_row * B / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "logprob rows/s", "value": B / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                                   "peak_kind": f"of {kind} copy rate", "bytes_per_row": bytes_row, "kernel": "k_logprobs",
+                                   "traffic": None},
+                      "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "rows/s", "steps": n_e2e,
+                              "h2d_bytes_per_step": int(rows.numel() * 4), "d2h_bytes_per_step": int(B * 4)},
+                      "gpu_launches": args.steps, "clocks": clk.summary()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -138,10 +209,14 @@ def main():
     ap.add_argument("--batch", type=int, default=1024, help="rows per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs"],
+                    help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives")
     ap.add_argument("--cluster", type=int, default=0,
                     help="0: the default streaming kernel; 1/2/4/8: the cluster-resident kernel with that cluster size")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload == "logprobs":
+        return run_logprobs(args)
     if args.impl == "reference":
         return run_reference(args)
 
