@@ -251,10 +251,12 @@ def test_many_distinct_history_ids_use_the_slow_count_path(cluster):
 
 
 @pytest.mark.parametrize("V", [20000, 151936])
-@pytest.mark.parametrize("k,tp", [(0, 0.6), (3000, 1.0), (5000, 0.7), (0, 0.999)])
-def test_heavy_ties_take_the_exact_select(V, k, tp):
+@pytest.mark.parametrize("k,tp", [(0, 0.6), (3000, 1.0), (5000, 0.7), (0, 0.999), (40, 0.9)])
+@pytest.mark.parametrize("pen", [False, True])
+def test_heavy_ties_take_the_exact_select(V, k, tp, pen):
     """Thousands of equal logits around the pivot overflow every candidate list: the radix select must give the same
-    kept set (all ties kept) and the same draw as the oracle."""
+    kept set (all ties kept) and the same draw as the oracle -- also for penalised slots, whose rows start on the
+    patch-afterwards path and have to leave it."""
     g = torch.Generator().manual_seed(V + k)
     B = 6
     logits = torch.randn(B, 1, V, generator=g)
@@ -262,6 +264,13 @@ def test_heavy_ties_take_the_exact_select(V, k, tp):
     logits[:, 0, tie] = 3.25                                       # 8000 tokens share the maximum
     logits[1::2, 0, tie[:10]] = 5.0                                # odd rows: a small head above the plateau
     params = wl._params(B, V, 0.9, k, tp, 0.0, list(range(11, 11 + B)))
+    if pen:
+        H = 300
+        hist = torch.randint(0, V, (B, H), generator=g, dtype=torch.int32)
+        hist[:, :40] = tie[:40].to(torch.int32)                    # penalties hit the plateau and the head
+        params.update(history=hist, hist_len=torch.full((B,), H, dtype=torch.int32),
+                      repetition_penalty=torch.full((B,), 1.3), presence_penalty=torch.full((B,), 0.25),
+                      frequency_penalty=torch.full((B,), 0.1))
     w = dict(logits=logits, params=params, pos=torch.arange(B, dtype=torch.int32), u=wl.open_unit(g, B, 1), name="ties")
     nb, out = run_workload(w, V)
     assert nb == 0
