@@ -201,6 +201,62 @@ def run_logprobs(args):
                       "gpu_launches": args.steps, "clocks": clk.summary()}), flush=True)
 
 
+def run_rescore(args):
+    """Draft-head candidate rescoring (the step just before verify): B slots x 256 candidates of a BF16 lm_head
+    [69,632, 2560] (356 MB, larger than L2; the rows a step touches are random).  One GPU.  --impl reference times the
+    reference's own kernel (csrc/sampling.cu built unmodified into oracle/_ref) on the same GPU and inputs."""
+    import ctypes as C
+    import torch
+    from colinfer_b200 import _lib
+    from colinfer_b200.kernels import ops
+    _lib.lib()
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    dev = torch.device("cuda", 0)
+    Vd, K, NC, B = 69_632, 2560, 256, min(args.batch, 256)
+    g = torch.Generator().manual_seed(3)
+    w = (torch.randn(Vd, K, generator=g) * 0.02).bfloat16().to(dev)
+    x = torch.randn(B, K, generator=g).bfloat16().to(dev)
+    cand = torch.randint(0, Vd, (B, NC), generator=g).to(dev)
+    cfg = {"workload": f"draft-head rescoring: {B} slots x {NC} candidates, BF16 lm_head [{Vd}, {K}]"}
+    if args.impl == "reference":
+        path = os.path.join(ROOT, "oracle", "_ref", "libref_sampling.so")
+        if not os.path.exists(path):
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref_sampling.so was not built"}), flush=True)
+            return
+        fn = getattr(C.CDLL(path), "_Z19launch_rescore_bf16PKvS0_PKlPfiiiP11CUstream_st")
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        out = torch.empty(B, NC, device=dev)
+        call = lambda: fn(x.data_ptr(), w.data_ptr(), cand.data_ptr(), out.data_ptr(), B, K, NC, torch.cuda.current_stream().cuda_stream)
+    else:
+        call = lambda: ops().rescore_bf16(x, w, cand)
+    for _ in range(max(args.warmup, 3)):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, kind = measured_peak()
+    bytes_slot = NC * K * 2 + K * 2 + NC * 12
+    ach = bytes_slot * B / (ms * 1e-3) / 1e9
+    line = {"metric": "rescored slots/s", "value": B / (ms * 1e-3), "unit": "slots/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_kind": f"of {kind} copy rate", "bytes_per_slot": bytes_slot,
+                         "kernel": "k_rescore_bf16", "traffic": None},
+            "gpu_launches": args.steps, "clocks": clk.summary()}
+    if args.impl == "reference":
+        line["impl"] = "reference"
+        line["roofline"]["kernel"] = "k_rescore_bf16 (reference, oracle/_ref)"
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -209,14 +265,17 @@ def main():
     ap.add_argument("--batch", type=int, default=1024, help="rows per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs"],
-                    help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives")
+    ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs", "rescore"],
+                    help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives; "
+                         "rescore: draft-head candidate rescoring (256 candidates of a 69,632 x 2560 BF16 lm_head per slot)")
     ap.add_argument("--cluster", type=int, default=0,
                     help="0: the default streaming kernel; 1/2/4/8: the cluster-resident kernel with that cluster size")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "logprobs":
         return run_logprobs(args)
+    if args.workload == "rescore":
+        return run_rescore(args)
     if args.impl == "reference":
         return run_reference(args)
 

@@ -48,6 +48,10 @@ SIGNATURES = {
                                        C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "colinfer_logprobs": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_int, C.c_int, C.c_void_p]),
+    "colinfer_rescore_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                        C.c_int64, C.c_void_p]),
+    "colinfer_rescore_nvfp4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int,
+                                         C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "colinfer_spec_verify_stats_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_spec_verify_ids_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.POINTER(Geometry)]),

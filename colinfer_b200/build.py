@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcolinfer_b200.so")
-SOURCES = ("sample.cu", "stream.cu", "ops.cu", "logprobs.cu")
+SOURCES = ("sample.cu", "stream.cu", "ops.cu", "logprobs.cu", "rescore.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC"]
 

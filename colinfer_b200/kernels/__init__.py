@@ -37,6 +37,46 @@ class _Ops:
         _lib.check(_lib.lib().colinfer_philox_uniform(seed.data_ptr(), offset.data_ptr(), out.data_ptr(),
                                                       out.size(0), out.size(1), _stream()), "philox_uniform")
 
+    @staticmethod
+    def rescore_bf16(x: torch.Tensor, w: torch.Tensor, cand: torch.Tensor) -> torch.Tensor:
+        """Exact logits of candidate rows of a BF16 matrix: x bf16 [B, K], w bf16 [V, K], cand int64 [B, NC] -> fp32
+        [B, NC] (csrc/bindings.cpp:561-572 of the reference: same checks, same result bit for bit)."""
+        check_tensor(x, torch.bfloat16, "x")
+        check_tensor(w, torch.bfloat16, "w")
+        check_tensor(cand, torch.int64, "cand")
+        K = x.size(-1)
+        B, NC = x.numel() // K, cand.size(-1)
+        if w.dim() != 2 or w.size(1) != K or K % 8 or cand.numel() != B * NC:
+            raise RuntimeError("x [B, K], w [V, K] with K % 8 == 0, cand [B, NC]")
+        if x.data_ptr() % 16 or w.data_ptr() % 16:
+            raise RuntimeError("x and w must be 16-byte aligned")
+        out = torch.empty(B, NC, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().colinfer_rescore_bf16(x.data_ptr(), w.data_ptr(), cand.data_ptr(), out.data_ptr(), B, K, NC,
+                                                    w.size(0), _stream()), "rescore_bf16")
+        return out
+
+    @staticmethod
+    def rescore_nvfp4(x: torch.Tensor, w: torch.Tensor, sf: torch.Tensor, gs: float, cand: torch.Tensor) -> torch.Tensor:
+        """Exact logits of candidate rows of an NVFP4 matrix: x bf16 [B, K], w uint8 [V, K / 2] (E2M1 pairs), sf [V, K / 16]
+        E4M3 scales (uint8 or float8_e4m3fn), global scale gs, cand int64 [B, NC] -> fp32 [B, NC]
+        (csrc/bindings.cpp:547-558)."""
+        check_tensor(x, torch.bfloat16, "x")
+        check_tensor(w, torch.uint8, "w")
+        check_tensor(cand, torch.int64, "cand")
+        if sf.dtype not in (torch.uint8, torch.float8_e4m3fn):
+            raise RuntimeError("sf must be uint8 or float8_e4m3fn")
+        check_tensor(sf, None, "sf")
+        K = x.size(-1)
+        B, NC = x.numel() // K, cand.size(-1)
+        if w.dim() != 2 or w.size(1) * 2 != K or K % 16 or cand.numel() != B * NC or sf.numel() != w.size(0) * (K // 16):
+            raise RuntimeError("x [B, K], w [V, K / 2], sf [V, K / 16] with K % 16 == 0, cand [B, NC]")
+        if x.data_ptr() % 16 or w.data_ptr() % 16:
+            raise RuntimeError("x and w must be 16-byte aligned")
+        out = torch.empty(B, NC, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().colinfer_rescore_nvfp4(x.data_ptr(), w.data_ptr(), sf.data_ptr(), float(gs), cand.data_ptr(),
+                                                     out.data_ptr(), B, K, NC, w.size(0), _stream()), "rescore_nvfp4")
+        return out
+
 
 _ops = None
 

@@ -156,6 +156,16 @@ int colinfer_max_active_clusters(int V, int dtype);
 int colinfer_logprobs(const void* logits, int dtype, const int64_t* toks, int n_top, float* chosen, int64_t* top_ids,
                       float* top_lp, int rows, int V, void* stream);
 
+/* Replace ops().rescore_bf16 / ops().rescore_nvfp4 (csrc/sampling.cu:36-115, csrc/bindings.cpp:547-572): exact logits of
+ * candidate rows of the lm_head, out[b, j] = sum_k x[b, k] * W[cand[b, j], k] (NVFP4: E2M1 pairs [rows_w, K / 2], E4M3
+ * scales sf [rows_w, K / 16], global scale gs).  x bf16 [B, K], cand int64 [B, NC], out fp32 [B, NC]; K a multiple of
+ * 8 (16 for NVFP4), x and w 16-byte aligned.  Results are bit-identical to the reference's kernels (same fma order)
+ * and independent of B and NC.  rows_w bounds the candidate ids: an id outside [0, rows_w) yields NaN, never a fault. */
+int colinfer_rescore_bf16(const void* x, const void* w, const int64_t* cand, float* out, int B, int K, int NC,
+                          int64_t rows_w, void* stream);
+int colinfer_rescore_nvfp4(const void* x, const void* w, const void* sf, float gs, const int64_t* cand, float* out,
+                           int B, int K, int NC, int64_t rows_w, void* stream);
+
 /* Library version (major * 100 + minor). */
 int colinfer_version(void);
 

@@ -362,3 +362,91 @@ def logprobs(rows, toks, n_top):
         order = np.lexsort((np.arange(V), -x[i]))[:n_top]           # value descending, then index ascending
         top_ids[i], top_lp[i] = order, lsm[i, order]
     return chosen, top_ids, top_lp
+
+
+# ------------------------------------------------------------------------------------------------ draft-head rescoring
+_E2M1 = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float64)
+
+
+def bf16_to_f64(u16):
+    """bfloat16 bit patterns (uint16) -> float64."""
+    return (np.asarray(u16, dtype=np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def e4m3_to_f64(u8):
+    """FP8 E4M3 (finite-only variant: no infinities, 0x7f / 0xff are NaN) bit patterns -> float64."""
+    u8 = np.asarray(u8, dtype=np.int64)
+    sign = np.where(u8 & 0x80, -1.0, 1.0)
+    e, m = (u8 >> 3) & 0xF, u8 & 7
+    val = np.where(e == 0, m * 2.0 ** -9, (1.0 + m / 8.0) * 2.0 ** (e.astype(np.float64) - 7))
+    val = np.where((e == 15) & (m == 7), np.nan, val)
+    return sign * val
+
+
+def _fma32(a, b, c):
+    """fp32 fused multiply-add of values whose product is exact in float64 (bf16 / fp4 / fp8 operands against fp32)."""
+    return (a * b + c.astype(np.float64)).astype(np.float32)
+
+
+def _warp_xor_sum(acc):
+    """acc [..., 32] fp32 per lane -> every lane's value after the xor-shuffle sums 16, 8, 4, 2, 1 (lane 0 is the result)."""
+    acc = acc.copy()
+    lanes = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        acc = (acc + acc[..., lanes ^ o]).astype(np.float32)
+    return acc[..., 0]
+
+
+def rescore_bf16(x_bits, w_bits, cand):
+    """Exact logits of candidate rows of a BF16 matrix in the reference kernel's accumulation order
+    (csrc/sampling.cu:88-109): one warp per candidate, lane l takes the 8-element chunks l, l + 32, ... in order, one
+    fp32 fma per element, then the xor-shuffle sum.  x_bits uint16 [B, K], w_bits uint16 [V, K], cand [B, NC]."""
+    x, w = bf16_to_f64(x_bits), bf16_to_f64(w_bits)
+    B, K = x.shape
+    NC = cand.shape[1]
+    chunks = K // 8
+    out = np.zeros((B, NC), dtype=np.float32)
+    for b in range(B):
+        rows = w[cand[b]]                                          # [NC, K]
+        acc = np.zeros((NC, 32), dtype=np.float32)
+        for c0 in range(0, chunks, 32):
+            lanes = np.arange(32)
+            cc = c0 + lanes
+            ok = cc < chunks
+            for i in range(8):
+                k = np.where(ok, cc * 8 + i, 0)
+                upd = _fma32(rows[:, k], x[b, k][None, :], acc)
+                acc = np.where(ok[None, :], upd, acc)
+        out[b] = _warp_xor_sum(acc)
+    return out
+
+
+def rescore_nvfp4(x_bits, w_u8, sf_u8, gs, cand):
+    """The NVFP4 variant (csrc/sampling.cu:45-75): per 16-element block s = sum of fma(w, x) in element order (byte i of
+    the block: element 2i in the low nibble, 2i + 1 in the high one), acc = fma(s, scale, acc) over the lane's blocks
+    l, l + 32, ...; xor-shuffle sum; times gs in fp32."""
+    x = bf16_to_f64(x_bits)
+    B, K = x.shape
+    NC = cand.shape[1]
+    blocks = K // 16
+    w_u8 = np.asarray(w_u8, dtype=np.uint8)
+    lo, hi = w_u8 & 0xF, w_u8 >> 4
+    dec = lambda n: np.where(n & 8, -1.0, 1.0) * _E2M1[n & 7]
+    wv = np.empty((w_u8.shape[0], K), dtype=np.float64)
+    wv[:, 0::2], wv[:, 1::2] = dec(lo), dec(hi)
+    sc = e4m3_to_f64(np.asarray(sf_u8, dtype=np.uint8).reshape(w_u8.shape[0], blocks))
+    out = np.zeros((B, NC), dtype=np.float32)
+    for b in range(B):
+        rows, scs = wv[cand[b]], sc[cand[b]]
+        acc = np.zeros((NC, 32), dtype=np.float32)
+        for b0 in range(0, blocks, 32):
+            bb = b0 + np.arange(32)
+            ok = bb < blocks
+            s = np.zeros((NC, 32), dtype=np.float32)
+            for i in range(16):
+                k = np.where(ok, bb * 16 + i, 0)
+                s = _fma32(rows[:, k], x[b, k][None, :], s)
+            upd = _fma32(s.astype(np.float64), scs[:, np.where(ok, bb, 0)], acc)
+            acc = np.where(ok[None, :], upd, acc)
+        out[b] = (_warp_xor_sum(acc) * np.float32(gs)).astype(np.float32)
+    return out

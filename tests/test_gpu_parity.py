@@ -717,3 +717,80 @@ def test_logprobs_long_ties_take_the_slow_path_and_bf16():
     c16, i16, l16 = logprobs_tensors(rows.bfloat16().cuda(), torch.tensor(toks, device="cuda"), 20)
     c32, i32, l32 = logprobs_tensors(rows.bfloat16().float().cuda(), torch.tensor(toks, device="cuda"), 20)
     assert torch.equal(i16, i32) and torch.allclose(l16, l32, atol=1e-6) and torch.allclose(c16, c32, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------------ draft-head rescoring
+def _bf16_bits(t):
+    return t.cpu().view(torch.int16).numpy().view(np.uint16)
+
+
+def _ref_sampling_lib():
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_sampling.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/libref_sampling.so was not built (needs the reference checkout at build time)")
+    return C.CDLL(path)
+
+
+@pytest.mark.parametrize("K", [8, 264, 2560, 5120])
+def test_rescore_bf16_bit_exact(K):
+    """Bit-identical to the oracle's ordered fp32 sums and to the reference's own kernel; close to the dense product
+    (tests/test_draft_head.py:25-40 of the reference); row invariant; wrong shapes raise."""
+    ops = mods()["ops"]()
+    g = torch.Generator().manual_seed(K)
+    V, B, NC = 5000, 4, 256
+    w = (torch.randn(V, K, generator=g) * 0.02).bfloat16().cuda()
+    x = torch.randn(B, K, generator=g).bfloat16().cuda()
+    cand = torch.randint(0, V, (B, NC), generator=g).cuda()
+    out = ops.rescore_bf16(x, w, cand)
+    ref = torch.stack([w[cand[b]].float() @ x[b].float() for b in range(B)])
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    want = O.rescore_bf16(_bf16_bits(x), _bf16_bits(w), cand.cpu().numpy())
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert torch.equal(ops.rescore_bf16(x[2:3].contiguous(), w, cand[2:3].contiguous()), out[2:3])
+    assert torch.equal(ops.rescore_bf16(x, w, cand[:, :7].contiguous()), out[:, :7])
+    if K > 8:
+        with pytest.raises(RuntimeError):
+            ops.rescore_bf16(x, w[:, :K - 4].contiguous(), cand)    # K must match x
+    lib = _ref_sampling_lib()
+    fn = getattr(lib, "_Z19launch_rescore_bf16PKvS0_PKlPfiiiP11CUstream_st")
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    theirs = torch.zeros(B, NC, device="cuda")
+    assert fn(x.data_ptr(), w.data_ptr(), cand.data_ptr(), theirs.data_ptr(), B, K, NC, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, theirs)
+
+
+@pytest.mark.parametrize("K", [16, 1040, 5120])
+def test_rescore_nvfp4_bit_exact(K):
+    ops = mods()["ops"]()
+    g = torch.Generator().manual_seed(K + 1)
+    V, B, NC = 3000, 3, 64
+    wq = torch.randint(0, 256, (V, K // 2), generator=g, dtype=torch.int64).to(torch.uint8).cuda()
+    sf = torch.randint(0x20, 0x60, (V, K // 16), generator=g, dtype=torch.int64).to(torch.uint8).cuda()
+    x = torch.randn(B, K, generator=g).bfloat16().cuda()
+    cand = torch.randint(0, V, (B, NC), generator=g).cuda()
+    gs = 0.00731
+    out = ops.rescore_nvfp4(x, wq, sf, gs, cand)
+    want = O.rescore_nvfp4(_bf16_bits(x), wq.cpu().numpy(), sf.cpu().numpy(), gs, cand.cpu().numpy())
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert torch.equal(ops.rescore_nvfp4(x[1:2].contiguous(), wq, sf, gs, cand[1:2].contiguous()), out[1:2])
+    lib = _ref_sampling_lib()
+    fn = getattr(lib, "_Z20launch_rescore_nvfp4PKvS0_S0_fPKlPfiiiP11CUstream_st")
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    theirs = torch.zeros(B, NC, device="cuda")
+    assert fn(x.data_ptr(), wq.data_ptr(), sf.data_ptr(), gs, cand.data_ptr(), theirs.data_ptr(), B, K, NC,
+              torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, theirs)
+
+
+def test_rescore_bad_candidate_ids_give_nan_not_a_fault():
+    ops = mods()["ops"]()
+    V, K = 100, 64
+    w = torch.randn(V, K).bfloat16().cuda()
+    x = torch.randn(1, K).bfloat16().cuda()
+    cand = torch.tensor([[0, V, -1, 5]], device="cuda")
+    out = ops.rescore_bf16(x, w, cand)
+    assert torch.isnan(out[0, 1]) and torch.isnan(out[0, 2]) and torch.isfinite(out[0, [0, 3]]).all()

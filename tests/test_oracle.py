@@ -239,3 +239,45 @@ def test_logprobs_match_reference_vectors():
     assert np.allclose(chosen, g["big_chosen"], atol=5e-6)
     for r in range(3):
         _tie_groups_equal(ids[r], lp[r], g["big_top_ids"][r], g["big_top_lp"][r], 5e-6)
+
+
+# ------------------------------------------------------------------------------------------------ draft-head rescoring
+def _bf16_bits(t):
+    import torch
+    return t.bfloat16().view(torch.int16).numpy().view(np.uint16)
+
+
+def test_rescore_oracles_equal_the_dense_products():
+    """The reference's own tests (tests/test_draft_head.py:8-40) compare its kernels with the dense fp32 products of
+    the candidate rows (rtol = atol = 1e-5 for BF16, 1e-4 for NVFP4): the oracle's ordered fp32 sums must as well."""
+    import torch
+    g = torch.Generator().manual_seed(1)
+    V, K, B, C = 500, 2560, 3, 40
+    w = (torch.randn(V, K, generator=g) * 0.02).bfloat16()
+    x = torch.randn(B, K, generator=g).bfloat16()
+    cand = torch.randint(0, V, (B, C), generator=g)
+    out = O.rescore_bf16(_bf16_bits(x), _bf16_bits(w), cand.numpy())
+    ref = torch.stack([w[cand[b]].double() @ x[b].double() for b in range(B)]).numpy()
+    assert np.allclose(out, ref, rtol=1e-5, atol=1e-5)
+    # row invariance: a slot alone, a prefix of the candidates
+    assert np.array_equal(O.rescore_bf16(_bf16_bits(x[2:3]), _bf16_bits(w), cand[2:3].numpy()), out[2:3])
+    assert np.array_equal(O.rescore_bf16(_bf16_bits(x), _bf16_bits(w), cand[:, :7].numpy()), out[:, :7])
+    # NVFP4: random packed rows and scales
+    K2 = 1024
+    wq = torch.randint(0, 256, (V, K2 // 2), generator=g, dtype=torch.int64).to(torch.uint8)
+    sf = torch.randint(0x20, 0x60, (V, K2 // 16), generator=g, dtype=torch.int64).to(torch.uint8)   # finite, moderate scales
+    x2 = torch.randn(B, K2, generator=g).bfloat16()
+    gs = 0.0123
+    out = O.rescore_nvfp4(_bf16_bits(x2), wq.numpy(), sf.numpy(), gs, cand.numpy())
+    lo, hi = wq & 0xF, wq >> 4
+    tab = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=torch.float64)
+    W = torch.empty(V, K2, dtype=torch.float64)
+    W[:, 0::2], W[:, 1::2] = tab[lo.long()], tab[hi.long()]
+    W = W * torch.from_numpy(O.e4m3_to_f64(sf.numpy())).repeat_interleave(16, 1) * gs
+    ref = torch.stack([W[cand[b]] @ x2[b].double() for b in range(B)]).numpy()
+    assert np.allclose(out, ref, rtol=1e-4, atol=1e-4)
+    # E4M3 decode against torch's own cast
+    codes = torch.arange(256, dtype=torch.int64).to(torch.uint8)
+    want = codes.view(torch.float8_e4m3fn).double().numpy()
+    got = O.e4m3_to_f64(codes.numpy())
+    assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(got[~np.isnan(got)], want[~np.isnan(want)])
