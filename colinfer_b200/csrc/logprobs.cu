@@ -242,32 +242,26 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_cons
                     off += __popc(bal);
                 }
                 __syncthreads();
-                if (warp == 0) {
-                    // n_top rounds of "best remaining" among at most FCAP candidates, four per lane
-                    constexpr int PERC = FCAP / 32;
-                    float l[PERC]; uint32_t ix[PERC];
+                {
+                    // rank of every candidate among the candidates (value descending, then token ascending): 8 threads
+                    // per candidate compare it with 16 others each; a candidate of rank < n_top is that alternative
+                    static_assert(NT == FCAP * 8, "eight threads per candidate");
+                    const int c = tid >> 3, part = tid & 7;
+                    int rank = 0;
+                    if (c < (int)nc) {
+                        const float lc = sc.fc_l[c]; const uint32_t ic = sc.fc_idx[c];
 #pragma unroll
-                    for (int t = 0; t < PERC; ++t) {
-                        const int e = lane * PERC + t;
-                        l[t] = e < (int)nc ? sc.fc_l[e] : CI_NEG_INF;
-                        ix[t] = e < (int)nc ? sc.fc_idx[e] : 0xFFFFFFFFu;
+                        for (int t = 0; t < FCAP / 8; ++t) {
+                            const int o = part * (FCAP / 8) + t;
+                            if (o < (int)nc && before(sc.fc_l[o], sc.fc_idx[o], lc, ic)) ++rank;
+                        }
                     }
-                    for (int r = 0; r < n_top; ++r) {
-                        float bl = CI_NEG_INF; uint32_t bi = 0xFFFFFFFFu;
-#pragma unroll
-                        for (int t = 0; t < PERC; ++t) if (ix[t] != 0xFFFFFFFFu && before(l[t], ix[t], bl, bi)) { bl = l[t]; bi = ix[t]; }
-#pragma unroll
-                        for (int o = 16; o; o >>= 1) {
-                            const float ol = __shfl_xor_sync(0xffffffffu, bl, o);
-                            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                            if (oi != 0xFFFFFFFFu && before(ol, oi, bl, bi)) { bl = ol; bi = oi; }
-                        }
-#pragma unroll
-                        for (int t = 0; t < PERC; ++t) if (ix[t] == bi) ix[t] = 0xFFFFFFFFu;
-                        if (lane == 0) {
-                            a.top_ids[(size_t)row * n_top + r] = (long long)bi;
-                            a.top_lp[(size_t)row * n_top + r] = bl - lse;
-                        }
+                    rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+                    rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+                    rank += __shfl_xor_sync(0xffffffffu, rank, 4);
+                    if (part == 0 && c < (int)nc && rank < n_top) {
+                        a.top_ids[(size_t)row * n_top + rank] = (long long)sc.fc_idx[c];
+                        a.top_lp[(size_t)row * n_top + rank] = sc.fc_l[c] - lse;
                     }
                 }
                 done = true;
