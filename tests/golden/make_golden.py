@@ -1,6 +1,6 @@
 """Generates tests/golden/ref_cpu_vectors.npz by running the parts of the reference that execute on a CPU:
 engine.runtime.sampler.SamplerParams / apply_mask and engine.spec.accept.inverse_cdf, imported unmodified from a
-colinfer checkout (default /root/reference; nothing is written there and engine.kernels.ops() is never called).
+colinfer checkout (its path is the first argument; nothing is written there and engine.kernels.ops() is never called).
 
     python tests/golden/make_golden.py [path-to-colinfer]
 
