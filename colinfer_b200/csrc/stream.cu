@@ -733,8 +733,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
     // ---------------------------------------------------------------------------------------- which rows are this CTA's
     // Rows differ in cost by a factor of ten (a wide top-p row takes several passes, a greedy row one), so dealing them
     // out by index would leave some CTAs with most of the expensive ones.  Every CTA orders the rows by cost class
-    // (wide sampled, small top-k, greedy; index order inside a class) -- the same order in all CTAs -- and takes every
-    // gridDim.x-th entry of it.  Launches with at most one row per CTA, or very many rows, keep the index order.
+    // (wide sampled, small top-k, greedy) -- the same order in all CTAs -- and takes every gridDim.x-th entry of it.  Launches with at most one row per CTA, or very many rows, keep the index order.
     const long long my_n = n_rows > blockIdx.x ? (n_rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const bool dealt = n_rows > gridDim.x && n_rows <= BAL_ROWS && gridDim.x >= 128;
     if (dealt) {
