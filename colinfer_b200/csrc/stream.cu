@@ -41,7 +41,7 @@ constexpr int FB_NB = 256;           // radix buckets per level of the fallback 
 constexpr int PEN_TABLE = 2048;      // distinct history ids with an O(1) count
 constexpr int XSTEPS = 128;           // 128-logit steps of one warp's region, at most (vocabularies up to 32 x 128 x 128)
 constexpr int BAL_ROWS = 16384;      // launches up to this many rows deal their rows to the CTAs by cost class
-constexpr int BAL_MINE = BAL_ROWS / 128 + 4;   // rows of one CTA then (the grid has at least 128 CTAs, or one row each)
+constexpr int BAL_MINE = BAL_ROWS / 128 + 8;   // rows of one CTA then (the grid has at least 128 CTAs, or one row each)
 #define ST_FLT_MAX 3.402823466e38f
 #define ST_POS_INF (__int_as_float(0x7f800000))
 
@@ -72,7 +72,7 @@ struct Sc {
     uint32_t fc_idx[FCAP]; float fc_l[FCAP];
     float fin_cut; u64 fin_total; int fin_token;
     long long prof[16];            // profiling hook: cycles per phase, summed over the CTA's rows
-    int my_rows[BAL_MINE];
+    int my_rows[BAL_MINE]; int my_count;
     u64 wsum2[NWA], woff2[NWA], wtotal2; int fb[3]; u64 fe[3];   // second scan and the three finds of fine_decide
     int x_warp; u64 x_off; u64 step_sum[XSTEPS];   // the draw's region, walked by all warps
     int glist_n;
@@ -734,7 +734,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
     // Rows differ in cost by a factor of ten (a wide top-p row takes several passes, a greedy row one), so dealing them
     // out by index would leave some CTAs with most of the expensive ones.  Every CTA orders the rows by cost class
     // (wide sampled, small top-k, greedy) -- the same order in all CTAs -- and takes every gridDim.x-th entry of it.  Launches with at most one row per CTA, or very many rows, keep the index order.
-    const long long my_n = n_rows > blockIdx.x ? (n_rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    long long my_n = n_rows > blockIdx.x ? (n_rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const bool dealt = n_rows > gridDim.x && n_rows <= BAL_ROWS && gridDim.x >= 128;
     if (dealt) {
         auto row_class = [&](int row) {
@@ -757,17 +757,30 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         }
         u64 tot;
         u64 ex = block_excl_scan(packed, sc, tot);
-        const u64 n0 = tot & 0x1FFFFFull, n1 = (tot >> 21) & 0x1FFFFFull;
+        // Wide rows go round the CTAs first.  Where that round ends, some CTAs hold one wide row fewer than the others: a
+        // wide row costs about as much as two to three small-top-k rows, so those CTAs get two small-top-k rows each
+        // before the rest of that class (and then the greedy rows) continue round the CTAs from there.
+        const int G = (int)gridDim.x;
+        const long long n0 = (long long)(tot & 0x1FFFFFull), n1 = (long long)((tot >> 21) & 0x1FFFFFull);
+        const int r0 = (int)(n0 % G), n_short = r0 ? G - r0 : 0;
+        const long long extra = min(2ll * n_short, n1);
+        if (tid == 0) sc->my_count = 0;
+        __syncthreads();
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
             if (cls[c] >= 0) {
                 const int j = cls[c];
-                const long long pos = (long long)((j == 0 ? 0ull : j == 1 ? n0 : n0 + n1) + ((ex >> (21 * j)) & 0x1FFFFFull));
+                const long long q = (long long)((ex >> (21 * j)) & 0x1FFFFFull);     // position inside the class
                 ex += 1ull << (21 * j);
-                if (pos % gridDim.x == blockIdx.x) sc->my_rows[pos / gridDim.x] = c * NT + tid;
+                int cta;
+                if (j == 0) cta = (int)(q % G);
+                else if (j == 1) cta = q < extra ? r0 + (int)(q % n_short) : (int)((r0 + q - extra) % G);
+                else cta = (int)((r0 + n1 - extra + q) % G);
+                if (cta == (int)blockIdx.x) sc->my_rows[atomicAdd(&sc->my_count, 1)] = c * NT + tid;   // any order
             }
         }
         __syncthreads();
+        my_n = sc->my_count;
     }
     for (long long it = 0; it < my_n; ++it) {
         __syncthreads();                                         // the previous row's shared tables are free
