@@ -39,6 +39,11 @@ def gather_ids(local: torch.Tensor, n_rows: int, group=None) -> torch.Tensor:
     lo, hi = shard_range(n_rows, world, rank)
     if local.size(0) != hi - lo:
         raise ValueError(f"rank {rank} holds {local.size(0)} rows, expected {hi - lo}")
+    if n_rows % world == 0 and local.is_contiguous():
+        # equal blocks: one collective straight into the result, no padding, no concatenation
+        out = torch.empty((n_rows,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local, group=group)
+        return out
     biggest = shard_range(n_rows, world, 0)[1]
     pad = torch.zeros((biggest,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     pad[: hi - lo] = local
