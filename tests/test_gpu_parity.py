@@ -794,3 +794,34 @@ def test_rescore_bad_candidate_ids_give_nan_not_a_fault():
     cand = torch.tensor([[0, V, -1, 5]], device="cuda")
     out = ops.rescore_bf16(x, w, cand)
     assert torch.isnan(out[0, 1]) and torch.isnan(out[0, 2]) and torch.isfinite(out[0, [0, 3]]).all()
+
+
+# ------------------------------------------------------------------------------------------------ peaked rows
+@pytest.mark.parametrize("gap", [3.0, 12.0, 40.0])
+@pytest.mark.parametrize("pen", [False, True])
+def test_peaked_rows_vs_oracle(gap, pen):
+    """Rows as a language model produces them: a handful of tokens far above a broad bulk.  The sample that places the
+    fine histogram usually misses them (the row maximum lies `gap` above everything else, up to beyond the histogram's
+    range), nuclei are a few tokens wide, and penalties hit exactly the leading tokens."""
+    V, B = wl.V_QWEN, 24
+    g = torch.Generator().manual_seed(int(gap * 10) + pen)
+    logits = torch.randn(B, 1, V, generator=g) * 1.5
+    for b in range(B):
+        lead = torch.randperm(V, generator=g)[:1 + b % 5]
+        logits[b, 0, lead] = logits[b, 0].max() + gap - 0.7 * torch.arange(len(lead), dtype=torch.float32)
+    T = [0.6, 1.0, 1.4][0:3] * (B // 3)
+    top_k = ([0] * 6 + [40] * 3 + [2000] * 3) * 2
+    top_p = ([0.5, 0.9, 0.99, 0.999, 1.0, 0.95] * 4)
+    min_p = [0.0] * 20 + [0.02] * 4
+    params = wl._params(B, V, T, top_k, top_p, min_p, list(range(100, 100 + B)))
+    if pen:
+        H = 64
+        hist = torch.randint(0, V, (B, H), generator=g, dtype=torch.int32)
+        hist[:, 0] = logits[:, 0].argmax(-1).to(torch.int32)       # the leading token was just emitted
+        hist[:, 1] = hist[:, 0]
+        params.update(history=hist, hist_len=torch.full((B,), H, dtype=torch.int32),
+                      repetition_penalty=torch.full((B,), 1.2), presence_penalty=torch.full((B,), 0.4),
+                      frequency_penalty=torch.full((B,), 0.3))
+    w = dict(logits=logits, params=params, pos=torch.arange(B, dtype=torch.int32), u=wl.open_unit(g, B, 1), name="peaked")
+    nb, out = run_workload(w, V)
+    assert nb <= 1
