@@ -125,16 +125,24 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_cons
             if (lane == 0) sc.wf[warp] = sm;
             for (int i = tid; i < BINS; i += NT) hist[i] = 0u;
             __syncthreads();
+            // the bins hang from the smallest finite warp maximum plus 4: a dominant token in the sample (far above
+            // everything else) must not stretch them beyond the bulk
             float lref = sc.wf[lane];
+            float lbulk = lref > CI_NEG_INF ? lref : LP_POS_INF;
 #pragma unroll
-            for (int o = 16; o; o >>= 1) lref = fmaxf(lref, __shfl_xor_sync(0xffffffffu, lref, o));
+            for (int o = 16; o; o >>= 1) {
+                lref = fmaxf(lref, __shfl_xor_sync(0xffffffffu, lref, o));
+                lbulk = fminf(lbulk, __shfl_xor_sync(0xffffffffu, lbulk, o));
+            }
+            const float top = fminf(lbulk + 4.0f, lref);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-                if (gm[k] > CI_NEG_INF && lref < LP_POS_INF) atomicAdd(&hist[min(BINS - 1, __float2int_rz((lref - gm[k]) * SAMPLE_SCALE))], 1u);
+                if (gm[k] > CI_NEG_INF && top < LP_POS_INF)
+                    atomicAdd(&hist[max(0, min(BINS - 1, __float2int_rz((top - gm[k]) * SAMPLE_SCALE)))], 1u);
             __syncthreads();
             uint32_t have;
             const int bk = warp_count_bin(hist, (uint32_t)n_top, lane, have);
-            tw = (bk >= 0 && bk < BINS - 1) ? lref - ((float)(bk + 1) + 0.01f) / SAMPLE_SCALE - fabsf(lref) * 1e-6f : -LP_FLT_MAX;
+            tw = (bk >= 0 && bk < BINS - 1) ? top - ((float)(bk + 1) + 0.01f) / SAMPLE_SCALE - fabsf(top) * 1e-6f : -LP_FLT_MAX;
             __syncthreads();                                        // every warp has read the sample's bins
         }
 

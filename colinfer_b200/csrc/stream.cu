@@ -469,6 +469,8 @@ __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo, float
                                     long long& token, float& lcut, u64& total) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const Cand* mine = ownlist + warp * WLIST;
+    const float bound = lo;
+    lo = fmaxf(lo, lcut_in);                                         // nothing below the min-p cut / the mass horizon matters
     if (!(lo <= L)) return false;
     const float scale = L > lo ? (float)(BINS - 2) / (L - lo) : 0.0f;
     auto bin_of = [&](float l) { return min(BINS - 1, __float2int_rz((L - l) * scale)); };
@@ -476,12 +478,20 @@ __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo, float
     if (tid == 0) sc->fin_ok = 0;
     __syncthreads();
     uint32_t run_b;
-    const int bstar = warp_count_bin(hist, (uint32_t)kk, lane, run_b);   // every warp scans the bins itself
-    if (bstar < 0) return false;                                     // a bound with fewer than kk above it is no bound
+    int bstar = warp_count_bin(hist, (uint32_t)kk, lane, run_b);     // every warp scans the bins itself
+    bool complete;
+    if (bstar < 0) {
+        // fewer than kk listed logits reach lo.  If lo is the sample's bound, the bound did not hold; if it is the cut,
+        // fewer than kk logits survive it and top-k removes nothing: all survivors are candidates
+        if (!(lo > bound) || run_b == 0) return false;
+        bstar = BINS - 1;
+        complete = true;
+    } else {
+        // every row element in bins <= bstar is a candidate while bstar stays clear of the bins around lo
+        complete = bstar <= BINS - 4;
+    }
     const int nc = (int)run_b;                                       // entries down to and including bin bstar
     if (nc > FCAP) return false;
-    // every row element in bins <= bstar is a candidate while bstar stays clear of the bins around lo
-    const bool complete = bstar <= BINS - 4;
     // candidates in token order: warps in order, entries in list order
     {
         int cnt = 0;
@@ -943,16 +953,24 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             for (int i = tid; i < BINS; i += NT) hist1[i] = 0u;
             __syncthreads();
             lref = sc->wf[lane];
+            // the bins of the bound hang from the smallest finite warp maximum plus 4: a few dominant tokens in the
+            // sample (far above everything else) must not stretch them beyond the bulk
+            float lbulk = lref > CI_NEG_INF ? lref : ST_POS_INF;
 #pragma unroll
-            for (int o = 16; o; o >>= 1) lref = fmaxf(lref, __shfl_xor_sync(0xffffffffu, lref, o));
+            for (int o = 16; o; o >>= 1) {
+                lref = fmaxf(lref, __shfl_xor_sync(0xffffffffu, lref, o));
+                lbulk = fminf(lbulk, __shfl_xor_sync(0xffffffffu, lbulk, o));
+            }
             if (do_lists) {
+                const float top = fminf(lbulk + 4.0f, lref);         // +inf when no warp saw a finite logit
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    if (gm[k] > CI_NEG_INF && lref < ST_POS_INF) atomicAdd(&hist1[min(BINS - 1, __float2int_rz((lref - gm[k]) * FAST_SCALE))], 1u);
+                    if (gm[k] > CI_NEG_INF && top < ST_POS_INF)
+                        atomicAdd(&hist1[max(0, min(BINS - 1, __float2int_rz((top - gm[k]) * FAST_SCALE)))], 1u);
                 __syncthreads();
                 uint32_t have;
                 const int bk = warp_count_bin(hist1, (uint32_t)kq, lane, have);
-                if (bk >= 0 && bk < BINS - 1) tw = lref - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(lref) * 1e-6f;
+                if (bk >= 0 && bk < BINS - 1) tw = top - ((float)(bk + 1) + 0.01f) / FAST_SCALE - fabsf(top) * 1e-6f;
             } else {
                 tw = ST_POS_INF;                                 // nothing to list
             }
@@ -1082,6 +1100,11 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             mass.init(tc, m);
             const float thr = __fadd_rn(m, log_min_p);
             lcut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
+            // Logits more than 22 temperatures below the maximum have integer mass 0 (2^30 exp(-22) < 1/2): they can never
+            // be drawn and add nothing to any sum, so every selection works above that horizon.  (A top-k whose k-th
+            // largest lies below it removes nothing that could be drawn.)  Rows with a dominant token -- everything else
+            // tens of logits below -- then stay on the fast paths instead of searching the massless bulk.
+            lcut = fmaxf(lcut, L - 22.0f * tc - fabsf(L) * 1e-6f);
             bool need_topk = kk > 0 && kk < V;
             const bool need_topp = topp < 1.0f;
             const float u = row_uniform(a, (int)row, b, r);
@@ -1123,7 +1146,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                 // The fine buckets: from pass 1 (laid out from the sample's maximum, HOFF of them above it) or counted now
                 // (from the row's maximum).  Bucket b holds the logits in (edge(b + 1), edge(b)].  A stored logit of a
                 // penalised token may lie above every bucket: bucket 0.
-                const bool hist_ready = lref > CI_NEG_INF;
+                const bool hist_ready = lref > CI_NEG_INF && (L - lref) * SC1 < (float)(HOFF - 2);   // the maximum lies inside the buckets laid out from the sample
                 const float href = hist_ready ? lref : L;
                 const int hoff = hist_ready ? HOFF : 0;
                 auto bucket1 = [&](float x) { return fine_bucket(x, href, SC1, (float)hoff - 0.5f); };
