@@ -906,12 +906,14 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         // the listed candidates (which give the penalised maximum, and decide small-top-k and greedy rows), and for
         // wide rows every count and sum, by the difference the few penalised tokens make.
         const bool patch = rw.has_pen && pen_distinct <= PEN_TABLE;
-        const bool do_lists = fastk || patch;                    // rows without a small top_k list a handful of top logits
+        // rows with a top-p (or a small top-k) list their top logits: a row whose listed logits hold all of its mass (a
+        // dominant token, everything unlisted below the mass horizon) is finished from the list alone
+        const bool do_lists = fastk || patch || (sampled && topp < 1.0f);   // (plain rows keep the lean pass)
         // Wide rows that need a pivot (large top_k, top_p) count the fine histogram in this pass too, in buckets laid
         // out from the sample's maximum (the row's is not known yet), HOFF of them above it.
         const bool wide_hist = sampled && !fastk && ((kk > 0 && kk < V) || topp < 1.0f);
         const bool listpass = do_lists || wide_hist;
-        const int kq = fastk ? kk : 4;
+        const int kq = fastk ? kk : 8;
         const float SCW = (float)NB1 / (RANGE * tc);
         float lref = CI_NEG_INF;
         if (patch) rw.pen_inline = false;
@@ -985,7 +987,15 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
                 float4 v[4];
                 ST_LOAD_BATCH(v, i0)
-                ST_TRACK_MAX(v, i0)
+                float bmax = CI_NEG_INF;                         // the batch's largest logit of this lane
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
+                    const bool up = m4 > lmax;                   // strict: the first (lowest) position of the maximum stays
+                    lmax = up ? m4 : lmax;
+                    lpos = up ? i0 + k * 128 + lane * 4 : lpos;
+                    bmax = fmaxf(bmax, m4);
+                }
                 if (count_hist) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
@@ -995,13 +1005,11 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
                             if (e[j] > CI_NEG_INF) atomicAdd(&hist1[fine_bucket(e[j], lref, SCW, (float)HOFF - 0.5f)], 1u);
                     }
                 }
-                unsigned mk[4], anym = 0;
+                if (__ballot_sync(0xffffffffu, bmax >= tw)) {    // some lane has a logit for its list
+                    unsigned mk[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    mk[k] = (v[k].x >= tw ? 1u : 0u) | (v[k].y >= tw ? 2u : 0u) | (v[k].z >= tw ? 4u : 0u) | (v[k].w >= tw ? 8u : 0u);
-                    anym |= mk[k];
-                }
-                if (__ballot_sync(0xffffffffu, anym != 0u)) {
+                    for (int k = 0; k < 4; ++k)
+                        mk[k] = (v[k].x >= tw ? 1u : 0u) | (v[k].y >= tw ? 2u : 0u) | (v[k].z >= tw ? 4u : 0u) | (v[k].w >= tw ? 8u : 0u);
                     // per-lane counts of the four groups, one byte each (a group holds at most 128: no carry)
                     const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
                     unsigned incl = cnt;
@@ -1054,9 +1062,10 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             }
         }
         if (patch && !from_lists) lref = CI_NEG_INF;             // the histogram of this pass counted stored logits: void
-        if (fastk) {                                             // bins of the finish (the reduce below has the barriers after)
-            __syncthreads();                                     // every warp has read the sample's bins
-            for (int i = tid; i < BINS; i += NT) hist1[i] = 0u;
+        uint32_t* fin_bins = fastk ? hist1 : reinterpret_cast<uint32_t*>(bins);   // wide rows keep their histogram in hist1
+        if (sampled) {                                           // bins of the finish (the reduce below has the barriers after)
+            if (fastk) __syncthreads();                          // every warp has read the sample's bins
+            for (int i = tid; i < BINS; i += NT) fin_bins[i] = 0u;
         }
         if (!from_lists && lpos >= 0) {
             const float4 v = rw.load4(lpos);
@@ -1111,10 +1120,14 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
             bool done = false;
 
             // -------------------------------------------------------------------------------- small top-k: finish from the running lists
-            if (fastk) {
+            // Small top-k rows; and any other row whose bound lies below the mass horizon: every logit that carries mass is
+            // listed (top-k, if any, then removes nothing: kk beyond the list).
+            const bool all_listed = !fastk && tw > -ST_FLT_MAX && tw < lcut;
+            if (fastk || all_listed) {
                 ST_PROF(4);
                 if (!__syncthreads_or(fk_bad || !(tw > -ST_FLT_MAX)) &&
-                    finish_running_topk(ownlist, wn1, tw, L, lcut, tc, mass, kk, need_topp, topp, u, hist1, sc, token, lcut, total_mass))
+                    finish_running_topk(ownlist, wn1, tw, L, lcut, tc, mass, fastk ? kk : (need_topk ? kk : 0x7fffffff), need_topp, topp, u,
+                                        fin_bins, sc, token, lcut, total_mass))
                     done = true;
                 __syncthreads();
                 ST_PROF(7);
