@@ -526,6 +526,7 @@ __device__ bool finish_pending(const SampleArgs& a, const Pending& pd, const Can
     mass.init(tc, m);
     const float thr = __fadd_rn(m, a.p.log_min_p[b]);
     float cut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
+    cut = fmaxf(cut, L - 22.0f * tc - fabsf(L) * 1e-6f);           // the mass horizon (see the generic path)
     const float u = row_uniform(a, row, b, r);
     int pre[9];
     pre[0] = 0;
@@ -646,9 +647,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     if (a.prof && tid == 0) for (int i = 0; i < 12; ++i) sc->prof[i] = 0;
 
     // Starts the bulk copies of one row's slice (thread 0 only; every thread must be done reading the buffer).
-    long long t_issue = 0, t_issue_end = 0;
     auto issue_row = [&](const long long rw) {
-        t_issue = clock64();
         fence_proxy_async();                                   // earlier reads of the buffer precede these writes
         const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)rw * V + slice_lo;
         for (int c = 0; c < nchunks; ++c) {
@@ -656,7 +655,6 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
             mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
             bulk_g2s(rowbuf + c * CI_CHUNK, src + c * CI_CHUNK, (uint32_t)len * 4u, &mbar[c]);
         }
-        t_issue_end = clock64();
     };
     bool prefetched = false;          // the next row's copies are already in flight
     bool fast_enabled = true;         // small top-k rows may take the deferred path (identical in every CTA)
@@ -775,7 +773,6 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     if (a.use_bulk) {
         for (int c = 0; c < nchunks; ++c)
             if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
-        if (a.prof && tid == 0) { sc->prof[8] += clock64() - t_issue; sc->prof[9] += t_issue_end - t_issue; }
     } else {
         const size_t g0 = (size_t)row * V + slice_lo;
         if (a.dtype == COLINFER_BF16) {
@@ -1019,6 +1016,9 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     // ---------------------------------------------------------------------------------------- min-p threshold
     const float thr = __fadd_rn(m, log_min_p);
     lcut = lower_logit_for(thr, tc, __fmul_rn(thr, tc));
+    // Mass horizon: a logit more than 22 temperatures below the maximum has integer mass 0 (2^30 exp(-22) < 1/2); it can
+    // never be drawn and adds nothing to any sum, so every selection works above it.
+    lcut = fmaxf(lcut, L - 22.0f * tc - fabsf(L) * 1e-6f);
     bool need_topk = kk > 0 && kk < V;
     const bool need_topp = topp < 1.0f;
     const float u = row_uniform(a, row, b, r);
