@@ -708,7 +708,10 @@ __device__ bool radix_select(const Row& rw, int r_lo, int r_hi, const MassFn& ma
 
 namespace strm {
 
-extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__ Args a) {
+// PEN: the launch has histories (penalties possible); MASK: it has a grammar mask.  Launches without them run an
+// instantiation from which those paths are compiled out.
+template <bool PEN, bool MASK>
+__global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int V = a.V;
     const int nw = (V + 31) >> 5;                                // bitmap words of a row
@@ -808,7 +811,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         rw.V = V; rw.vec = a.vec != 0;
         rw.p32 = a.dtype == COLINFER_F32 ? reinterpret_cast<const float*>(a.logits) + (size_t)row * V : nullptr;
         rw.p16 = a.dtype == COLINFER_BF16 ? reinterpret_cast<const __nv_bfloat16*>(a.logits) + (size_t)row * V : nullptr;
-        rw.mrow = a.mask ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
+        rw.mrow = (MASK && a.mask) ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
         rw.rp = a.p.repetition_penalty ? a.p.repetition_penalty[b] : 1.0f;
         rw.pp = a.p.presence_penalty ? a.p.presence_penalty[b] : 0.0f;
         rw.fp = a.p.frequency_penalty ? a.p.frequency_penalty[b] : 0.0f;
@@ -816,7 +819,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         int hlen = rw.hist ? (a.p.hist_len ? a.p.hist_len[b] : a.p.hist_stride) : 0;
         hlen = max(0, min(hlen, a.p.hist_stride));
         rw.hlen = hlen;
-        rw.has_pen = hlen > 0 && !(rw.rp == 1.0f && rw.pp == 0.0f && rw.fp == 0.0f);
+        rw.has_pen = PEN && hlen > 0 && !(rw.rp == 1.0f && rw.pp == 0.0f && rw.fp == 0.0f);
         rw.pen_bits = pen_bits; rw.pen_prefix = pen_prefix; rw.pen_val = pen_val; rw.hist_slow = &sc->hist_slow;
         if (tid == 0) sc->hist_slow = 0;
 
@@ -905,7 +908,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         // Penalised rows read the logits as stored -- no per-element test of the history bitmap -- and patch afterwards:
         // the listed candidates (which give the penalised maximum, and decide small-top-k and greedy rows), and for
         // wide rows every count and sum, by the difference the few penalised tokens make.
-        const bool patch = rw.has_pen && pen_distinct <= PEN_TABLE;
+        const bool patch = PEN && rw.has_pen && pen_distinct <= PEN_TABLE;
         // rows with a top-p (or a small top-k) list their top logits: a row whose listed logits hold all of its mass (a
         // dominant token, everything unlisted below the mass horizon) is finished from the list alone
         const bool do_lists = fastk || patch || (sampled && topp < 1.0f);   // (plain rows keep the lean pass)
@@ -935,8 +938,16 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid
         lpos = up ? (i0) + k * 128 + lane * 4 : lpos;                                                                     \
     }
         if (!listpass) {
-            const float2 mp = pass1_lean(rw, r_lo, r_hi, lane);
-            lmax = mp.x; lpos = __float_as_int(mp.y);
+            if constexpr (PEN) {
+                const float2 mp = pass1_lean(rw, r_lo, r_hi, lane);
+                lmax = mp.x; lpos = __float_as_int(mp.y);
+            } else {
+                for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                    float4 v[4];
+                    ST_LOAD_BATCH(v, i0)
+                    ST_TRACK_MAX(v, i0)
+                }
+            }
         } else {
             // The first batch of every warp (a tenth of the row at 151,936 logits) bounds the row's kk-th largest logit
             // from below: the kk-th largest of the sample's float4 maxima.  The pass then lists what reaches the bound.
@@ -1573,10 +1584,15 @@ int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, i
     a.out = out_ids; a.stats = stats; a.status = status;
     a.B = B; a.R = R; a.V = V; a.flags = flags;
     colinfer_profile_buffer(&a.prof, &a.prof_slots);
-    e = cudaFuncSetAttribute(strm::k_sample_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // four instantiations: with / without histories (penalties), with / without a grammar mask
+    using Kernel = void (*)(const strm::Args);
+    static const Kernel kernels[4] = {strm::k_sample_stream<false, false>, strm::k_sample_stream<false, true>,
+                                      strm::k_sample_stream<true, false>, strm::k_sample_stream<true, true>};
+    const Kernel kernel = kernels[(params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0)];
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     const long long rows = (long long)B * R;
     const int grid = (int)(rows < sm_count[dev] ? rows : sm_count[dev]);
-    strm::k_sample_stream<<<grid, strm::NT, smem, stream>>>(a);
+    kernel<<<grid, strm::NT, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }
