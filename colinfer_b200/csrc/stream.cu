@@ -708,9 +708,9 @@ __device__ bool radix_select(const Row& rw, int r_lo, int r_hi, const MassFn& ma
 
 namespace strm {
 
-// PEN: the launch has histories (penalties possible); MASK: it has a grammar mask.  Launches without them run an
-// instantiation from which those paths are compiled out.
-template <bool PEN, bool MASK>
+// PEN: the launch has histories (penalties possible); MASK: it has a grammar mask; VEC: fp32 rows that take 128-bit
+// loads (16-byte aligned, V a multiple of 4).  Every launch runs the instantiation without the paths it cannot take.
+template <bool PEN, bool MASK, bool VEC>
 __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int V = a.V;
@@ -808,7 +808,7 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
         const float topp = a.p.top_p[b];
         const float log_min_p = a.p.log_min_p[b];
         Row rw;
-        rw.V = V; rw.vec = a.vec != 0;
+        rw.V = V; rw.vec = VEC;
         rw.p32 = a.dtype == COLINFER_F32 ? reinterpret_cast<const float*>(a.logits) + (size_t)row * V : nullptr;
         rw.p16 = a.dtype == COLINFER_BF16 ? reinterpret_cast<const __nv_bfloat16*>(a.logits) + (size_t)row * V : nullptr;
         rw.mrow = (MASK && a.mask) ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
@@ -1584,11 +1584,14 @@ int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, i
     a.out = out_ids; a.stats = stats; a.status = status;
     a.B = B; a.R = R; a.V = V; a.flags = flags;
     colinfer_profile_buffer(&a.prof, &a.prof_slots);
-    // four instantiations: with / without histories (penalties), with / without a grammar mask
+    // eight instantiations: histories (penalties) or not, grammar mask or not, 128-bit fp32 loads or the general loader
     using Kernel = void (*)(const strm::Args);
-    static const Kernel kernels[4] = {strm::k_sample_stream<false, false>, strm::k_sample_stream<false, true>,
-                                      strm::k_sample_stream<true, false>, strm::k_sample_stream<true, true>};
-    const Kernel kernel = kernels[(params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0)];
+    static const Kernel kernels[8] = {
+        strm::k_sample_stream<false, false, false>, strm::k_sample_stream<false, false, true>,
+        strm::k_sample_stream<false, true, false>,  strm::k_sample_stream<false, true, true>,
+        strm::k_sample_stream<true, false, false>,  strm::k_sample_stream<true, false, true>,
+        strm::k_sample_stream<true, true, false>,   strm::k_sample_stream<true, true, true>};
+    const Kernel kernel = kernels[(params->history != nullptr ? 4 : 0) + (mask != nullptr ? 2 : 0) + (vec ? 1 : 0)];
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     const long long rows = (long long)B * R;
