@@ -92,7 +92,9 @@ struct Args {
     int rows, V;
 };
 
-extern "C" __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args a) {
+// VEC: fp32 rows that take 128-bit loads; the other instantiation holds the general loader (bf16, unaligned rows).
+template <bool VEC>
+__global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int V = a.V, n_top = a.n_top;
     __shared__ __align__(16) uint32_t hist[BINS];
@@ -105,7 +107,7 @@ extern "C" __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_cons
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
         __syncthreads();
         Row rw;
-        rw.V = V; rw.vec = a.vec != 0;
+        rw.V = V; rw.vec = VEC;
         rw.p32 = a.dtype == COLINFER_F32 ? reinterpret_cast<const float*>(a.logits) + (size_t)row * V : nullptr;
         rw.p16 = a.dtype == COLINFER_BF16 ? reinterpret_cast<const __nv_bfloat16*>(a.logits) + (size_t)row * V : nullptr;
 
@@ -349,6 +351,7 @@ extern "C" int colinfer_logprobs(const void* logits, int dtype, const int64_t* t
     a.toks = toks; a.n_top = n_top; a.chosen = chosen; a.top_ids = top_ids; a.top_lp = top_lp;
     a.rows = rows; a.V = V;
     const int grid = rows < sm_count[dev] ? rows : sm_count[dev];
-    lpk::k_logprobs<<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
+    if (a.vec) lpk::k_logprobs<true><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
+    else lpk::k_logprobs<false><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
     return (int)cudaGetLastError();
 }
