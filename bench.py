@@ -38,7 +38,7 @@ HIST = 2048
 CPU_SAMPLE_ROWS = 256
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_sample_stream launch divided by its rows (ncu capture at
 # B = 256, summarised in profiles/k_sample_stream_config3_b256_ncu.md; traffic grows in proportion to the rows).
-NCU_TRAFFIC_BYTES_PER_ROW = 766_400
+NCU_TRAFFIC_BYTES_PER_ROW = 762_200
 
 
 def measured_peak():
