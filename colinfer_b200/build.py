@@ -5,9 +5,11 @@ so no GPU is needed to build.  The library has a plain C ABI (include/colinfer_b
 """
 from __future__ import annotations
 
+import concurrent.futures
 import os
 import subprocess
 import sys
+import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
@@ -32,11 +34,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB,
-           *[os.path.join(CSRC, s) for s in SOURCES]]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + (["-Xptxas", "-v"] if verbose else [])
+    # one nvcc per source, side by side (stream.cu holds eight kernel instantiations and dominates), then the link
+    with tempfile.TemporaryDirectory(prefix="colinfer_b200_obj_") as tmp:
+        def compile_one(src):
+            obj = os.path.join(tmp, src.replace(".cu", ".o"))
+            cmd = [nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+            return obj, r.stderr
+        with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+            done = list(pool.map(compile_one, SOURCES))
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *[o for o, _ in done]]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        res.stderr = "".join(e for _, e in done) + res.stderr
     if verbose:
         sys.stderr.write(res.stderr)
     return LIB
