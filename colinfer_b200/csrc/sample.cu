@@ -1386,7 +1386,7 @@ static int pick_geometry(int V, int dtype, const void* logits, colinfer_geometry
     const int max_slice = CI_CHUNK * CI_MAX_CHUNKS;
     int cs = 0, slice = 0;
     auto slice_for = [&](int c) { return (((V + c - 1) / c) + 127) & ~127; };
-    if (g_cluster_override) {
+    if (g_cluster_override > 0) {
         cs = g_cluster_override; slice = slice_for(cs);
         if (slice > cap1 || slice > max_slice) return 1;
     } else {
@@ -1453,7 +1453,7 @@ extern "C" int colinfer_max_active_clusters(int V, int dtype) {
 }
 
 extern "C" int colinfer_set_cluster_override(int cluster) {
-    if (cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
+    if (cluster != -1 && cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
     g_cluster_override = cluster;
     return 0;
 }
@@ -1470,12 +1470,25 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     if (out_ids && u == nullptr && (pos == nullptr || params->seed == nullptr)) return (int)cudaErrorInvalidValue;
     if (mask && (W < (V + 31) / 32 || mask_rows < R)) return (int)cudaErrorInvalidValue;
     if ((long long)B * R > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-    if (g_cluster_override == 0) {
-        // default: the streaming kernel (one CTA per row, passes over L2); the cluster-resident kernel below runs when
-        // colinfer_set_cluster_override selects a cluster size, or when the row's penalty bitmap would not fit
-        const int rc = colinfer_launch_stream(logits, dtype, mask, mask_rows, W, params, pos, pos_is_i64, u, out_ids, stats, status,
-                                              B, R, V, flags, (cudaStream_t)stream);
-        if (rc != (int)cudaErrorInvalidValue) return rc;
+    if (g_cluster_override <= 0) {
+        // Automatic choice (override 0).  Few rows -- at most as many as the device holds clusters at once -- are a
+        // latency problem: one CTA per row would leave most SMs idle, so each row gets a whole 8-CTA cluster of the
+        // cluster-resident kernel (config 3: 8 rows in 43 us against 89 us).  More rows are a throughput problem: the
+        // streaming kernel (one CTA per row, passes over L2).  Override -1 forces the streaming kernel; the
+        // cluster-resident kernel also runs when a row's penalty bitmap does not fit the streaming kernel.
+        bool use_stream = true;
+        if (g_cluster_override == 0) {
+            colinfer_geometry g0;
+            if (!pick_geometry(V, dtype, logits, &g0)) {
+                const int res0 = active_clusters(g0);
+                if (res0 > 0 && (long long)B * R <= res0) use_stream = false;
+            }
+        }
+        if (use_stream) {
+            const int rc = colinfer_launch_stream(logits, dtype, mask, mask_rows, W, params, pos, pos_is_i64, u, out_ids, stats, status,
+                                                  B, R, V, flags, (cudaStream_t)stream);
+            if (rc != (int)cudaErrorInvalidValue) return rc;
+        }
     }
     colinfer_geometry g;
     if (pick_geometry(V, dtype, logits, &g)) return (int)cudaErrorInvalidValue;

@@ -1149,7 +1149,7 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
             rw.pen_inline = rw.has_pen && !corr;
             // the penalised tokens of this warp's own region (corrections of the warp's own sums need no atomics)
             auto for_my_pen = [&](auto f) {
-                for (int wi = (r_lo >> 5) + lane; wi < ((r_hi + 31) >> 5); wi += 32) {
+                for (int wi = (r_lo >> 5) + lane; r_lo < r_hi && wi < ((r_hi + 31) >> 5); wi += 32) {   // (an empty region owns no word)
                     uint32_t rest = pen_bits[wi], rk = pen_prefix[wi];
                     while (rest) { const int bit = __ffs(rest) - 1; rest &= rest - 1; f((wi << 5) + bit, pen_raw[rk], pen_val[rk]); ++rk; }
                 }

@@ -138,7 +138,9 @@ typedef struct colinfer_geometry {
 } colinfer_geometry;
 int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geometry* out);
 
-/* Test hook: force the cluster size (1, 2, 4 or 8; 0 = automatic) of later colinfer_sample calls of this process. */
+/* Test hook for later colinfer_sample calls of this process.  0 = automatic (few rows: the cluster-resident kernel, one
+ * 8-CTA cluster per row; otherwise the streaming kernel); -1 = always the streaming kernel; 1, 2, 4 or 8 = the
+ * cluster-resident kernel with that cluster size. */
 int colinfer_set_cluster_override(int cluster);
 
 /* Profiling hook: when dev is not NULL, the first `ctas` CTAs of later colinfer_sample launches add, into 16 int64

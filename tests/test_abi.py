@@ -42,7 +42,7 @@ def test_geometry_of_the_benchmark_vocabularies(built_lib):
     assert g.cluster * g.slice_elems >= 262144 and g.smem_bytes <= 227 * 1024
     assert L.colinfer_sample_geometry(50, _lib.F32, None, C.byref(g)) == 0 and g.cluster == 1 and g.bulk_copy == 0
     assert L.colinfer_sample_geometry(10_000_000, _lib.F32, None, C.byref(g)) == 1   # beyond the resident-row limit
-    assert L.colinfer_set_cluster_override(3) == 1 and L.colinfer_set_cluster_override(0) == 0
+    assert L.colinfer_set_cluster_override(3) == 1 and L.colinfer_set_cluster_override(-1) == 0 and L.colinfer_set_cluster_override(0) == 0
 
 
 def test_sampler_params_host_logic(golden):

@@ -21,11 +21,13 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 MARGIN = 1e-6          # fp32 exponentials differ from float64 ones by ~1e-7 relative
 
 
-@pytest.fixture(autouse=True)
-def _need_cuda():
+@pytest.fixture(autouse=True, params=["auto", "stream"])
+def _kernel_choice(request):
+    """Every test runs twice: with the automatic kernel choice (few rows: cluster-resident kernel, else the streaming
+    kernel) and with the streaming kernel forced, so that small cases cover both kernels."""
     assert torch.cuda.is_available(), "the gpu tests need a CUDA device"
-    _lib.lib().colinfer_set_cluster_override(0)
-    yield
+    _lib.lib().colinfer_set_cluster_override(0 if request.param == "auto" else -1)
+    yield request.param
     _lib.lib().colinfer_set_cluster_override(0)
 
 
@@ -54,10 +56,11 @@ def check_tokens(got, want, info, what=""):
     return len(bad)
 
 
-def run_workload(w, V, cluster=0, use_philox=False):
+def run_workload(w, V, cluster=None, use_philox=False):
     """draw() on a workload dict vs the oracle.  Returns (#boundary mismatches, tokens)."""
     m = mods()
-    _lib.lib().colinfer_set_cluster_override(cluster)
+    if cluster is not None:
+        _lib.lib().colinfer_set_cluster_override(cluster)
     dev = "cuda"
     logits = w["logits"].to(dev)
     sp = wl.sampler_params(w["params"], V, dev)
@@ -142,7 +145,7 @@ GRID = [(0.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.7, 20, 1.0, 0.0), (1.0, 0, 0.
         (0.5, 1, 1.0, 0.0), (1.0, 0, 1e-4, 0.0), (1e-9, 0, 0.9, 0.0), (2.0, 5000, 0.999, 0.3)]
 
 
-@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+@pytest.mark.parametrize("cluster", [-1, 1, 2, 4, 8])
 @pytest.mark.parametrize("V", [1, 31, 33, 1000, 4099])
 def test_draw_vs_oracle_grid(V, cluster):
     m = mods()
@@ -172,7 +175,7 @@ def test_draw_vs_oracle_grid(V, cluster):
               presence_penalty=sp.presence_penalty.cpu().numpy(), frequency_penalty=sp.frequency_penalty.cpu().numpy())
     want, info = O.draw(logits.numpy(), pr, None, mask=mask.numpy(), history=hist.numpy(),
                         hist_len=np.full(B, H - 4), u=u.numpy())
-    assert (st == 0).all()
+    assert ((st & ~(_lib.ROW_HIST_SLOW | _lib.ROW_SELECT_SLOW)) == 0).all()   # slower exact paths are fine at toy sizes
     check_tokens(out.cpu().numpy(), want, info, f"V={V} cluster={cluster}")
 
 
@@ -232,7 +235,7 @@ def test_neutral_penalties_are_a_bit_exact_no_op():
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
-@pytest.mark.parametrize("cluster", [0, 1])
+@pytest.mark.parametrize("cluster", [-1, 1])
 def test_many_distinct_history_ids_use_the_slow_count_path(cluster):
     """More than 2048 distinct history ids in one table: counts come from scanning the history."""
     m = mods()
@@ -520,9 +523,11 @@ def test_config3_full_batch_properties():
     assert int(a.min()) >= 0 and int(a.max()) < V
 
 
-def test_missed_band_estimate_retries_exactly():
+def test_missed_band_estimate_retries_exactly(_kernel_choice):
     """The top-p band is an estimate; with the test hook it is misplaced (above the pivot on odd rows, below on even
     ones): the exact window pass must find the pivot's bucket and the tokens must not change."""
+    if _kernel_choice != "stream":
+        pytest.skip("the hook belongs to the streaming kernel")
     m = mods()
     V = wl.V_QWEN
     w = wl.config3(32)
