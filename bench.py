@@ -269,7 +269,8 @@ def main():
                     help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives; "
                          "rescore: draft-head candidate rescoring (256 candidates of a 69,632 x 2560 BF16 lm_head per slot)")
     ap.add_argument("--cluster", type=int, default=0,
-                    help="0: the default streaming kernel; 1/2/4/8: the cluster-resident kernel with that cluster size")
+                    help="0: automatic (few rows: cluster-resident kernel, else the streaming kernel); -1: streaming kernel; "
+                         "1/2/4/8: the cluster-resident kernel with that cluster size")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "logprobs":
@@ -375,6 +376,10 @@ def main():
     ms, kernel_ms, e2e_ms = t.tolist()
 
     if rank == 0:
+        # which kernel colinfer_sample ran: few rows (at most the clusters the device holds at once) take the
+        # cluster-resident kernel, more rows the streaming kernel; --cluster forces one of them
+        few = B <= _lib.lib().colinfer_max_active_clusters(V, _lib.F32)
+        kernel_name = "k_sample" if args.cluster > 0 or (args.cluster == 0 and few) else "k_sample_stream"
         peak, peak_kind = measured_peak()
         achieved = bytes_row * B / (kernel_ms * 1e-3) / 1e9
         line = {
@@ -387,8 +392,8 @@ def main():
                        "sharding": f"rows x{world}, ids all-gathered" if world > 1 else "single GPU"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind} copy rate", "frac_of_nominal_8000": achieved / 8000.0,
-                         "bytes_per_row": bytes_row, "kernel": "k_sample" if args.cluster else "k_sample_stream", "kernel_ms": kernel_ms,
-                         "traffic": None if args.cluster else NCU_TRAFFIC_BYTES_PER_ROW * B},
+                         "bytes_per_row": bytes_row, "kernel": kernel_name, "kernel_ms": kernel_ms,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_ROW * B if kernel_name == "k_sample_stream" else None},
             "e2e": {"value": n_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "steps": e2e_steps,
                     "h2d_bytes_per_step": int(h_logits.numel() * 4 + h_hist.numel() * 4 + h_pos.numel() * 4),
                     "d2h_bytes_per_step": int(h_ids.numel() * 8)},
