@@ -64,6 +64,7 @@ struct Sc {
     float wf[NWA]; int wi[NWA];
     int found; u64 found_excl;
     int ncand; float cand_l[FIN_CAND]; u64 cand_w[FIN_CAND]; float res_f; int sel_ok;
+    uint32_t cand_kmin, cand_kmax; // ordered keys: extremes of the pivot bin's entries (a crowded bin of equal logits)
     int hist_slow, overflow;
     int wcount[NWA], woffs[NWA + 1];
     float bc_f; int bc_i;
@@ -212,7 +213,7 @@ template <class GL, class W>
 __device__ bool lean_select(GL getl, W wt, int n, float base, float scale, u64 target, u64* bins, Sc* sc, float& value) {
     const int tid = threadIdx.x;
     for (int i = tid; i < BINS; i += NT) bins[i] = 0;
-    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; }
+    if (tid == 0) { sc->ncand = 0; sc->sel_ok = 0; sc->cand_kmin = 0xFFFFFFFFu; sc->cand_kmax = 0u; }
     __syncthreads();
     for (int i = tid; i < n; i += NT) {
         const u64 w = wt(i);
@@ -227,11 +228,20 @@ __device__ bool lean_select(GL getl, W wt, int n, float base, float scale, u64 t
         if (w && max(0, min(BINS - 1, __float2int_rz((base - getl(i)) * scale))) == b_star) {
             const int slot = atomicAdd(&sc->ncand, 1);
             if (slot < FIN_CAND) { sc->cand_l[slot] = getl(i); sc->cand_w[slot] = w; }
+            else { const uint32_t k = f2key(getl(i)); atomicMin(&sc->cand_kmin, k); atomicMax(&sc->cand_kmax, k); }
         }
     }
     __syncthreads();
     const int nc = sc->ncand;
-    if (nc > FIN_CAND) return false;
+    if (nc > FIN_CAND) {
+        // A crowded pivot bin.  When all of its entries are one value (bf16 logits: a hundred tokens share every value)
+        // that value is the pivot: the weight above the bin is below the target, with the bin it reaches it.
+        uint32_t kmin = sc->cand_kmin, kmax = sc->cand_kmax;
+        for (int i = 0; i < FIN_CAND; ++i) { const uint32_t k = f2key(sc->cand_l[i]); kmin = min(kmin, k); kmax = max(kmax, k); }
+        if (kmin != kmax) return false;
+        value = key2f(kmin);
+        return true;
+    }
     if (tid < nc) {
         const float mine = sc->cand_l[tid];
         u64 gt = 0, eq = 0;
@@ -254,7 +264,7 @@ __device__ __forceinline__ float apply_penalty(float l, int cnt, float rp, float
 
 // One row as the passes see it: effective logits (penalties, then mask), four at a time.
 struct Row {
-    const float* p32; const __nv_bfloat16* p16; int V; bool vec;
+    const float* p32; const __nv_bfloat16* p16; int V; bool vec, vec16;   // 128-bit fp32 loads / 64-bit bf16 loads of four logits
     const int32_t* mrow;
     bool has_pen; const uint32_t* pen_bits; const uint32_t* pen_prefix; const float* pen_val;
     bool pen_inline;                   // the passes apply the penalties element by element (else: raw logits, lists patched afterwards)
@@ -275,6 +285,14 @@ struct Row {
         float4 v;
         if (vec) {
             v = i < V ? __ldcg(reinterpret_cast<const float4*>(p32 + i)) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+        } else if (vec16) {
+            if (i < V) {
+                const uint2 u = __ldcg(reinterpret_cast<const uint2*>(p16 + i));    // four bf16: a float's upper halves
+                v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u),
+                                __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
+            } else {
+                v = make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+            }
         } else {
             float e[4];
 #pragma unroll
@@ -708,9 +726,10 @@ __device__ bool radix_select(const Row& rw, int r_lo, int r_hi, const MassFn& ma
 
 namespace strm {
 
-// PEN: the launch has histories (penalties possible); MASK: it has a grammar mask; VEC: fp32 rows that take 128-bit
-// loads (16-byte aligned, V a multiple of 4).  Every launch runs the instantiation without the paths it cannot take.
-template <bool PEN, bool MASK, bool VEC>
+// PEN: the launch has histories (penalties possible); MASK: it has a grammar mask; LOADER: 1 = fp32 rows that take
+// 128-bit loads (16-byte aligned, V a multiple of 4), 2 = bf16 rows that take 64-bit loads (8-byte aligned, V a multiple
+// of 4), 0 = the general loader.  Every launch runs the instantiation without the paths it cannot take.
+template <bool PEN, bool MASK, int LOADER>
 __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int V = a.V;
@@ -808,7 +827,7 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
         const float topp = a.p.top_p[b];
         const float log_min_p = a.p.log_min_p[b];
         Row rw;
-        rw.V = V; rw.vec = VEC;
+        rw.V = V; rw.vec = LOADER == 1; rw.vec16 = LOADER == 2;
         rw.p32 = a.dtype == COLINFER_F32 ? reinterpret_cast<const float*>(a.logits) + (size_t)row * V : nullptr;
         rw.p16 = a.dtype == COLINFER_BF16 ? reinterpret_cast<const __nv_bfloat16*>(a.logits) + (size_t)row * V : nullptr;
         rw.mrow = (MASK && a.mask) ? a.mask + ((size_t)b * a.mask_rows + r) * a.W : nullptr;
@@ -1584,14 +1603,18 @@ int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, i
     a.out = out_ids; a.stats = stats; a.status = status;
     a.B = B; a.R = R; a.V = V; a.flags = flags;
     colinfer_profile_buffer(&a.prof, &a.prof_slots);
-    // eight instantiations: histories (penalties) or not, grammar mask or not, 128-bit fp32 loads or the general loader
+    // one instantiation per loader (general, fp32 x 4, bf16 x 4), histories (penalties) or not, grammar mask or not; the
+    // general loader (unaligned rows, odd vocabularies) only in its fullest form
     using Kernel = void (*)(const strm::Args);
-    static const Kernel kernels[8] = {
-        strm::k_sample_stream<false, false, false>, strm::k_sample_stream<false, false, true>,
-        strm::k_sample_stream<false, true, false>,  strm::k_sample_stream<false, true, true>,
-        strm::k_sample_stream<true, false, false>,  strm::k_sample_stream<true, false, true>,
-        strm::k_sample_stream<true, true, false>,   strm::k_sample_stream<true, true, true>};
-    const Kernel kernel = kernels[(params->history != nullptr ? 4 : 0) + (mask != nullptr ? 2 : 0) + (vec ? 1 : 0)];
+    static const Kernel kernels[2][4] = {
+        {strm::k_sample_stream<false, false, 1>, strm::k_sample_stream<false, true, 1>,
+         strm::k_sample_stream<true, false, 1>, strm::k_sample_stream<true, true, 1>},
+        {strm::k_sample_stream<false, false, 2>, strm::k_sample_stream<false, true, 2>,
+         strm::k_sample_stream<true, false, 2>, strm::k_sample_stream<true, true, 2>}};
+    const bool vec16 = dtype == COLINFER_BF16 && (V % 4) == 0 && (((uintptr_t)logits) & 7) == 0;
+    const Kernel kernel = vec ? kernels[0][(params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0)]
+                        : vec16 ? kernels[1][(params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0)]
+                                : strm::k_sample_stream<true, true, 0>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     const long long rows = (long long)B * R;
