@@ -37,9 +37,15 @@ struct Sc {
 };
 
 struct Row {
-    const float* p32; const __nv_bfloat16* p16; int V; bool vec;
+    const float* p32; const __nv_bfloat16* p16; int V; bool vec, vec16;
     __device__ __forceinline__ float4 load4(int i) const {
         if (vec) return i < V ? __ldcg(reinterpret_cast<const float4*>(p32 + i)) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+        if (vec16) {
+            if (i >= V) return make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+            const uint2 u = __ldcg(reinterpret_cast<const uint2*>(p16 + i));        // four bf16: a float's upper halves
+            return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u),
+                               __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
+        }
         float e[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -92,8 +98,9 @@ struct Args {
     int rows, V;
 };
 
-// VEC: fp32 rows that take 128-bit loads; the other instantiation holds the general loader (bf16, unaligned rows).
-template <bool VEC>
+// LOADER: 1 = fp32 rows that take 128-bit loads, 2 = bf16 rows that take 64-bit loads of four logits, 0 = the general
+// loader (unaligned rows, vocabularies that are not a multiple of 4).
+template <int LOADER>
 __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int V = a.V, n_top = a.n_top;
@@ -107,7 +114,7 @@ __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
         __syncthreads();
         Row rw;
-        rw.V = V; rw.vec = VEC;
+        rw.V = V; rw.vec = LOADER == 1; rw.vec16 = LOADER == 2;
         rw.p32 = a.dtype == COLINFER_F32 ? reinterpret_cast<const float*>(a.logits) + (size_t)row * V : nullptr;
         rw.p16 = a.dtype == COLINFER_BF16 ? reinterpret_cast<const __nv_bfloat16*>(a.logits) + (size_t)row * V : nullptr;
 
@@ -351,7 +358,9 @@ extern "C" int colinfer_logprobs(const void* logits, int dtype, const int64_t* t
     a.toks = toks; a.n_top = n_top; a.chosen = chosen; a.top_ids = top_ids; a.top_lp = top_lp;
     a.rows = rows; a.V = V;
     const int grid = rows < sm_count[dev] ? rows : sm_count[dev];
-    if (a.vec) lpk::k_logprobs<true><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
-    else lpk::k_logprobs<false><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
+    const bool vec16 = dtype == COLINFER_BF16 && (V % 4) == 0 && (((uintptr_t)logits) & 7) == 0;
+    if (a.vec) lpk::k_logprobs<1><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
+    else if (vec16) lpk::k_logprobs<2><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
+    else lpk::k_logprobs<0><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
     return (int)cudaGetLastError();
 }
