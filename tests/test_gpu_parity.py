@@ -804,7 +804,8 @@ def test_rescore_bad_candidate_ids_give_nan_not_a_fault():
 # ------------------------------------------------------------------------------------------------ peaked rows
 @pytest.mark.parametrize("gap", [3.0, 12.0, 40.0])
 @pytest.mark.parametrize("pen", [False, True])
-def test_peaked_rows_vs_oracle(gap, pen):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_peaked_rows_vs_oracle(gap, pen, dtype):
     """Rows as a language model produces them: a handful of tokens far above a broad bulk.  The sample that places the
     fine histogram usually misses them (the row maximum lies `gap` above everything else, up to beyond the histogram's
     range), nuclei are a few tokens wide, and penalties hit exactly the leading tokens."""
@@ -827,6 +828,7 @@ def test_peaked_rows_vs_oracle(gap, pen):
         params.update(history=hist, hist_len=torch.full((B,), H, dtype=torch.int32),
                       repetition_penalty=torch.full((B,), 1.2), presence_penalty=torch.full((B,), 0.4),
                       frequency_penalty=torch.full((B,), 0.3))
+    logits = logits.to(dtype)                                       # bf16: a hundred tokens share every value of the bulk
     w = dict(logits=logits, params=params, pos=torch.arange(B, dtype=torch.int32), u=wl.open_unit(g, B, 1), name="peaked")
     nb, out = run_workload(w, V)
     assert nb <= 1
