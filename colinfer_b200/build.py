@@ -2,6 +2,10 @@
 
 `python -m colinfer_b200.build` (or build() from the graft entry) runs nvcc on the sources in csrc/.  nvcc cross-compiles,
 so no GPU is needed to build.  The library has a plain C ABI (include/colinfer_b200.h) and does not link against torch.
+
+The streaming kernel is compiled once per instantiation (csrc/stream_part.cu with -DCOLINFER_STREAM_PART=0..8), side by
+side, which keeps a full build to about a minute.  Objects are kept under colinfer_b200/build/obj and reused while they
+are newer than every source and header.
 """
 from __future__ import annotations
 
@@ -9,52 +13,67 @@ import concurrent.futures
 import os
 import subprocess
 import sys
-import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build", "obj")
 LIB = os.path.join(HERE, "libcolinfer_b200.so")
-SOURCES = ("sample.cu", "stream.cu", "ops.cu", "logprobs.cu", "rescore.cu")
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
-              "-Xcompiler", "-fPIC"]
+STREAM_PARTS = 9
+# (source, object name, extra flags)
+UNITS = [("sample.cu", "sample.o", []), ("ops.cu", "ops.o", []), ("logprobs.cu", "logprobs.o", []),
+         ("rescore.cu", "rescore.o", []), ("stream_host.cu", "stream_host.o", [])] + \
+        [("stream_part.cu", f"stream_part_{i}.o", [f"-DCOLINFER_STREAM_PART={i}"]) for i in range(STREAM_PARTS)]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 
-def _newest(paths):
-    return max(os.path.getmtime(p) for p in paths)
+def _deps():
+    return [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "colinfer_b200.h")]
 
 
 def needs_build() -> bool:
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "colinfer_b200.h")]
-    return not os.path.exists(LIB) or os.path.getmtime(LIB) < _newest(deps)
+    return not os.path.exists(LIB) or os.path.getmtime(LIB) < max(os.path.getmtime(p) for p in _deps())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile csrc/*.cu into libcolinfer_b200.so (skipped when it is newer than every source)."""
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, only: set[str] | None = None) -> str:
+    """Compile csrc/*.cu into libcolinfer_b200.so (skipped when it is newer than every source).
+
+    only: object names to recompile even though the others are stale too (a development shortcut: the stale objects
+    are linked as they are)."""
+    if not force and not needs_build() and only is None:
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    flags = [f for f in NVCC_FLAGS if f != "-shared"] + (["-Xptxas", "-v"] if verbose else [])
-    # one nvcc per source, side by side (stream.cu holds eight kernel instantiations and dominates), then the link
-    with tempfile.TemporaryDirectory(prefix="colinfer_b200_obj_") as tmp:
-        def compile_one(src):
-            obj = os.path.join(tmp, src.replace(".cu", ".o"))
-            cmd = [nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj]
-            r = subprocess.run(cmd, capture_output=True, text=True)
-            if r.returncode != 0:
-                raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
-            return obj, r.stderr
-        with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
-            done = list(pool.map(compile_one, SOURCES))
-        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *[o for o, _ in done]]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
-        res.stderr = "".join(e for _, e in done) + res.stderr
+    extra = os.environ.get("COLINFER_NVCC_EXTRA", "").split()
+    flags = NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else [])
+    os.makedirs(OBJ, exist_ok=True)
+    newest = max(os.path.getmtime(p) for p in _deps())
+
+    def compile_one(unit):
+        src, name, defs = unit
+        obj = os.path.join(OBJ, name)
+        fresh = os.path.exists(obj) and os.path.getmtime(obj) >= newest
+        if only is not None:
+            if name not in only and os.path.exists(obj):
+                return obj, ""
+        elif fresh and not force:
+            return obj, ""
+        cmd = [nvcc, *flags, *defs, "-c", os.path.join(CSRC, src), "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+        return obj, r.stderr
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(len(UNITS), os.cpu_count() or 4))) as pool:
+        done = list(pool.map(compile_one, UNITS))
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *[o for o, _ in done]]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
     if verbose:
-        sys.stderr.write(res.stderr)
+        sys.stderr.write("".join(e for _, e in done) + res.stderr)
     return LIB
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    names = {a.split("=", 1)[1] for a in sys.argv if a.startswith("--only=")}
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, only=names or None))

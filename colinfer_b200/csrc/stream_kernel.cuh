@@ -1,4 +1,4 @@
-// stream.cu -- the streaming form of the fused logits -> token kernel (sm_100a): one CTA per row.
+// stream_kernel.cuh -- the streaming form of the fused logits -> token kernel (sm_100a): one CTA per row.
 //
 // A persistent grid of one 1024-thread CTA per SM; each CTA owns one row at a time and streams it from global memory
 // with 128-bit loads in two to three passes: the first pass comes from HBM, the later ones hit the 126 MB L2 (at most
@@ -16,12 +16,17 @@
 //   neither  pass 2 sums the masses; the draw rescans one warp's region
 // Masses are exp(z - max) in integer units of 2^-30 and all sums are integer: results do not depend on the batch.
 // If a list overflows or the estimated band misses, an exact radix select over the 32-bit keys runs (4 more passes).
+#pragma once
 #include "common.cuh"
 #include "../../include/colinfer_b200.h"
 
 namespace strm {
 
+#ifdef COLINFER_PROFILE
 #define ST_PROF(slot) do { if (a.prof && tid == 0) { const long long t_ = clock64(); sc->prof[slot] += t_ - prof_last; prof_last = t_; } } while (0)
+#else
+#define ST_PROF(slot) do { } while (0)
+#endif
 
 constexpr int NT = 1024;             // threads per CTA
 constexpr int NW = NT / 32;
@@ -335,7 +340,7 @@ struct Row {
 
 // Pass 1 of rows that list nothing: maximum of the warp's region and the float4 group it was first seen in.  Its own
 // function (and register allocation): the loop must keep four 128-bit loads per thread in flight.
-__device__ __noinline__ float2 pass1_lean(const Row rw, int r_lo, int r_hi, int lane) {
+static __device__ __noinline__ float2 pass1_lean(const Row rw, int r_lo, int r_hi, int lane) {
     float lmax = CI_NEG_INF;
     int lpos = -1;
     for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
@@ -396,7 +401,7 @@ __device__ __forceinline__ int warp_drop_penalised(Cand* mylist, int wn, const u
 }
 
 // Concatenates the warps' lists (token order) into glist with masses; returns n, or -1 on overflow.  All threads call.
-__device__ int gather_lists(const Cand* ownlist, int wn, Entry* glist, const MassFn& mass, Sc* sc) {
+static __device__ int gather_lists(const Cand* ownlist, int wn, Entry* glist, const MassFn& mass, Sc* sc) {
     const int lane = lane_id(), warp = warp_id();
     if (lane == 0) sc->wcount[warp] = wn;
     __syncthreads();
@@ -482,7 +487,7 @@ __device__ __forceinline__ int warp_count_bin(const uint32_t* hist, uint32_t kk,
 // warp compacted).  BINS linear bins over [lo, L] find the bin of the kk-th largest; the entries down to that bin, at
 // most FCAP and in token order, go to warp 0, which finishes exactly by bisection on the ordered keys.
 // False: the caller takes the general path.  All threads call.
-__device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo, float L, float lcut_in, float tc, const MassFn& mass,
+static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo, float L, float lcut_in, float tc, const MassFn& mass,
                                     int kk, bool need_topp, float topp, float u, uint32_t* hist, Sc* sc,
                                     long long& token, float& lcut, u64& total) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
@@ -619,7 +624,7 @@ namespace strm {
 
 // Top-k, top-p and the draw on a gathered list that holds every logit >= tl of the row (tl below the top-k pivot;
 // -inf when the list is known to contain the row's whole top k).  False: the caller takes another path.
-__device__ bool finish_on_list(const Entry* gl, int n, float tl, float lcut_in, float tc, float L, bool use_topk, int kk,
+static __device__ bool finish_on_list(const Entry* gl, int n, float tl, float lcut_in, float tc, float L, bool use_topk, int kk,
                                bool need_topp, float topp, float u, u64* bins, Sc* sc, long long& token, float& lcut, u64& total) {
     const int tid = threadIdx.x;
     float cut = lcut_in;
@@ -676,7 +681,7 @@ __device__ bool finish_on_list(const Entry* gl, int n, float tl, float lcut_in, 
 
 // Exact radix select over the order-preserving keys of the effective logits >= lcut (four 8-bit levels, one streaming
 // pass each).  by_mass: the top-p pivot; else the kk-th largest.  False when the filter removes nothing.
-__device__ bool radix_select(const Row& rw, int r_lo, int r_hi, const MassFn& mass, float lcut, bool by_mass, u64 kk, float topp,
+static __device__ bool radix_select(const Row& rw, int r_lo, int r_hi, const MassFn& mass, float lcut, bool by_mass, u64 kk, float topp,
                              u64* fb_hist, Sc* sc, float& pivot) {
     const int tid = threadIdx.x, lane = lane_id();
     const float lk = fmaxf(lcut, -ST_FLT_MAX);
@@ -754,8 +759,10 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
     const int r_lo = min(warp * reg, V), r_hi = min(r_lo + reg, V);
     Cand* mylist = ownlist + warp * WLIST;
     const long long n_rows = (long long)a.B * a.R;
+#ifdef COLINFER_PROFILE
     long long prof_last = clock64();
     if (a.prof && tid == 0) for (int i = 0; i < 16; ++i) sc->prof[i] = 0;
+#endif
     if (tid < NWA) {                                             // neutral values for the warps a smaller CTA does not have
         sc->wsum[tid] = 0; sc->wsum2[tid] = 0; sc->wmass[tid] = 0; sc->wf[tid] = CI_NEG_INF; sc->wi[tid] = 0x7fffffff; sc->wcount[tid] = 0;
         sc->wtw[tid] = -ST_FLT_MAX; sc->wmin[tid] = ST_POS_INF;
@@ -1560,65 +1567,11 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
             }
         }
     }
+#ifdef COLINFER_PROFILE
     if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots)
         for (int i = 0; i < 16; ++i) a.prof[(size_t)blockIdx.x * 16 + i] = sc->prof[i];
+#endif
 }
 
 }  // namespace strm
 
-// ------------------------------------------------------------------------------------------------ host side
-static int stream_smem_bytes(int V) {
-    const int nw = (V + 31) / 32;
-    return strm::NB1 * 4 + strm::BINS * 8 + strm::FB_NB * 8 + strm::NW * strm::WLIST * (int)sizeof(strm::Cand) +
-           (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 12 + 256;
-}
-
-void colinfer_profile_buffer(long long** buf, int* slots);   // sample.cu: the buffer colinfer_set_profile_buffer registered
-
-// Launches the streaming kernel; returns cudaErrorInvalidValue when the vocabulary's penalty bitmap does not fit.
-int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, int mask_rows, int W,
-                           const colinfer_sampler_params* params, const void* pos, int pos_is_i64, const float* u,
-                           int64_t* out_ids, colinfer_row_stats* stats, int32_t* status, int B, int R, int V, int flags,
-                           cudaStream_t stream) {
-    const int smem = stream_smem_bytes(V);
-    if (smem > 226 * 1024 || V > strm::NW * 128 * strm::XSTEPS) return (int)cudaErrorInvalidValue;
-    const bool vec = dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)logits) & 15) == 0;
-    static int sm_count[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-    if (sm_count[dev] == 0) {
-        int n = 0;
-        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return (int)e;
-        sm_count[dev] = n > 0 ? n : 1;
-    }
-    strm::Args a;
-    a.logits = logits; a.dtype = dtype;
-    a.vec = vec ? 1 : 0;
-    a.mask = mask; a.mask_rows = mask_rows; a.W = W;
-    a.p = *params;
-    a.pos = pos; a.pos_i64 = pos_is_i64; a.u = u;
-    a.out = out_ids; a.stats = stats; a.status = status;
-    a.B = B; a.R = R; a.V = V; a.flags = flags;
-    colinfer_profile_buffer(&a.prof, &a.prof_slots);
-    // one instantiation per loader (general, fp32 x 4, bf16 x 4), histories (penalties) or not, grammar mask or not; the
-    // general loader (unaligned rows, odd vocabularies) only in its fullest form
-    using Kernel = void (*)(const strm::Args);
-    static const Kernel kernels[2][4] = {
-        {strm::k_sample_stream<false, false, 1>, strm::k_sample_stream<false, true, 1>,
-         strm::k_sample_stream<true, false, 1>, strm::k_sample_stream<true, true, 1>},
-        {strm::k_sample_stream<false, false, 2>, strm::k_sample_stream<false, true, 2>,
-         strm::k_sample_stream<true, false, 2>, strm::k_sample_stream<true, true, 2>}};
-    const bool vec16 = dtype == COLINFER_BF16 && (V % 4) == 0 && (((uintptr_t)logits) & 7) == 0;
-    const Kernel kernel = vec ? kernels[0][(params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0)]
-                        : vec16 ? kernels[1][(params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0)]
-                                : strm::k_sample_stream<true, true, 0>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    const long long rows = (long long)B * R;
-    const int grid = (int)(rows < sm_count[dev] ? rows : sm_count[dev]);
-    kernel<<<grid, strm::NT, smem, stream>>>(a);
-    return (int)cudaGetLastError();
-}
