@@ -1407,6 +1407,12 @@ extern "C" int colinfer_sample_geometry(int V, int dtype, const void* logits, co
 
 void colinfer_profile_buffer(long long** buf, int* slots) { *buf = g_prof; *slots = g_prof_slots; }
 
+extern "C" int colinfer_set_profile_buffer(void* dev, int ctas) {
+    g_prof = reinterpret_cast<long long*>(dev);
+    g_prof_slots = dev ? ctas : 0;
+    return 0;
+}
+
 static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, const colinfer_geometry& g, long long clusters, cudaStream_t st) {
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = dim3((unsigned)(clusters * g.cluster), 1, 1);
