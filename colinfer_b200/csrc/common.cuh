@@ -60,26 +60,15 @@ struct MassFn {
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((z - m) * CI_LOG2E));
         return __float2uint_rn(e * CI_MASS_SCALE);
     }
-    // Four masses at once for a converged warp (0 for logits below lk); the same values as operator().  While all of
-    // the warp's products stay below 2^23 -- all but the few logits within 4.85 of the maximum -- the conversion to
-    // integer is a rounding float add instead of a conversion instruction (which shares its pipe with ex2).
+    // Four masses at once (0 for logits below lk); the same values as operator().
     __device__ __forceinline__ void four(const float (&l)[4], float lk, uint32_t (&q)[4]) const {
-        float x[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float q0 = l[j] * rinv;
             const float z = fmaf(fmaf(-q0, tc, l[j]), rinv, q0);
             float e;
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((z - m) * CI_LOG2E));
-            x[j] = l[j] >= lk ? e * CI_MASS_SCALE : 0.0f;
-        }
-        const float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-        if (__any_sync(0xffffffffu, mx >= 8388608.0f)) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) q[j] = __float2uint_rn(x[j]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) q[j] = __float_as_uint(x[j] + 8388608.0f) - 0x4B000000u;
+            q[j] = l[j] >= lk ? __float2uint_rn(e * CI_MASS_SCALE) : 0u;
         }
     }
 };

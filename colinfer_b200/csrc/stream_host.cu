@@ -15,7 +15,7 @@ const PartFn kParts[9] = {colinfer_stream_part_0, colinfer_stream_part_1, colinf
 int stream_smem_bytes(int V) {
     const int nw = (V + 31) / 32;
     return strm::NB1 * 4 + strm::BINS * 8 + strm::FB_NB * 8 + strm::NW * strm::WLIST * (int)sizeof(strm::Cand) +
-           (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 12 + 256;
+           (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 16 + 256;
 }
 
 // Multiprocessors of a device, looked up once (the engine calls from one thread; a second thread that races here
@@ -62,6 +62,7 @@ int colinfer_launch_stream(const void* logits, int dtype, const int32_t* mask, i
     const int variant = (params->history != nullptr ? 2 : 0) + (mask != nullptr ? 1 : 0);
     const int part = vec ? variant : vec16 ? 4 + variant : 8;
     const long long rows = (long long)B * R;
-    const int grid = (int)(rows < sms ? rows : sms);
+    const int slots = sms * strm::CTAS_PER_SM;
+    const int grid = (int)(rows < slots ? rows : slots);
     return kParts[part](&a, grid, strm::NT, smem, stream, dev);
 }

@@ -23,12 +23,19 @@
 namespace strm {
 
 #ifdef COLINFER_PROFILE
+#define FK_PROF_PARAMS , long long& prof_last, bool prof_on
+#define FK_PROF_ARGS , prof_last, a.prof != nullptr
+#define FK_PROF(slot) do { if (prof_on && threadIdx.x == 0) { const long long t_ = clock64(); sc->prof[slot] += t_ - prof_last; prof_last = t_; } } while (0)
 #define ST_PROF(slot) do { if (a.prof && tid == 0) { const long long t_ = clock64(); sc->prof[slot] += t_ - prof_last; prof_last = t_; } } while (0)
 #else
+#define FK_PROF_PARAMS
+#define FK_PROF_ARGS
+#define FK_PROF(slot) do { } while (0)
 #define ST_PROF(slot) do { } while (0)
 #endif
 
 constexpr int NT = 1024;             // threads per CTA
+constexpr int CTAS_PER_SM = 1;       // (two CTAs of 512 threads per SM were measured: slower -- their rows split unevenly)
 constexpr int NW = NT / 32;
 constexpr int NWA = 32;              // per-warp exchange arrays are sized (and reduced) for a full warp of warps
 constexpr int NB1 = 8192;            // fine buckets over the distance from the row maximum (or from the sample's)
@@ -38,7 +45,7 @@ constexpr int FASTK = 100;           // largest top_k finished from the group-ma
 constexpr int BINS = 512;            // bins of the sample histogram and of the exact list selection
 constexpr float FAST_SCALE = 32.0f;  // sample-histogram bins per unit logit (16 units below the sample's maximum)
 constexpr float FIN_SCALE = 64.0f;   // list-selection bins per unit logit (8 units below the maximum)
-constexpr int WLIST = 64;            // list entries per warp
+constexpr int WLIST = 2048 / (NT / 32);  // list entries per warp
 constexpr int FCAP = 128;            // candidates of the one-warp finish
 constexpr int GLIST = 1365;          // gathered list entries
 constexpr int FIN_CAND = 64;         // entries of one bin compared pairwise
@@ -60,6 +67,7 @@ struct Args {
     long long* prof; int prof_slots;   // optional cycles per phase (profiling hook)
 };
 
+template <bool B> struct BoolTag { static constexpr bool value = B; };
 struct Cand { uint32_t idx; float l; };
 struct Entry { uint32_t idx; float l; uint32_t q; };
 
@@ -310,10 +318,15 @@ struct Row {
         return v;
     }
     __device__ __forceinline__ float4 load4(int i) const { return fix4(raw4(i), i, V); }
+    __device__ __forceinline__ float4 fix4(float4 v, int i, int lim) const {
+        return pen_inline ? fix4t<true>(v, i, lim) : fix4t<false>(v, i, lim);
+    }
     // the effective logits of a loaded group: penalties, then mask.  Groups at or beyond lim (the end of the caller's
     // region; at most V) keep the caller's filler values.
-    __device__ __forceinline__ float4 fix4(float4 v, int i, int lim) const {
-        if (pen_inline && i < lim) {
+    // PI: the row's penalties are applied here, element by element (the hot loops are compiled once for each case)
+    template <bool PI>
+    __device__ __forceinline__ float4 fix4t(float4 v, int i, int lim) const {
+        if (PI && i < lim) {
             // the few penalised logits of the row were computed once (pen_val, by rank of the token in the history bitmap)
             const uint32_t word = pen_bits[i >> 5];
             const uint32_t nib = (word >> (i & 31)) & 0xFu;
@@ -489,7 +502,7 @@ __device__ __forceinline__ int warp_count_bin(const uint32_t* hist, uint32_t kk,
 // False: the caller takes the general path.  All threads call.
 static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo, float L, float lcut_in, float tc, const MassFn& mass,
                                     int kk, bool need_topp, float topp, float u, uint32_t* hist, Sc* sc,
-                                    long long& token, float& lcut, u64& total) {
+                                    long long& token, float& lcut, u64& total FK_PROF_PARAMS) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const Cand* mine = ownlist + warp * WLIST;
     const float bound = lo;
@@ -537,6 +550,7 @@ static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo
         }
     }
     __syncthreads();
+    FK_PROF(5);
     if (warp == 0) {
         constexpr int PERC = FCAP / 32;
         float l[PERC]; uint32_t key[PERC], q[PERC];
@@ -613,6 +627,7 @@ static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo
         }
     }
     __syncthreads();
+    FK_PROF(6);
     if (!sc->fin_ok) return false;
     token = sc->fin_token; lcut = sc->fin_cut; total = sc->fin_total;
     return true;
@@ -735,7 +750,7 @@ namespace strm {
 // 128-bit loads (16-byte aligned, V a multiple of 4), 2 = bf16 rows that take 64-bit loads (8-byte aligned, V a multiple
 // of 4), 0 = the general loader.  Every launch runs the instantiation without the paths it cannot take.
 template <bool PEN, bool MASK, int LOADER>
-__global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__ Args a) {
+__global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = lane_id(), warp = warp_id();
     const int V = a.V;
     const int nw = (V + 31) >> 5;                                // bitmap words of a row
@@ -752,6 +767,7 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
     uint32_t* pen_cnt = pen_prefix + nw;                                      // [PEN_TABLE] occurrences per rank
     float* pen_val = reinterpret_cast<float*>(pen_cnt + PEN_TABLE);            // [PEN_TABLE] penalised logit per rank
     float* pen_raw = pen_val + PEN_TABLE;                                      // [PEN_TABLE] stored logit per rank
+    int* pen_tok = reinterpret_cast<int*>(pen_raw + PEN_TABLE);                // [PEN_TABLE] token per rank (ascending)
 
     // warp w owns the contiguous region [r_lo, r_hi) of the row; lanes interleave float4 groups: token order inside a
     // region is (step, lane, component)
@@ -848,14 +864,31 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
         rw.has_pen = PEN && hlen > 0 && !(rw.rp == 1.0f && rw.pp == 0.0f && rw.fp == 0.0f);
         rw.pen_bits = pen_bits; rw.pen_prefix = pen_prefix; rw.pen_val = pen_val; rw.hist_slow = &sc->hist_slow;
         if (tid == 0) sc->hist_slow = 0;
+        const bool fastk = sampled && kk > 0 && kk <= FASTK && kk < V;
+        // Rows that are finished from their candidate lists alone -- greedy and small-top-k rows -- need the penalties of
+        // the listed tokens only.  When the penalties can only lower a logit (the usual setting) such a row builds no
+        // tables: after the pass every history entry looks itself up in the lists (they are ordered by token) and the
+        // entries found take their penalised value.  If the row then turns out to need more than its lists (a list
+        // overflowed, too few candidates stay above the bound, the finish leaves the lists), it starts again with tables.
+        const bool lowering = rw.rp >= 1.0f && rw.pp >= 0.0f && rw.fp >= 0.0f;
+      for (int redo = 0; redo < 2; ++redo) {
+        if (redo) __syncthreads();
+        const bool lazy = PEN && rw.has_pen && lowering && (fastk || !sampled) && redo == 0;
+        int* hist_s = reinterpret_cast<int*>(pen_raw);               // lazy rows: the first PEN_TABLE history entries, staged
+        if (lazy) {
+            for (int i = tid; i < PEN_TABLE; i += NT) pen_cnt[i] = 0u;   // occurrences per list entry (NW * WLIST = PEN_TABLE)
+            for (int i = tid; i < min(hlen, PEN_TABLE); i += NT)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(hist_s + i)), "l"(rw.hist + i) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
 
         // ------------------------------------------------------------------------------------ penalty tables (whole row)
         int pen_distinct = 0;
         rw.pen_inline = rw.has_pen;
-        if (rw.has_pen) {
+        if (rw.has_pen && !lazy) {
             // Each thread keeps its first HP history entries and their stored logits in registers: the two dependent loads
             // (id, then logit) run under the bitmap and rank steps.  Longer histories re-read the rest.
-            constexpr int HP = 2;
+            constexpr int HP = 2048 / NT;
             int ht[HP]; float hx[HP];
             for (int i = tid; i < nw; i += NT) pen_bits[i] = 0u;
             for (int i = tid; i < PEN_TABLE; i += NT) pen_cnt[i] = 0u;
@@ -906,20 +939,21 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
                     __syncthreads();
                 }
                 // the stored and the penalised logit of every marked token (equal tokens write equal values)
-                auto put = [&](uint32_t rk, float x) {
+                auto put = [&](uint32_t rk, float x, int tok) {
                     if (rk < PEN_TABLE) {
                         const int cnt = rw.fp != 0.0f ? (int)pen_cnt[rk] : 1;
                         pen_raw[rk] = x;
+                        pen_tok[rk] = tok;
                         pen_val[rk] = x > CI_NEG_INF ? apply_penalty(x, cnt, rw.rp, rw.pp, rw.fp) : CI_NEG_INF;
                     }
                 };
 #pragma unroll
-                for (int j = 0; j < HP; ++j) put(hr[j], hx[j]);
+                for (int j = 0; j < HP; ++j) put(hr[j], hx[j], ht[j]);
                 for (int i = tid + HP * NT; i < hlen; i += NT) {
                     const int v = __ldg(rw.hist + i);
                     if (v >= 0 && v < V) {
                         const bool masked = rw.mrow != nullptr && !((__ldg(rw.mrow + (v >> 5)) >> (v & 31)) & 1);
-                        put(rank_of(v), masked ? CI_NEG_INF : rw.raw(v));
+                        put(rank_of(v), masked ? CI_NEG_INF : rw.raw(v), v);
                     }
                 }
             }
@@ -930,7 +964,6 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
         // ------------------------------------------------------------------------------------ pass 1: maximum, argmax; running top-k lists
         // Small top_k: each warp lists the logits of its region that are >= its own threshold -- the kk-th largest it
         // has seen, raised whenever the list fills -- so that the lists together always hold the row's top kk.
-        const bool fastk = sampled && kk > 0 && kk <= FASTK && kk < V;
         // Penalised rows read the logits as stored -- no per-element test of the history bitmap -- and patch afterwards:
         // the listed candidates (which give the penalised maximum, and decide small-top-k and greedy rows), and for
         // wide rows every count and sum, by the difference the few penalised tokens make.
@@ -956,6 +989,12 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
         v[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);                       \
     }                                                                                                                     \
     _Pragma("unroll") for (int k = 0; k < 4; ++k) v[k] = rw.fix4(v[k], (i0) + k * 128 + lane * 4, r_hi);
+#define ST_LOAD_BATCH_T(v, i0, PI)                                                                                       \
+    _Pragma("unroll") for (int k = 0; k < 4; ++k) {                                                                       \
+        const int i = (i0) + k * 128 + lane * 4;                                                                          \
+        v[k] = i < r_hi ? rw.raw4(i) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);                       \
+    }                                                                                                                     \
+    _Pragma("unroll") for (int k = 0; k < 4; ++k) v[k] = rw.template fix4t<PI>(v[k], (i0) + k * 128 + lane * 4, r_hi);
 #define ST_TRACK_MAX(v, i0)                                                                                               \
     _Pragma("unroll") for (int k = 0; k < 4; ++k) {                                                                       \
         const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));                                             \
@@ -977,13 +1016,15 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
         } else {
             // The first batch of every warp (a tenth of the row at 151,936 logits) bounds the row's kk-th largest logit
             // from below: the kk-th largest of the sample's float4 maxima.  The pass then lists what reaches the bound.
-            float gm[4];
-            {
-                float4 v[4];
-                ST_LOAD_BATCH(v, r_lo)
-                ST_TRACK_MAX(v, r_lo)
+            constexpr int NSB = 32 / NW;                             // sample batches per warp: 16,384 logits per row in all
+            float gm[4 * NSB];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) gm[k] = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
+            for (int sb = 0; sb < NSB; ++sb) {
+                float4 v[4];
+                ST_LOAD_BATCH(v, r_lo + sb * 512)
+                ST_TRACK_MAX(v, r_lo + sb * 512)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) gm[sb * 4 + k] = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
             }
             float sm = lmax;
 #pragma unroll
@@ -1003,7 +1044,7 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
             if (do_lists) {
                 const float top = fminf(lbulk + 4.0f, lref);         // +inf when no warp saw a finite logit
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
+                for (int k = 0; k < 4 * NSB; ++k)
                     if (gm[k] > CI_NEG_INF && top < ST_POS_INF)
                         atomicAdd(&hist1[max(0, min(BINS - 1, __float2int_rz((top - gm[k]) * FAST_SCALE)))], 1u);
                 __syncthreads();
@@ -1021,40 +1062,44 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
             } else {
                 lref = CI_NEG_INF;                               // marks: no histogram from this pass
             }
-            for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
-                float4 v[4];
-                ST_LOAD_BATCH(v, i0)
-                float bmax = CI_NEG_INF;                         // the batch's largest logit of this lane
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
-                    const bool up = m4 > lmax;                   // strict: the first (lowest) position of the maximum stays
-                    lmax = up ? m4 : lmax;
-                    lpos = up ? i0 + k * 128 + lane * 4 : lpos;
-                    bmax = fmaxf(bmax, m4);
-                }
-                if (count_hist) {
-#pragma unroll
+            auto listing_pass = [&](auto pi_tag) {
+                constexpr bool PI = decltype(pi_tag)::value;
+                for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                    float4 v[4];
+                    ST_LOAD_BATCH_T(v, i0, PI)
+                    float bmax = CI_NEG_INF;                         // the batch's largest logit of this lane
+    #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (e[j] > CI_NEG_INF) atomicAdd(&hist1[fine_bucket(e[j], lref, SCW, (float)HOFF - 0.5f)], 1u);
+                        const float m4 = fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w));
+                        const bool up = m4 > lmax;                   // strict: the first (lowest) position of the maximum stays
+                        lmax = up ? m4 : lmax;
+                        lpos = up ? i0 + k * 128 + lane * 4 : lpos;
+                        bmax = fmaxf(bmax, m4);
+                    }
+                    if (count_hist) {
+    #pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+    #pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (e[j] > CI_NEG_INF) atomicAdd(&hist1[fine_bucket(e[j], lref, SCW, (float)HOFF - 0.5f)], 1u);
+                        }
+                    }
+                    if (__ballot_sync(0xffffffffu, bmax >= tw)) {    // some lane has a logit for its list
+                        unsigned mk[4];
+    #pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            mk[k] = (v[k].x >= tw ? 1u : 0u) | (v[k].y >= tw ? 2u : 0u) | (v[k].z >= tw ? 4u : 0u) | (v[k].w >= tw ? 8u : 0u);
+                        // per-lane counts of the four groups, one byte each (a group holds at most 128: no carry)
+                        const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
+                        unsigned incl = cnt;
+    #pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+                        warp_append_batch<WLIST>(mylist, wn1, mk, v, (uint32_t)(i0 + lane * 4), lane, incl, cnt);
                     }
                 }
-                if (__ballot_sync(0xffffffffu, bmax >= tw)) {    // some lane has a logit for its list
-                    unsigned mk[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        mk[k] = (v[k].x >= tw ? 1u : 0u) | (v[k].y >= tw ? 2u : 0u) | (v[k].z >= tw ? 4u : 0u) | (v[k].w >= tw ? 8u : 0u);
-                    // per-lane counts of the four groups, one byte each (a group holds at most 128: no carry)
-                    const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
-                    unsigned incl = cnt;
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-                    warp_append_batch<WLIST>(mylist, wn1, mk, v, (uint32_t)(i0 + lane * 4), lane, incl, cnt);
-                }
-            }
+            };
+            if (PEN && rw.pen_inline) listing_pass(BoolTag<PEN>{}); else listing_pass(BoolTag<false>{});
             if (wn1 > WLIST) fk_bad = 1;                         // a list overflowed (its tail was dropped): general path
             if (!do_lists) { tw = -ST_FLT_MAX; wn1 = 0; }
         }
@@ -1065,18 +1110,41 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
             // provided no penalised token rose from below the bound to above it, and enough candidates remain
             int bad = fk_bad;
             float pm = CI_NEG_INF; int pi = 0x7fffffff, cnt_ok = 0;
-            for (int j = lane; j < min(wn1, WLIST); j += 32) {
-                const uint32_t idx = mylist[j].idx;
-                const uint32_t word = pen_bits[idx >> 5];
-                float l = mylist[j].l;
-                if ((word >> (idx & 31)) & 1u) {
-                    l = pen_val[pen_prefix[idx >> 5] + __popc(word & ((1u << (idx & 31)) - 1u))];
-                    mylist[j].l = l;
+            if (lazy) {
+                // every history entry finds its token in the list of the warp that owns it and counts itself there
+                if (lane == 0) sc->wcount[warp] = min(wn1, WLIST);
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncthreads();
+                for (int i = tid; i < hlen; i += NT) {
+                    const int v = i < PEN_TABLE ? hist_s[i] : __ldg(rw.hist + i);
+                    if (v < 0 || v >= V) continue;
+                    const int w = v / reg;
+                    const Cand* lst = ownlist + w * WLIST;
+                    int lo = 0, hi = sc->wcount[w];
+                    while (lo < hi) { const int mid = (lo + hi) >> 1; if (lst[mid].idx < (uint32_t)v) lo = mid + 1; else hi = mid; }
+                    if (lo < sc->wcount[w] && lst[lo].idx == (uint32_t)v) atomicAdd(&pen_cnt[w * WLIST + lo], 1u);
                 }
-                if (l >= tw) { ++cnt_ok; if (l > pm) { pm = l; pi = (int)idx; } }   // token order: the first maximum stays
+                __syncthreads();
+                for (int j = lane; j < min(wn1, WLIST); j += 32) {
+                    const uint32_t c = pen_cnt[warp * WLIST + j];
+                    float l = mylist[j].l;
+                    if (c) { l = apply_penalty(l, rw.fp != 0.0f ? (int)c : 1, rw.rp, rw.pp, rw.fp); mylist[j].l = l; }
+                    if (l >= tw) { ++cnt_ok; if (l > pm) { pm = l; pi = (int)mylist[j].idx; } }   // token order: the first maximum stays
+                }
+            } else {
+                for (int j = lane; j < min(wn1, WLIST); j += 32) {
+                    const uint32_t idx = mylist[j].idx;
+                    const uint32_t word = pen_bits[idx >> 5];
+                    float l = mylist[j].l;
+                    if ((word >> (idx & 31)) & 1u) {
+                        l = pen_val[pen_prefix[idx >> 5] + __popc(word & ((1u << (idx & 31)) - 1u))];
+                        mylist[j].l = l;
+                    }
+                    if (l >= tw) { ++cnt_ok; if (l > pm) { pm = l; pi = (int)idx; } }   // token order: the first maximum stays
+                }
+                for (int rk = tid; rk < pen_distinct; rk += NT)
+                    if (pen_val[rk] >= tw && !(pen_raw[rk] >= tw)) bad = 1;
             }
-            for (int rk = tid; rk < pen_distinct; rk += NT)
-                if (pen_val[rk] >= tw && !(pen_raw[rk] >= tw)) bad = 1;
             cnt_ok = (int)__reduce_add_sync(0xffffffffu, (unsigned)cnt_ok);
             if (lane == 0) sc->wcount[warp] = cnt_ok;
             bad = __syncthreads_or(bad);
@@ -1085,6 +1153,8 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
             if (!bad && have_ok >= kq && tw > -ST_FLT_MAX) {
                 from_lists = true;
                 lmax = pm; lidx = pi;
+            } else if (lazy) {
+                continue;                                        // the lists do not decide this row: again, with tables
             } else {
                 // the bound does not hold for the penalised values: the element-wise pass after all
                 __syncthreads();
@@ -1164,27 +1234,26 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
                 ST_PROF(4);
                 if (!__syncthreads_or(fk_bad || !(tw > -ST_FLT_MAX)) &&
                     finish_running_topk(ownlist, wn1, tw, L, lcut, tc, mass, fastk ? kk : (need_topk ? kk : 0x7fffffff), need_topp, topp, u,
-                                        fin_bins, sc, token, lcut, total_mass))
+                                        fin_bins, sc, token, lcut, total_mass FK_PROF_ARGS))
                     done = true;
                 __syncthreads();
                 ST_PROF(7);
+                if (!done && lazy) continue;                     // the general path needs the tables: again, with them
             }
             // Wide rows of a penalised slot keep reading the stored logits: every count and sum is corrected afterwards by
             // the difference the (at most PEN_TABLE) penalised tokens make.  Without the patched maximum: element by element.
             bool corr = !done && from_lists;
             rw.pen_inline = rw.has_pen && !corr;
             // the penalised tokens of this warp's own region (corrections of the warp's own sums need no atomics)
+            // (dense loops over the ranks: the tables hold the tokens in ascending order, a region's are consecutive)
             auto for_my_pen = [&](auto f) {
-                for (int wi = (r_lo >> 5) + lane; r_lo < r_hi && wi < ((r_hi + 31) >> 5); wi += 32) {   // (an empty region owns no word)
-                    uint32_t rest = pen_bits[wi], rk = pen_prefix[wi];
-                    while (rest) { const int bit = __ffs(rest) - 1; rest &= rest - 1; f((wi << 5) + bit, pen_raw[rk], pen_val[rk]); ++rk; }
+                if (r_lo < r_hi) {
+                    const int rk_hi = r_hi < V ? (int)pen_prefix[r_hi >> 5] : pen_distinct;
+                    for (int rk = (int)pen_prefix[r_lo >> 5] + lane; rk < rk_hi; rk += 32) f(pen_tok[rk], pen_raw[rk], pen_val[rk]);
                 }
             };
             auto for_each_pen = [&](auto f) {
-                for (int wi = tid; wi < nw; wi += NT) {
-                    uint32_t rest = pen_bits[wi], rk = pen_prefix[wi];
-                    while (rest) { const int bit = __ffs(rest) - 1; rest &= rest - 1; f((wi << 5) + bit, pen_raw[rk], pen_val[rk]); ++rk; }
-                }
+                for (int rk = tid; rk < pen_distinct; rk += NT) f(pen_tok[rk], pen_raw[rk], pen_val[rk]);
             };
 
             if (!done) {
@@ -1343,34 +1412,40 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
                     for (int attempt = 0; attempt < 2; ++attempt) {
                     u64 acc_all = 0, acc_above = 0;
                     int wn = 0;
-                    for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
-                        float4 v[4];
-                        ST_LOAD_BATCH(v, i0)
-                        unsigned mk[4], anym = 0;
+                    auto mass_pass = [&](auto pi_tag, auto band_tag) {
+                        constexpr bool PI = decltype(pi_tag)::value;
+                        constexpr bool BAND = decltype(band_tag)::value;
+                        for (int i0 = r_lo; i0 < r_hi; i0 += 512) {
+                            float4 v[4];
+                            ST_LOAD_BATCH_T(v, i0, PI)
+                            unsigned mk[4], anym = 0;
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
-                            uint32_t q[4];
-                            mass.four(e, lk, q);
-                            acc_all += ((u64)q[0] + q[1]) + ((u64)q[2] + q[3]);   // 64-bit adds: a stored logit of a penalised token may exceed the maximum
-                            mk[k] = 0;
-                            if (band) {
+                            for (int k = 0; k < 4; ++k) {
+                                const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                                uint32_t q[4];
+                                mass.four(e, lk, q);
+                                acc_all += ((u64)q[0] + q[1]) + ((u64)q[2] + q[3]);   // 64-bit adds: a stored logit of a penalised token may exceed the maximum
+                                mk[k] = 0;
+                                if (BAND) {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    if (e[j] > t_hi) acc_above += q[j];
-                                    else if (e[j] >= t_lo && e[j] >= lk) mk[k] |= 1u << j;
+                                    for (int j = 0; j < 4; ++j) {
+                                        if (e[j] > t_hi) acc_above += q[j];
+                                        else if (e[j] >= t_lo && e[j] >= lk) mk[k] |= 1u << j;
+                                    }
                                 }
+                                anym |= mk[k];
                             }
-                            anym |= mk[k];
-                        }
-                        if (band && __ballot_sync(0xffffffffu, anym != 0u)) {
-                            const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
-                            unsigned incl = cnt;
+                            if (BAND && __ballot_sync(0xffffffffu, anym != 0u)) {
+                                const unsigned cnt = __popc(mk[0]) | (__popc(mk[1]) << 8) | (__popc(mk[2]) << 16) | (__popc(mk[3]) << 24);
+                                unsigned incl = cnt;
 #pragma unroll
-                            for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-                            warp_append_batch<WLIST>(mylist, wn, mk, v, (uint32_t)(i0 + lane * 4), lane, incl, cnt);
+                                for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+                                warp_append_batch<WLIST>(mylist, wn, mk, v, (uint32_t)(i0 + lane * 4), lane, incl, cnt);
+                            }
                         }
-                    }
+                    };
+                    if (PEN && rw.pen_inline) { if (band) mass_pass(BoolTag<PEN>{}, BoolTag<true>{}); else mass_pass(BoolTag<PEN>{}, BoolTag<false>{}); }
+                    else { if (band) mass_pass(BoolTag<false>{}, BoolTag<true>{}); else mass_pass(BoolTag<false>{}, BoolTag<false>{}); }
                     ST_PROF(11);
                     wkeep = warp_sum_u64(band ? acc_above : acc_all);       // kept mass of the region known so far
                     u64 wall_corr = 0;
@@ -1566,6 +1641,8 @@ __global__ void __launch_bounds__(NT, 1) k_sample_stream(const __grid_constant__
                 a.stats[row] = st;
             }
         }
+        break;
+      }
     }
 #ifdef COLINFER_PROFILE
     if (a.prof && tid == 0 && (int)blockIdx.x < a.prof_slots)

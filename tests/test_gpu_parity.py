@@ -235,9 +235,11 @@ def test_neutral_penalties_are_a_bit_exact_no_op():
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
 
 
+@pytest.mark.parametrize("rp", [1.2, 0.8])
 @pytest.mark.parametrize("cluster", [-1, 1])
-def test_many_distinct_history_ids_use_the_slow_count_path(cluster):
-    """More than 2048 distinct history ids in one table: counts come from scanning the history."""
+def test_many_distinct_history_ids_use_the_slow_count_path(cluster, rp):
+    """More than 2048 distinct history ids in one table: counts come from scanning the history.  The streaming kernel
+    builds no table for a greedy row whose penalties can only lower a logit (rp >= 1) as long as its lists decide it."""
     m = mods()
     V, H = 8192, 6000
     _lib.lib().colinfer_set_cluster_override(cluster)
@@ -247,10 +249,14 @@ def test_many_distinct_history_ids_use_the_slow_count_path(cluster):
     sp = m["SamplerParams"](1, V, "cuda")
     sp.set(0, temperature=0.0)
     sp.set_history(hist.cuda())
-    sp.set_penalties(0, 1.2, 0.3, 0.7)
+    sp.set_penalties(0, rp, 0.3, 0.7)
     out, st = m["draw"](logits.cuda(), sp, torch.zeros(1, dtype=torch.int32, device="cuda"), status=True)
-    want = O.argmax(O.penalties(logits[0, 0].numpy(), hist[0].numpy(), 1.2, 0.3, 0.7))
-    assert int(out) == want and int(st) == _lib.ROW_HIST_SLOW
+    want = O.argmax(O.penalties(logits[0, 0].numpy(), hist[0].numpy(), rp, 0.3, 0.7))
+    assert int(out) == want
+    if cluster == -1 and rp >= 1.0:
+        assert int(st) in (0, _lib.ROW_HIST_SLOW)      # (the tables are built after all when the lists do not decide the row)
+    else:
+        assert int(st) == _lib.ROW_HIST_SLOW
 
 
 @pytest.mark.parametrize("V", [20000, 151936])
