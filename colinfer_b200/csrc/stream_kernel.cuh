@@ -43,6 +43,9 @@ constexpr int HOFF = 4096;           // buckets kept above the sample's maximum 
 constexpr float RANGE = 50.0f;       // they cover distances up to RANGE * temperature (RANGE / 2 above a sample's maximum)
 constexpr int FASTK = 100;           // largest top_k finished from the group-maxima bound
 constexpr int BINS = 512;            // bins of the sample histogram and of the exact list selection
+constexpr int BINS_PAD = BINS + BINS / 16;   // the count histograms keep one spare word per sixteen bins: a lane that reads its
+                                              // sixteen consecutive bins then hits a bank of its own
+__host__ __device__ __forceinline__ int padbin(int i) { return i + (i >> 4); }
 constexpr float FAST_SCALE = 32.0f;  // sample-histogram bins per unit logit (16 units below the sample's maximum)
 constexpr float FIN_SCALE = 64.0f;   // list-selection bins per unit logit (8 units below the maximum)
 constexpr int WLIST = 2048 / (NT / 32);  // list entries per warp
@@ -474,13 +477,10 @@ __device__ __forceinline__ void warp_append_batch(Cand* mylist, int& wn, const u
 // including that bin.
 __device__ __forceinline__ int warp_count_bin(const uint32_t* hist, uint32_t kk, int lane, uint32_t& run_out) {
     constexpr int PERB = BINS / 32;
+    static_assert(PERB == 16, "padbin() pads after every sixteenth bin");
     uint32_t h[PERB]; uint32_t s = 0;
 #pragma unroll
-    for (int t = 0; t < PERB; t += 4) {
-        const uint4 x = *reinterpret_cast<const uint4*>(hist + lane * PERB + t);
-        h[t] = x.x; h[t + 1] = x.y; h[t + 2] = x.z; h[t + 3] = x.w;
-        s += x.x + x.y + x.z + x.w;
-    }
+    for (int t = 0; t < PERB; ++t) { h[t] = hist[lane * (PERB + 1) + t]; s += h[t]; }
     uint32_t incl = s;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) { const uint32_t x = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += x; }
@@ -493,6 +493,27 @@ __device__ __forceinline__ int warp_count_bin(const uint32_t* hist, uint32_t kk,
     for (int t = 0; t < PERB; ++t) { if (run + h[t] >= kk) { b = lane * PERB + t; run += h[t]; break; } run += h[t]; }
     run_out = __shfl_sync(0xffffffffu, run, hl);
     return __shfl_sync(0xffffffffu, b, hl);
+}
+
+// Sorts 128 ordered keys held four per lane (element lane * 4 + t) into descending order across the warp: a bitonic
+// network of 28 compare-exchange stages, the wide ones by shuffle.
+__device__ __forceinline__ void warp_sort_desc4(uint32_t (&a)[4], int lane) {
+#pragma unroll
+    for (int k = 2; k <= 128; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            uint32_t b[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int i = lane * 4 + t;
+                const uint32_t o = j >= 4 ? __shfl_xor_sync(0xffffffffu, a[t], j >> 2) : a[t ^ (j & 3)];
+                const bool take_max = ((i & j) == 0) == ((i & k) == 0);
+                b[t] = take_max ? max(a[t], o) : min(a[t], o);
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) a[t] = b[t];
+        }
+    }
 }
 
 // Top-k (kk <= FASTK), then top-p and the draw, from the warps' running lists after the single pass over the row.
@@ -510,9 +531,10 @@ static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo
     if (!(lo <= L)) return false;
     const float scale = L > lo ? (float)(BINS - 2) / (L - lo) : 0.0f;
     auto bin_of = [&](float l) { return min(BINS - 1, __float2int_rz((L - l) * scale)); };
-    for (int j = lane; j < wn; j += 32) { const float l = mine[j].l; if (l >= lo) atomicAdd(&hist[bin_of(l)], 1u); }
+    for (int j = lane; j < wn; j += 32) { const float l = mine[j].l; if (l >= lo) atomicAdd(&hist[padbin(bin_of(l))], 1u); }
     if (tid == 0) sc->fin_ok = 0;
     __syncthreads();
+    FK_PROF(8);
     uint32_t run_b;
     int bstar = warp_count_bin(hist, (uint32_t)kk, lane, run_b);     // every warp scans the bins itself
     bool complete;
@@ -538,6 +560,7 @@ static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo
         }
         if (lane == 0) sc->wcount[warp] = cnt;
         __syncthreads();
+        FK_PROF(9);
         int off = 0;
         for (int w2 = 0; w2 < warp; ++w2) off += sc->wcount[w2];
         const unsigned lt = (1u << lane) - 1u;
@@ -554,10 +577,7 @@ static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo
     if (warp == 0) {
         constexpr int PERC = FCAP / 32;
         float l[PERC]; uint32_t key[PERC], q[PERC];
-        // the candidates' ordered keys share the bits above the highest one in which key(lo) and key(L) differ
-        const uint32_t kd = f2key(L) ^ f2key(lo);
-        const int top = kd ? 31 - __clz(kd) : -1;
-        const uint32_t pre0 = top >= 0 ? (f2key(L) & ~((2u << top) - 1u)) : f2key(L);
+        static_assert(PERC == 4, "the warp sort holds four keys per lane");
         int surv = 0;
 #pragma unroll
         for (int t = 0; t < PERC; ++t) {
@@ -567,50 +587,58 @@ static __device__ bool finish_running_topk(const Cand* ownlist, int wn, float lo
             surv += (e < nc && l[t] >= lcut_in) ? 1 : 0;
         }
         surv = (int)__reduce_add_sync(0xffffffffu, (unsigned)surv);
+        // the candidates' keys in descending order (absent entries, key 0, come last): the kk-th largest is read off,
+        // the top-p pivot is where the running mass of the sorted candidates reaches its target
+        uint32_t sk[PERC];
+#pragma unroll
+        for (int t = 0; t < PERC; ++t) sk[t] = key[t];
+        warp_sort_desc4(sk, lane);
+        auto sorted_at = [&](int pos) {                              // key at sorted position pos (warp-uniform pos)
+            const int t = pos & 3;
+            const uint32_t mine = t == 0 ? sk[0] : t == 1 ? sk[1] : t == 2 ? sk[2] : sk[3];
+            return __shfl_sync(0xffffffffu, mine, pos >> 2);
+        };
         float cut = lcut_in;
         bool ok = surv > 0;
         if (ok && kk <= surv) {                                      // else fewer than k survive min-p: top-k removes nothing
-            uint32_t pre = pre0;
-#pragma unroll 1
-            for (int bit = top; bit >= 0; --bit) {
-                const uint32_t c = pre | (1u << bit);
-                int n = 0;
-#pragma unroll
-                for (int t = 0; t < PERC; ++t) n += key[t] >= c ? 1 : 0;
-                if ((int)__reduce_add_sync(0xffffffffu, (unsigned)n) >= kk) pre = c;
-            }
-            const float lk = key2f(pre);
+            const float lk = key2f(sorted_at(kk - 1));
             const float ck = lower_logit_for(scale_logit(lk, tc), tc, lk);
             ok = complete && ck >= lo && bin_of(ck) <= bstar;        // else a tie partner could lie outside the candidates
             cut = fmaxf(cut, ck);
         } else {
             ok = ok && complete;                                     // every logit >= the min-p cut is a candidate
         }
+        FK_PROF(10);
 #pragma unroll
         for (int t = 0; t < PERC; ++t) q[t] = l[t] >= cut ? mass(l[t]) : 0u;
         if (ok && need_topp) {
-            u64 s = 0;
+            // masses of the sorted candidates (the same function of the same logits), their running sum in sorted order
+            u64 sq[PERC], s = 0;
 #pragma unroll
-            for (int t = 0; t < PERC; ++t) s += q[t];
-            const u64 s1 = warp_sum_u64(s);
+            for (int t = 0; t < PERC; ++t) {
+                const float sl = sk[t] ? key2f(sk[t]) : CI_NEG_INF;
+                sq[t] = sl >= cut ? (u64)mass(sl) : 0ull;
+                s += sq[t];
+            }
+            const u64 incl = warp_incl_scan_u64(s, lane);
+            const u64 s1 = __shfl_sync(0xffffffffu, incl, 31);
             ok = s1 > 0;
             const u64 target = ceil_target(topp, s1);
-            uint32_t pre = pre0;
-#pragma unroll 1
-            for (int bit = top; bit >= 0; --bit) {
-                const uint32_t c = pre | (1u << bit);
-                u64 w = 0;
+            const unsigned hit = __ballot_sync(0xffffffffu, incl >= target);
+            int pos = 0;
+            if (hit) {
+                const int hl = __ffs(hit) - 1;
+                u64 run = incl - s; int tt = 0;
 #pragma unroll
-                for (int t = 0; t < PERC; ++t) w += key[t] >= c ? q[t] : 0u;
-                const u64 tot = ((u64)__reduce_add_sync(0xffffffffu, (unsigned)(w >> 24)) << 24) +
-                                __reduce_add_sync(0xffffffffu, (unsigned)(w & 0xFFFFFFu));
-                if (tot >= target) pre = c;
+                for (int t = 0; t < PERC; ++t) { run += sq[t]; if (run >= target) { tt = t; break; } }
+                pos = hl * PERC + __shfl_sync(0xffffffffu, tt, hl);
             }
-            const float lp = key2f(pre);
-            cut = fmaxf(cut, lower_logit_for(scale_logit(lp, tc), tc, lp));
+            const float lp = key2f(sorted_at(pos));
+            if (ok) cut = fmaxf(cut, lower_logit_for(scale_logit(lp, tc), tc, lp));
 #pragma unroll
             for (int t = 0; t < PERC; ++t) q[t] = l[t] >= cut ? q[t] : 0u;
         }
+        FK_PROF(11);
         u64 s = 0;
 #pragma unroll
         for (int t = 0; t < PERC; ++t) s += q[t];
@@ -1030,7 +1058,7 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
 #pragma unroll
             for (int o = 16; o; o >>= 1) sm = fmaxf(sm, __shfl_xor_sync(0xffffffffu, sm, o));
             if (lane == 0) sc->wf[warp] = sm;
-            for (int i = tid; i < BINS; i += NT) hist1[i] = 0u;
+            for (int i = tid; i < BINS_PAD; i += NT) hist1[i] = 0u;
             __syncthreads();
             lref = sc->wf[lane];
             // the bins of the bound hang from the smallest finite warp maximum plus 4: a few dominant tokens in the
@@ -1046,7 +1074,7 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
 #pragma unroll
                 for (int k = 0; k < 4 * NSB; ++k)
                     if (gm[k] > CI_NEG_INF && top < ST_POS_INF)
-                        atomicAdd(&hist1[max(0, min(BINS - 1, __float2int_rz((top - gm[k]) * FAST_SCALE)))], 1u);
+                        atomicAdd(&hist1[padbin(max(0, min(BINS - 1, __float2int_rz((top - gm[k]) * FAST_SCALE))))], 1u);
                 __syncthreads();
                 uint32_t have;
                 const int bk = warp_count_bin(hist1, (uint32_t)kq, lane, have);
@@ -1172,7 +1200,7 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
         uint32_t* fin_bins = fastk ? hist1 : reinterpret_cast<uint32_t*>(bins);   // wide rows keep their histogram in hist1
         if (sampled) {                                           // bins of the finish (the reduce below has the barriers after)
             if (fastk) __syncthreads();                          // every warp has read the sample's bins
-            for (int i = tid; i < BINS; i += NT) fin_bins[i] = 0u;
+            for (int i = tid; i < BINS_PAD; i += NT) fin_bins[i] = 0u;
         }
         if (!from_lists && lpos >= 0) {
             const float4 v = rw.load4(lpos);
