@@ -3,20 +3,25 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
 
-Workload (config.workload): the batched sampling sweep -- fp32 logits [B, 151936] ~ N(0, 2^2), per-row histories of
-2,048 ids with repetition / presence / frequency penalties, per-row temperature in U[0.5, 1.2], top_k in {0, 20, 100},
-top_p in U[0.8, 1.0], Philox draws keyed by (seed, position) -- seeded synthetic tensors standing in for model logits.
-One step = one fused draw() over the batch (B rows per GPU; with N GPUs every rank holds its own B rows -- weak
-scaling -- and the sampled ids are all-gathered over NCCL inside the timed region).  The batch (B x 608 KB = 630 MB at
+Workload of the headline line (config.workload): the batched sampling sweep -- fp32 logits [B, 151936] ~ N(0, 2^2),
+per-row histories of 2,048 ids with repetition / presence / frequency penalties, per-row temperature in U[0.5, 1.2],
+top_k in {0, 20, 100}, top_p in U[0.8, 1.0], Philox draws keyed by (seed, position) -- seeded synthetic tensors standing
+in for model logits.  One step = one fused draw() over the batch (B rows per GPU; with N GPUs every rank holds its own
+B rows -- weak scaling -- and the sampled ids are gathered inside the timed region).  The batch (B x 608 KB = 630 MB at
 B = 1024) is larger than the 126 MB L2, so no step is served from cache.
 
-value   whole-job rows/s with inputs resident in HBM (CUDA events on the launching stream, max over ranks).
+value   whole-job rows/s with inputs resident in HBM: blocks of --steps steps are timed with CUDA events on the
+        launching stream (max over ranks) until at least --min-seconds have been measured; the median block counts.
 e2e     the same through the public API with HOST buffers: every step copies the step's logits, histories and
         positions from pinned host memory to the device and the sampled ids back.
 roofline  algorithmic bytes per row (one read of every input + outputs) x rows / measured kernel time, against the
-        measured HBM copy rate of MEASURED_PEAKS.json (fallback 6,650 GB/s).
+        measured HBM copy rate of MEASURED_PEAKS.json (fallback 6,650 GB/s).  `traffic` is DRAM traffic from an ncu
+        capture recorded under profiles/ (with the commit it was taken at), scaled by rows -- not measured in this run.
+sweep   (one GPU) the other configurations, each timed per launch with the L2 flushed in between: the batched sweep at
+        8 / 64 / 256 rows, the bf16 large-vocabulary stress [512, 262144], the speculative verify (verifies/s).
+strong  (N > 1) fixed batches split over the ranks with sharding.shard_rows: 1024 rows of the sweep, 512 of the stress.
 cpu_baseline  the reference's torch path restated for the CPU (oracle/torch_cpu_path.py), timed on this box's host
-        cores on a bounded sample of the same batch.  --impl reference times only that.
+        cores on a bounded sample of the same batch.  --impl reference times only that, on the whole batch.
 """
 from __future__ import annotations
 
@@ -36,9 +41,7 @@ if ROOT not in sys.path:
 V = 151_936
 HIST = 2048
 CPU_SAMPLE_ROWS = 256
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_sample_stream launch divided by its rows (ncu capture at
-# B = 256, summarised in profiles/k_sample_stream_config3_b256_ncu.md; traffic grows in proportion to the rows).
-NCU_TRAFFIC_BYTES_PER_ROW = 762_200
+TRAFFIC_RECORD = os.path.join(ROOT, "profiles", "k_sample_stream_config3_traffic.json")
 
 
 def measured_peak():
@@ -47,6 +50,26 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def recorded_traffic(kernel_name: str, rows: int):
+    """DRAM bytes of one launch, from the ncu capture recorded under profiles/ (None when there is no record)."""
+    try:
+        with open(TRAFFIC_RECORD) as f:
+            rec = json.load(f)
+        if rec.get("kernel") != kernel_name:
+            return None, None
+        return int(rec["dram_bytes_per_row"] * rows), {k: rec.get(k) for k in ("captured_at_commit", "captured_rows", "source")}
+    except Exception:
+        return None, None
+
+
+def config_of(B: int, world: int) -> dict:
+    """The `config` object of the headline line: identical for both arms of a run."""
+    return {"workload": f"config3 batched sampling sweep: fp32 logits [{B}, {V}] per GPU, history {HIST}, "
+                        "penalties, T~U[0.5,1.2], top_k in {0,20,100}, top_p~U[0.8,1.0]",
+            "rows_per_gpu": B, "vocab": V, "l2": "inputs (630 MB per GPU) larger than L2, no flush needed",
+            "sharding": f"rows x{world}, ids gathered" if world > 1 else "single GPU"}
 
 
 class ClockSampler:
@@ -60,9 +83,10 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            time.sleep(0.3)                                # the first sample lands before the region starts
         except Exception:
             self.proc = None
         return self
@@ -73,7 +97,6 @@ class ClockSampler:
 
     def __exit__(self, *a):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -89,15 +112,15 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def cpu_baseline_rows_per_s(w, reps: int, warm: int):
-    """The reference's torch path on host cores over the first CPU_SAMPLE_ROWS rows of the batch."""
+def cpu_rows_per_s(w, n, reps: int, warm: int):
+    """The reference's torch path on host cores over the first n rows of the batch."""
     import torch
     from oracle import torch_cpu_path as T
     try:                                                   # every host core this process may use (launchers pin OMP to 1)
         torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     except Exception:
         pass
-    n = min(CPU_SAMPLE_ROWS, w["logits"].shape[0])
+    n = min(n, w["logits"].shape[0])
     sub = {k: (v[:n] if isinstance(v, torch.Tensor) else v) for k, v in w.items() if k != "params"}
     sub["params"] = {k: v[:n] for k, v in w["params"].items()}
     times = []
@@ -110,22 +133,23 @@ def cpu_baseline_rows_per_s(w, reps: int, warm: int):
 
 
 def run_reference(args):
-    """--impl reference: the CPU restatement of the reference path, rank 0 only."""
+    """--impl reference: the CPU restatement of the reference path over the whole batch, rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
     from colinfer_b200 import workloads as wl
-    w = wl.config3(CPU_SAMPLE_ROWS, V=V, H=HIST)
-    n, times, threads = cpu_baseline_rows_per_s(w, reps=args.steps, warm=args.warmup)
+    B = args.batch
+    w = wl.config3(B, V=V, H=HIST)
+    n, times, threads = cpu_rows_per_s(w, B, reps=args.steps, warm=args.warmup)
     total = sum(times)
     value = n * len(times) / total
     line = {"impl": "reference", "metric": "sampled rows/s", "value": value, "unit": "rows/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"config3 batched sampling sweep, vocab {V}, history {HIST}", "rows_per_step": n},
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(B, world),
             "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
-                             "sample": f"{n} rows of the batch per step (torch CPU restatement of the reference path, "
-                                       f"{os.cpu_count()} host cpus)"},
+                             "sample": f"all {n} rows of one GPU's batch per step (torch CPU restatement of the reference "
+                                       f"path, {os.cpu_count()} host cpus)"},
             "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -257,14 +281,91 @@ def run_rescore(args):
     print(json.dumps(line), flush=True)
 
 
+def per_launch_us(torch, fn, flush, reps: int, warm: int = 3):
+    """Median / best device time of one call of fn (CUDA events on the current stream), the L2 overwritten in between."""
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        flush.zero_()                                      # 256 MB of writes: nothing of the inputs stays in the 126 MB L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(ts), min(ts)
+
+
+def run_sweep(torch, dev, lib, peak, reps: int):
+    """The other configurations on one GPU, per launch, L2 flushed between launches."""
+    from colinfer_b200 import _lib, workloads as wl
+    from colinfer_b200.spec.accept import draw
+    from colinfer_b200.spec.verify import spec_verify
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {"timing": "per launch, CUDA events, L2 flushed (256 MB written) between launches; median and best of "
+                     f"{reps}", "of_peak": peak}
+
+    def entry(us_med, us_best, units, bytes_unit, kernel, unit_name):
+        gbs = bytes_unit * units / (us_med * 1e-6) / 1e9
+        return {"kernel_us": round(us_med, 2), "kernel_us_best": round(us_best, 2), unit_name + "_per_s": units / (us_med * 1e-6),
+                "bytes_per_" + unit_name: bytes_unit, "gbs": gbs, "frac": gbs / peak, "frac_of_nominal_8000": gbs / 8000.0,
+                "kernel": kernel}
+
+    few = lib.colinfer_max_active_clusters(V, _lib.F32)
+    c3 = {}
+    for B in (8, 64, 256):
+        w = wl.config3(B, V=V, H=HIST)
+        sp = wl.sampler_params(w["params"], V, dev)
+        logits, pos = w["logits"].to(dev), w["pos"].to(dev)
+        med, best = per_launch_us(torch, lambda: draw(logits, sp, pos), flush, reps)
+        c3[str(B)] = entry(med, best, B, wl.bytes_per_row(V, 4, False, HIST), "k_sample" if B <= few else "k_sample_stream", "row")
+        del logits, sp
+    out["config3_rows"] = c3
+    # bf16 large-vocabulary stress: [512, 262144], 30 % grammar mask, top_k 1000, top_p 0.98, min_p 0.01
+    w = wl.config4()
+    VL = wl.V_LARGE
+    sp = wl.sampler_params(w["params"], VL, dev)
+    logits, pos, mask = w["logits"].to(dev), w["pos"].to(dev), w["mask"].to(dev)
+    med, best = per_launch_us(torch, lambda: draw(logits, sp, pos, mask=mask), flush, reps)
+    out["config4_bf16_512x262144"] = entry(med, best, 512, wl.bytes_per_row(VL, 2, True, 0), "k_sample_stream", "row")
+    del logits, mask, sp
+    # speculative verify: k = 8 drafts per slot, temperature 0.8, top_p 0.95; one slot (latency) and 64 slots
+    ver = {}
+    for B in (1, 64):
+        c2 = wl.config2(V=V, k=8, B=B)
+        sp = wl.sampler_params(c2["params"], V, dev)
+        target, draft = c2["target"].to(dev), c2["draft"].to(dev)
+        d_ids = draw(draft, sp, None, u=c2["ud"].to(dev))
+        ua, us = c2["ua"].to(dev), c2["us"].to(dev)
+        med, best = per_launch_us(torch, lambda: spec_verify(target, draft, d_ids, sp, ua, us), flush, max(5, reps // 2))
+        e = entry(med, best, B, 17 * V * 4, "k_sample / k_sample_stream x2 + k_verify_finish", "verify")
+        ver[str(B)] = e
+        del target, draft
+    out["config2_verify_slots"] = ver
+    return out
+
+
+def numa_node_of(torch, index: int):
+    try:
+        p = torch.cuda.get_device_properties(index)
+        bus = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            return int(f.read().strip())
+    except Exception:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1024, help="rows per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the other configurations (and the fixed-batch split)")
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="measure blocks of --steps steps for at least this long")
     ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs", "rescore"],
                     help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives; "
                          "rescore: draft-head candidate rescoring (256 candidates of a 69,632 x 2560 BF16 lm_head per slot)")
@@ -283,11 +384,11 @@ def main():
     import torch
     import torch.distributed as dist
     from colinfer_b200 import _lib, workloads as wl
-    from colinfer_b200.sharding import gather_ids
+    from colinfer_b200.sharding import gather_ids, shard_rows
     from colinfer_b200.spec.accept import draw
 
-    _lib.lib()                                             # fail loudly if the CUDA library is missing
-    _lib.lib().colinfer_set_cluster_override(args.cluster)
+    lib = _lib.lib()                                       # fail loudly if the CUDA library is missing
+    lib.colinfer_set_cluster_override(args.cluster)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -320,26 +421,36 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed_blocks(fn, steps, min_seconds, max_blocks=2000):
+        """Blocks of `steps` calls, each bracketed by a barrier + synchronize and timed with CUDA events, until
+        min_seconds of device time have been measured (three blocks at least).  Returns the per-block ms, max over ranks."""
+        blocks, total = [], 0.0
+        while (len(blocks) < 3 or total < min_seconds * 1e3) and len(blocks) < max_blocks:
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            barrier()
+            ms = e0.elapsed_time(e1)
+            if world > 1:                                  # every rank leaves the loop after the same block
+                t = torch.tensor([ms], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            blocks.append(ms)
+            total += ms
+        return blocks
+
     for _ in range(args.warmup):
         step()
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
-        e0.record()
-        for _ in range(args.steps):
-            ids = step()
-        e1.record()
-        barrier()
-    ms = e0.elapsed_time(e1)
-    # kernel-only time of the same launches (no gather), events on the launching stream
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    k0.record()
-    for _ in range(args.steps):
-        draw(logits, sp, pos)
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / args.steps
+        blocks = timed_blocks(step, args.steps, args.min_seconds)
+        # kernel-only time of the same launches (no gather), events on the launching stream
+        kblocks = timed_blocks(lambda: draw(logits, sp, pos), args.steps, min(args.min_seconds, 0.3))
+    ms = statistics.median(blocks)
+    kernel_ms = statistics.median(kblocks) / args.steps
 
     # end to end: host buffers in, ids out, every step
     h_logits = w["logits"].pin_memory()
@@ -368,40 +479,71 @@ def main():
         e2e_step()
     x1.record()
     barrier()
-    e2e_ms = x0.elapsed_time(x1)
-
-    t = torch.tensor([ms, kernel_ms, e2e_ms], dtype=torch.float64, device=dev)
+    e2e_ms_own = x0.elapsed_time(x1)
+    h2d_bytes = int(h_logits.numel() * 4 + h_hist.numel() * 4 + h_pos.numel() * 4)
+    e2e_ms = e2e_ms_own
+    h2d_rates = [h2d_bytes * e2e_steps / (e2e_ms_own * 1e-3) / 1e9]
     if world > 1:
+        t = torch.tensor([e2e_ms_own], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, kernel_ms, e2e_ms = t.tolist()
+        e2e_ms = float(t.item())
+        allr = [torch.zeros(1, dtype=torch.float64, device=dev) for _ in range(world)]
+        dist.all_gather(allr, torch.tensor([h2d_rates[0]], dtype=torch.float64, device=dev))
+        h2d_rates = [float(x.item()) for x in allr]
+    del d_logits, h_logits
+
+    # fixed batches split over the ranks (strong scaling): every rank runs the kernel on its block, the ids are gathered
+    strong = None
+    if world > 1 and not args.no_sweep:
+        strong = {}
+        for name, total_rows, maker, vv, kw_mask in (("config3_1024_rows", 1024, lambda: wl.config3(1024, V=V, H=HIST), V, False),
+                                                     ("config4_bf16_512_rows", 512, lambda: wl.config4(), wl.V_LARGE, True)):
+            full = maker()
+            mine = shard_rows(full, total_rows, world, rank)
+            sps = wl.sampler_params(mine["params"], vv, dev)
+            lg, ps = mine["logits"].to(dev), mine["pos"].to(dev)
+            mk = mine["mask"].to(dev) if kw_mask else None
+            fn = lambda: gather_ids(draw(lg, sps, ps, mask=mk), total_rows)
+            for _ in range(3):
+                fn()
+            bl = timed_blocks(fn, args.steps, 0.2)
+            sms = statistics.median(bl) / args.steps
+            strong[name] = {"rows_total": total_rows, "rows_per_gpu": int(lg.size(0)), "ms_per_step": sms,
+                            "value": total_rows / (sms * 1e-3), "unit": "rows/s",
+                            "note": "device-timed incl. the id gather; fewer rows than 2 x SMs per GPU: occupancy-limited"}
+            del lg, full, mine
 
     if rank == 0:
         # which kernel colinfer_sample ran: few rows (at most the clusters the device holds at once) take the
         # cluster-resident kernel, more rows the streaming kernel; --cluster forces one of them
-        few = B <= _lib.lib().colinfer_max_active_clusters(V, _lib.F32)
+        few = B <= lib.colinfer_max_active_clusters(V, _lib.F32)
         kernel_name = "k_sample" if args.cluster > 0 or (args.cluster == 0 and few) else "k_sample_stream"
         peak, peak_kind = measured_peak()
         achieved = bytes_row * B / (kernel_ms * 1e-3) / 1e9
+        traffic, traffic_src = recorded_traffic(kernel_name, B)
         line = {
             "metric": "sampled rows/s", "value": n_rows * args.steps / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"config3 batched sampling sweep: fp32 logits [{B}, {V}] per GPU, history {HIST}, "
-                                   "penalties, T~U[0.5,1.2], top_k in {0,20,100}, top_p~U[0.8,1.0]",
-                       "rows_per_gpu": B, "vocab": V, "l2": "inputs (630 MB per GPU) larger than L2, no flush needed",
-                       "sharding": f"rows x{world}, ids all-gathered" if world > 1 else "single GPU"},
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(B, world),
+            "timed_region_s": sum(blocks) * 1e-3, "blocks": len(blocks),
+            "block_ms": {"median": ms, "min": min(blocks), "max": max(blocks)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind} copy rate", "frac_of_nominal_8000": achieved / 8000.0,
                          "bytes_per_row": bytes_row, "kernel": kernel_name, "kernel_ms": kernel_ms,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_ROW * B if kernel_name == "k_sample_stream" else None},
+                         "traffic": traffic, "traffic_from_capture": traffic_src},
             "e2e": {"value": n_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "steps": e2e_steps,
-                    "h2d_bytes_per_step": int(h_logits.numel() * 4 + h_hist.numel() * 4 + h_pos.numel() * 4),
-                    "d2h_bytes_per_step": int(h_ids.numel() * 8)},
-            "gpu_launches": args.steps,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(h_ids.numel() * 8),
+                    "h2d_gbs_per_rank": [round(x, 2) for x in h2d_rates],
+                    "gpu_numa_nodes": [numa_node_of(torch, i) for i in range(world)]},
+            "gpu_launches": args.steps * len(blocks),
             "clocks": clk.summary(),
         }
+        if strong is not None:
+            line["strong"] = strong
+        if world == 1 and not args.no_sweep:
+            line["sweep"] = run_sweep(torch, dev, lib, peak, reps=15)
         if world == 1 and not args.no_cpu_baseline:
-            n, times, threads = cpu_baseline_rows_per_s(w, reps=3, warm=1)
+            n, times, threads = cpu_rows_per_s(w, CPU_SAMPLE_ROWS, reps=3, warm=1)
             line["cpu_baseline"] = {"value": n / statistics.median(times), "unit": "rows/s", "cores": threads, "kind": "port",
                                     "sample": f"first {n} rows of the batch, median of 3 (torch CPU restatement of the "
                                               f"reference path, {os.cpu_count()} host cpus)"}

@@ -191,6 +191,7 @@ __global__ void __launch_bounds__(ICDF_THREADS) k_inverse_cdf(const float* __res
     __syncthreads();
     double total = 0.0, woff = 0.0;
     for (int w = 0; w < nwarps; ++w) { if (w < warp) woff += wtot[w]; total += wtot[w]; }
+    if (threadIdx.x == 0 && !(total > 0.0)) result = 0;          // a row without mass: no prefix lies below u * 0 (the reference counts none)
     const double t = (double)u[row] * total;
     // first index whose inclusive prefix reaches t; the owning warp is the first whose inclusive total reaches it
     if (woff < t && woff + wt >= t) {
@@ -318,7 +319,9 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_finish(const __grid_const
                 float ld = load_logit(a.dl, a.dtype, ((size_t)b * k + j) * V + d);
                 if (!mask_allows(mrow, (int)d)) { lt = CI_NEG_INF; ld = CI_NEG_INF; }
                 const double p = token_prob(st_t[j], lt, d), q = token_prob(st_d[j], ld, d);
-                ok = (double)a.ua[(size_t)b * k + j] * q <= p;
+                // (a draft token the target gives no probability -- masked, or outside its kept set -- is never accepted,
+                // whatever the draft thought of it: 0 <= 0 must not pass)
+                ok = p > 0.0 && (double)a.ua[(size_t)b * k + j] * q <= p;
             }
             if (!ok) break;
         }

@@ -1518,7 +1518,8 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
                             ok = s_above < target && target <= s_above + s_band;   // the pivot lies inside the band
                             if (ok) {
                                 const float base = t_hi < ST_POS_INF ? t_hi : L;
-                                const float scale = (float)(BINS - 2) / fmaxf(base - t_lo, 1e-30f);
+                                // (a small nucleus gathers everything above the cut: the bins span [cut, base], not [-max, base])
+                                const float scale = (float)(BINS - 2) / fmaxf(base - fmaxf(t_lo, lk), 1e-30f);
                                 float lp;
                                 ok = lean_select([&](int i) { return glist[i].l; }, [&](int i) { return (u64)glist[i].q; }, n, base, scale,
                                                  target - s_above, bins, sc, lp);

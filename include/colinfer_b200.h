@@ -114,7 +114,7 @@ int colinfer_spec_accept(const int64_t* pred, const int64_t* tok, const int64_t*
                          int64_t* out_tok, int32_t* n, int B, int k1, int S, void* stream);
 
 /* Rejection verify with the (p - q)+ residual resample (no counterpart in the reference, which accepts by exact match;
- * semantics: accept draft i iff ua[i] * q_i(d_i) <= p_i(d_i); at the first rejection j emit a draw from
+ * semantics: accept draft i iff p_i(d_i) > 0 and ua[i] * q_i(d_i) <= p_i(d_i); at the first rejection j emit a draw from
  * normalize(max(p_j - q_j, 0)) with us[j]; if none is rejected emit a draw from p_k with us[k]; temperature <= 0 uses
  * the argmax rule).  target_logits [B, k+1, V], draft_logits [B, k, V] (dtype), mask [B, k+1, W] or NULL (applies to
  * both), draft_ids [B, k] int64, ua [B, k], us [B, k+1].  scratch: B * (2k + 1) colinfer_row_stats and B * (k + 1)

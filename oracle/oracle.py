@@ -308,7 +308,7 @@ def spec_verify_reject(target_logits, draft_logits, draft_ids, temperature, top_
     target_logits [k+1, V], draft_logits [k, V], draft_ids [k], ua [k] accept uniforms, us [k+1] sampling uniforms.
     p_i, q_i = processed() of target / draft row i (the same parameters; the mask, if any, applies to both).
     temperature <= 0: accept while draft == argmax(target row), emit the argmax of the first mismatching row.
-    Else accept draft i iff ua_i * q_i(d_i) <= p_i(d_i); at the first rejection j emit inverse_cdf(max(p_j - q_j, 0),
+    Else accept draft i iff p_i(d_i) > 0 and ua_i * q_i(d_i) <= p_i(d_i); at the first rejection j emit inverse_cdf(max(p_j - q_j, 0),
     us_j) (from p_j if that residual has no mass); if none is rejected emit inverse_cdf(p_k, us_k).
     Returns dict(n_accept, token, margins)."""
     tl = np.asarray(target_logits, dtype=F32)
@@ -332,7 +332,7 @@ def spec_verify_reject(target_logits, draft_logits, draft_ids, temperature, top_
         d = int(draft_ids[j])
         lhs, rhs = float(F32(ua[j])) * q[d], p[d]
         accept_margin = min(accept_margin, abs(lhs - rhs) / max(rhs, lhs, 1e-300))
-        if lhs <= rhs:
+        if rhs > 0 and lhs <= rhs:                     # a token the target gives no probability is never accepted
             continue
         res = np.maximum(p - q, 0.0)
         if res.sum() <= 0:

@@ -16,7 +16,9 @@ import sys
 import numpy as np
 import torch
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("COLINFER_REF", "")
+if not os.path.isdir(os.path.join(ref, "engine")):
+    sys.exit("usage: make_golden.py <reference checkout>   (or set COLINFER_REF)")
 sys.path.insert(0, ref)
 sys.dont_write_bytecode = True
 from engine.runtime.sampler import SamplerParams, apply_mask  # noqa: E402

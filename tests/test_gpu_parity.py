@@ -329,6 +329,15 @@ def test_inverse_cdf_matches_reference_vectors(golden):
     assert np.array_equal(out.cpu().numpy(), golden["icdf_wout"])
 
 
+def test_inverse_cdf_row_without_mass_gives_index_zero():
+    """engine/spec/accept.py:36-40 counts the prefixes below u * total: none when the row has no mass at all."""
+    m = mods()
+    P = torch.zeros(3, 77, device="cuda")
+    P[1, 40] = 0.25
+    out = m["inverse_cdf"](P, torch.tensor([0.3, 0.3, 1.0], device="cuda"))
+    assert out.tolist() == [0, 40, 0]
+
+
 def test_inverse_cdf_marginal_is_exact():
     """Reference tests/test_spec_accept.py:12-21."""
     m = mods()
@@ -648,6 +657,43 @@ def test_spec_verify_small_vocab_many_slots():
     n = verify_case(target, draft, wl.open_unit(g, B, k), wl.open_unit(g, B, k), wl.open_unit(g, B, k + 1), params, V, k,
                     mask=wl.pack_mask(allowed))
     assert len(set(n.tolist())) >= 3                               # several accept lengths occur
+
+
+def test_spec_verify_never_accepts_a_token_the_target_excludes():
+    """Drafts that are not drawn from q (a suffix or argmax drafter): a draft id the grammar mask forbids, or one outside
+    the target's top-k, has p = 0 (and possibly q = 0 too) -- it must be rejected and never emitted."""
+    m = mods()
+    g = torch.Generator().manual_seed(77)
+    B, k, V = 64, 3, 512
+    target = torch.randn(B, k + 1, V, generator=g) * 2
+    draft = (target[:, :k] + torch.randn(B, k, V, generator=g) * 0.3).contiguous()
+    allowed = torch.rand(B, k + 1, V, generator=g) < 0.7
+    allowed[..., 5] = True
+    mask = wl.pack_mask(allowed)
+    params = wl._params(B, V, 0.8, 10, 1.0, 0.0)
+    sp = wl.sampler_params(params, V, "cuda")
+    # even slots: the first draft is a masked token; odd slots: the target's 30th largest allowed logit (outside top-10)
+    d_ids = torch.zeros(B, k, dtype=torch.int64)
+    for b in range(B):
+        row = target[b, 0].clone()
+        if b % 2 == 0:
+            d_ids[b, 0] = int(torch.nonzero(~allowed[b, 0])[0])
+        else:
+            row[~allowed[b, 0]] = -float("inf")
+            d_ids[b, 0] = int(torch.argsort(row, descending=True)[29])
+        d_ids[b, 1:] = 5
+    ua = torch.full((B, k), 1e-7)                                  # the most permissive accept uniforms
+    us = wl.open_unit(g, B, k + 1)
+    out, n = m["spec_verify"](target.cuda(), draft.cuda(), d_ids.cuda(), sp, ua.cuda(), us.cuda(), mask=mask.cuda())
+    out, n = out.cpu(), n.cpu()
+    assert (n == 1).all()                                          # rejected at the first position
+    for b in range(B):
+        tok = int(out[b, 0])
+        assert tok != int(d_ids[b, 0]) and bool(allowed[b, 0, tok])
+        r = O.spec_verify_reject(target[b].numpy(), draft[b].numpy(), d_ids[b].numpy(), 0.8, 10, 1.0, -np.inf, ua[b].numpy(),
+                                 us[b].numpy(), target_mask=mask[b].numpy())
+        assert r["n_accept"] == 0
+        assert tok == r["token"] or r["margin"] < 1e-5
 
 
 def test_spec_verify_preserves_the_target_distribution():
