@@ -53,6 +53,7 @@ def check_tokens(got, want, info, what=""):
         m = min(info[i]["margin"], info[i]["margin_top_p"])
         assert m < MARGIN, f"{what}: row {i}: got {got[i]}, oracle {want[i]}, margin {m:.3e}"
     assert len(bad) <= max(1, len(got) // 200), f"{what}: {len(bad)} boundary rows of {len(got)}"
+    print(f"[parity] {what}: {len(got)} rows, {len(bad)} differ from the oracle (all within the {MARGIN:g} margin)")
     return len(bad)
 
 
@@ -501,7 +502,40 @@ def test_config1_grammar_mask():
 @pytest.mark.parametrize("B", [8, 64])
 def test_config3_batched_sweep_vs_oracle(B):
     w = wl.config3(B)
-    run_workload(w, wl.V_QWEN, use_philox=True)
+    nb, _ = run_workload(w, wl.V_QWEN, use_philox=True)
+    assert nb == 0                                                 # on these seeds no row differs at all
+
+
+def test_config3_all_1024_rows_vs_oracle():
+    """The benchmarked batch itself, every row against the oracle (the oracle runs on the host cores in parallel)."""
+    from _oracle_pool import oracle_draw_rows
+    m = mods()
+    B, V = 1024, wl.V_QWEN
+    w = wl.config3(B)
+    sp = wl.sampler_params(w["params"], V, "cuda")
+    out, st = m["draw"](w["logits"].cuda(), sp, w["pos"].cuda(), status=True)
+    torch.cuda.synchronize()
+    want, info = oracle_draw_rows(w["logits"].numpy(), np_params(w["params"]), w["pos"].numpy(),
+                                  history=w["params"]["history"].numpy(), hist_len=w["params"]["hist_len"].numpy())
+    assert (st.cpu().numpy() & ~(_lib.ROW_HIST_SLOW | _lib.ROW_SELECT_SLOW) == 0).all()
+    assert check_tokens(out.cpu().numpy(), want, info, "config3 B=1024, all rows") == 0
+
+
+def test_config4_all_512_rows_vs_oracle():
+    """The bf16 large-vocabulary stress at full size (512 x 262,144, 30 % grammar mask), every row against the oracle."""
+    from _oracle_pool import oracle_draw_rows
+    m = mods()
+    V = wl.V_LARGE
+    w = wl.config4()
+    sp = wl.sampler_params(w["params"], V, "cuda")
+    out, st = m["draw"](w["logits"].cuda(), sp, w["pos"].cuda(), mask=w["mask"].cuda(), status=True)
+    torch.cuda.synchronize()
+    want, info = oracle_draw_rows(w["logits"].float().numpy(), np_params(w["params"]), w["pos"].numpy(), mask=w["mask"].numpy())
+    assert (st.cpu().numpy() & ~_lib.ROW_SELECT_SLOW == 0).all()
+    got = out.cpu().numpy()
+    assert check_tokens(got, want, info, "config4 B=512, all rows") == 0
+    for b in range(0, 512, 37):
+        assert O.mask_bits(w["mask"][b, 0].numpy(), V)[int(got[b, 0])]
 
 
 def test_config3_full_batch_properties():
@@ -610,6 +644,50 @@ def test_spec_accept_lengths_cover_every_n():
         assert out[j, j] == pred[j, j]
 
 
+def _stub_logits(ctx, V):
+    """A deterministic stand-in for a model: the logits of the next token are a fixed function of the last three tokens."""
+    seed = 0
+    for t in ctx[-3:]:
+        seed = (seed * 1000003 + int(t) + 17) % (2**31 - 1)
+    return torch.randn(V, generator=torch.Generator().manual_seed(seed)) * 2.0
+
+
+@pytest.mark.parametrize("sampled", [False, True])
+def test_speculative_cycles_reproduce_plain_decoding(sampled):
+    """The reference's end-to-end property (tests/test_mtp4.py:284-328): cycles of verify -- draw() over the k + 1 rows
+    at positions pos + r, then the exact-match accept -- emit the same stream as decoding one token at a time with
+    sample(), whatever the drafts are; every accept length 1 .. k + 1 occurs."""
+    m = mods()
+    V, k, N = 4096, 2, 48
+    sp = m["SamplerParams"](1, V, "cuda")
+    if sampled:
+        sp.set(0, temperature=0.8, top_k=50, top_p=0.95, seed=1234)
+    prompt = [3, 1, 4, 1, 5]
+    # plain decoding: the token at sequence index p is drawn with the uniform at counter p
+    want = list(prompt)
+    for _ in range(N + 8):
+        row = _stub_logits(want, V)[None].cuda()
+        want.append(int(m["sample"](row, sp, torch.tensor([len(want)], dtype=torch.int32, device="cuda"))))
+    g = torch.Generator().manual_seed(5)
+    seq, seen = list(prompt), set()
+    while len(seq) < len(prompt) + N:
+        n0 = len(seq)
+        j = int(torch.randint(0, k + 1, (1,), generator=g))        # j right drafts, then a wrong one
+        drafts = [want[n0 + i] for i in range(k)]
+        if j < k:
+            drafts[j] = (drafts[j] + 1) % V
+        rows = torch.stack([_stub_logits(seq + drafts[:r], V) for r in range(k + 1)])[None].cuda()   # [1, k + 1, V]
+        pred = m["draw"](rows, sp, torch.tensor([n0], dtype=torch.int32, device="cuda"))
+        tok = torch.tensor([[seq[-1]] + drafts], dtype=torch.int64, device="cuda")
+        out_tok, n = m["spec_accept"](pred, tok)
+        n = int(n[0])
+        assert n == j + 1
+        seen.add(n)
+        seq += out_tok[0, :n].tolist()
+    assert seq[:len(prompt) + N] == want[:len(prompt) + N]
+    assert seen == set(range(1, k + 2))
+
+
 def verify_case(target, draft, ud, ua, us, params, V, k, mask=None):
     """Draft tokens are drawn from the draft's processed distribution with ud; then the verify is compared."""
     m = mods()
@@ -712,6 +790,60 @@ def test_spec_verify_preserves_the_target_distribution():
     emp = torch.bincount(out[:, 0], minlength=V).double().cpu() / B
     p = torch.softmax(tl[0, 0].double(), -1)
     assert 0.5 * (emp - p).abs().sum().item() < 0.02
+
+
+# ------------------------------------------------------------------------------------------------ the mass horizon
+# Masses are integers in units of 2^-30 of the largest token's: a logit more than ~21.5 temperatures below the maximum
+# has mass 0 and can never be drawn, one a little above that is rounded coarsely.  Against the reference's fp32 softmax
+# this moves at most V * 2^-31 of the mass (7.1e-5 at 151,936 tokens) -- the bound the next tests pin.
+HORIZON_BOUND = 151936 * 2.0 ** -31
+
+
+def _bulk_row(gap_t, T, V=151936, seed=3):
+    """One dominant token; every other logit `gap_t` temperatures below it (with a little jitter)."""
+    g = torch.Generator().manual_seed(seed)
+    row = 3.0 - gap_t * T + 0.05 * torch.randn(V, generator=g)
+    row[1000] = 3.0
+    return row
+
+
+@pytest.mark.parametrize("gap_t", [18.0, 20.0, 21.0, 23.0, 24.0])
+def test_mass_horizon_moves_at_most_its_bound(gap_t):
+    m = mods()
+    V, T = 151936, 0.7
+    row = _bulk_row(gap_t, T)
+    one = lambda v, dt=torch.float32: torch.tensor([v], dtype=dt, device="cuda")  # noqa: E731
+    got = m["processed_probs"](row[None].cuda(), one(T), one(V, torch.int32), one(1.0), one(float("-inf")))[0].cpu().numpy().astype(np.float64)
+    pr = O.processed(row.numpy(), T, V, 1.0, -np.inf)
+    want = pr["probs"]
+    assert np.abs(got - want).sum() <= 2.0 * HORIZON_BOUND + 1e-6      # total variation <= the bound
+    assert not np.any((got > 0) & ~(want > 0))                          # nothing outside the reference's support
+    assert np.all(want[(want > 0) & ~(got > 0)] <= 2.0 ** -30)          # what is dropped is below one mass unit each
+    # draws: the token's interval of the reference CDF lies within the bound of u
+    us = [0.5, 0.99999, 1.0 - 2.0 ** -24, 1.0]
+    sp = m["SamplerParams"](len(us), V, "cuda")
+    for b in range(len(us)):
+        sp.set(b, temperature=T, seed=b)
+    toks = m["draw"](row[None, None].expand(len(us), 1, V).contiguous().cuda(), sp, None, u=torch.tensor(us, device="cuda")[:, None])
+    cdf = np.cumsum(want)
+    for u, t in zip(us, toks[:, 0].tolist()):
+        assert want[t] > 0
+        lo, hi = (cdf[t - 1] if t else 0.0), cdf[t]
+        assert lo - 2.0 * HORIZON_BOUND <= np.float32(u) <= hi + 2.0 * HORIZON_BOUND, (u, t, lo, hi)
+
+
+def test_top_k_reaching_below_the_horizon_keeps_the_reference_support_above_it():
+    """A peaked row whose k-th largest logit lies below the horizon: the reference keeps k tokens, 49 of them with
+    probability ~1e-13; here they carry no mass.  The probabilities agree to far better than 1e-5."""
+    m = mods()
+    V, T = 151936, 1.0
+    row = _bulk_row(30.0, T, seed=5)
+    one = lambda v, dt=torch.float32: torch.tensor([v], dtype=dt, device="cuda")  # noqa: E731
+    got = m["processed_probs"](row[None].cuda(), one(T), one(50, torch.int32), one(1.0), one(float("-inf")))[0].cpu().numpy().astype(np.float64)
+    want = O.processed(row.numpy(), T, 50, 1.0, -np.inf)["probs"]
+    assert int((want > 0).sum()) == 50 and got[1000] > 0
+    assert not np.any((got > 0) & ~(want > 0))
+    assert np.abs(got - want).sum() < 1e-9
 
 
 # ------------------------------------------------------------------------------------------------ logprobs of emitted tokens
