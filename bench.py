@@ -154,6 +154,74 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_gpu(args):
+    """--impl reference-gpu: the reference's own GPU path for the same batch -- its Python loop over slots around
+    processed_probs / inverse_cdf (engine/spec/accept.py:23-52: four torch expressions and two FlashInfer calls per
+    slot, stated here as the reference has them, since its checkout does not travel to a GPU box) with the FlashInfer
+    installed on the box.  The reference has no penalties: none are applied.  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    try:
+        import flashinfer
+        import flashinfer.sampling as fs
+        import torch
+        from colinfer_b200 import workloads as wl
+        from colinfer_b200.kernels import ops
+        assert torch.cuda.is_available(), "no GPU"
+    except Exception as e:                                 # noqa: BLE001
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"FlashInfer / CUDA not usable here: {e!r}"[:200]}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    B = args.batch
+    w = wl.config3(B, V=V, H=HIST)
+    logits = w["logits"].to(dev)
+    p = {k: w["params"][k].to(dev) for k in ("temperature", "top_k", "top_p", "log_min_p", "seed")}
+    pos = w["pos"].to(dev)
+
+    def processed_probs(lg, temperature, top_k, top_p, log_min_p):           # accept.py:23-33
+        z = lg / temperature.clamp_min(1e-6)
+        z = z.masked_fill(z < z.amax(-1, keepdim=True) + log_min_p, float("-inf"))
+        pr = torch.softmax(z, -1)
+        R = pr.shape[0]
+        pr = fs.top_k_renorm_probs(pr, top_k.expand(R).contiguous())
+        return fs.top_p_renorm_probs(pr, top_p.expand(R).contiguous())
+
+    def inverse_cdf(P, u):                                                   # accept.py:36-40
+        c = P.cumsum(-1)
+        return (c < (u * c[:, -1])[:, None]).sum(-1).clamp_max(P.shape[-1] - 1)
+
+    def draw():                                                              # accept.py:43-52
+        u = torch.empty(B, 1, device=dev)
+        ops().philox_uniform(p["seed"], pos.long().contiguous(), u)          # (this project's kernel: bit-identical uniforms)
+        greedy = logits.argmax(-1)
+        rows = [inverse_cdf(processed_probs(logits[b], p["temperature"][b:b + 1], p["top_k"][b:b + 1], p["top_p"][b:b + 1],
+                                            p["log_min_p"][b:b + 1]), u[b]) for b in range(B)]
+        return torch.where(p["temperature"][:, None] > 0, torch.stack(rows), greedy)
+
+    try:
+        for _ in range(max(1, args.warmup)):
+            draw()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            draw()
+        e1.record()
+        torch.cuda.synchronize()
+    except Exception as e:                                 # noqa: BLE001
+        print(json.dumps({"impl": "reference-gpu", "unavailable": f"the reference's GPU expressions failed here: {e!r}"[:200]}), flush=True)
+        return
+    ms = e0.elapsed_time(e1) / args.steps
+    value = B / (ms * 1e-3)
+    print(json.dumps({"impl": "reference-gpu", "metric": "sampled rows/s", "value": value, "unit": "rows/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(B, world),
+                      "note": f"the reference's accept.py expressions, one slot at a time, FlashInfer {flashinfer.__version__} "
+                              "(the reference pins 0.7.0.post1); no penalties (the reference has none)",
+                      "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
 def run_logprobs(args):
     """Logprobs of emitted tokens (the first row after the headline path): one GPU, rows resident, 20 alternatives.
     --impl reference times the reference's own expression (log_softmax + gather + topk, torch) on the host cores."""
@@ -362,7 +430,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1024, help="rows per GPU")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
+                    help="reference: the reference path restated for the host cores; reference-gpu: the reference's own GPU "
+                         "expressions with the box's FlashInfer (an extra arm: the existing GPU implementation to beat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the other configurations (and the fixed-batch split)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="measure blocks of --steps steps for at least this long")
@@ -380,6 +450,8 @@ def main():
         return run_rescore(args)
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "reference-gpu":
+        return run_reference_gpu(args)
 
     import torch
     import torch.distributed as dist
@@ -542,6 +614,15 @@ def main():
             line["strong"] = strong
         if world == 1 and not args.no_sweep:
             line["sweep"] = run_sweep(torch, dev, lib, peak, reps=15)
+            # the reference's own GPU path on the same batch (its expressions + the box's FlashInfer), in a child process
+            # with a time limit: FlashInfer compiles its kernels on first use
+            try:
+                r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--batch", str(B),
+                                    "--steps", "2", "--warmup", "1"], capture_output=True, text=True, timeout=420)
+                rec = json.loads(r.stdout.strip().splitlines()[-1])
+                line["sweep"]["reference_gpu_path"] = {k: rec[k] for k in ("value", "unit", "ms_per_step", "note", "unavailable") if k in rec}
+            except Exception as e:                         # noqa: BLE001
+                line["sweep"]["reference_gpu_path"] = {"unavailable": f"{e!r}"[:160]}
         if world == 1 and not args.no_cpu_baseline:
             n, times, threads = cpu_rows_per_s(w, CPU_SAMPLE_ROWS, reps=3, warm=1)
             line["cpu_baseline"] = {"value": n / statistics.median(times), "unit": "rows/s", "cores": threads, "kind": "port",

@@ -792,6 +792,37 @@ def test_spec_verify_preserves_the_target_distribution():
     assert 0.5 * (emp - p).abs().sum().item() < 0.02
 
 
+# ------------------------------------------------------------------------------------------------ the reference's GPU arithmetic
+def test_kernels_agree_with_the_reference_expressions_run_on_a_gpu():
+    """tests/golden/ref_gpu_vectors.npz (the reference's processed_probs / inverse_cdf expressions with FlashInfer, run on
+    a B200): same tokens from draw() -- penalties, mask and filters fused -- and, from processed_probs, the same kept
+    sets and probabilities to 1e-5 relative."""
+    import _ref_gpu
+    m = mods()
+    g = _ref_gpu.load()
+    one = lambda v, dt=torch.float32: torch.tensor([v], dtype=dt, device="cuda")  # noqa: E731
+    for name, w, u, lg in _ref_gpu.cases():
+        V = lg.shape[-1]
+        sp = wl.sampler_params(w["params"], V, "cuda")
+        mask = w.get("mask")
+        out = m["draw"](w["logits"].cuda(), sp, None, u=torch.from_numpy(u).cuda(), mask=None if mask is None else mask.cuda())
+        got, want = out.cpu().numpy().reshape(-1), g[name + "_tok"].reshape(-1)
+        p = w["params"]
+        for b in np.flatnonzero(got != want):
+            r = O.draw_row(lg[b, 0], float(p["temperature"][b]), int(p["top_k"][b]), float(p["top_p"][b]), float(p["log_min_p"][b]), u[b, 0])
+            assert min(r["margin"], r["margin_top_p"]) < MARGIN, (name, b, got[b], want[b])
+        print(f"[parity] {name}: {len(got)} rows, {int((got != want).sum())} differ from the FlashInfer vectors")
+        for b in range(0, lg.shape[0], 7):                          # processed_probs on the effective logits of some rows
+            T, k, tp, lmp = float(p["temperature"][b]), int(p["top_k"][b]), float(p["top_p"][b]), float(p["log_min_p"][b])
+            if not T > 0:
+                continue
+            P = m["processed_probs"](torch.from_numpy(lg[b]).cuda(), one(T), one(k, torch.int32), one(tp), one(lmp))[0].cpu().numpy()
+            if (k < V or tp < 1.0) and int((P > 0).sum()) != int(g[name + "_nkept"][b, 0]):
+                assert O.processed(lg[b, 0], T, k, tp, lmp)["margin_top_p"] < MARGIN, (name, b)   # a cut within the margin of a step
+            ti, tv = g[name + "_top_idx"][b, 0], g[name + "_top_prob"][b, 0]
+            assert np.allclose(P[ti], tv, rtol=1e-5, atol=1e-30), (name, b)
+
+
 # ------------------------------------------------------------------------------------------------ the mass horizon
 # Masses are integers in units of 2^-30 of the largest token's: a logit more than ~21.5 temperatures below the maximum
 # has mass 0 and can never be drawn, one a little above that is rounded coarsely.  Against the reference's fp32 softmax

@@ -281,3 +281,36 @@ def test_rescore_oracles_equal_the_dense_products():
     want = codes.view(torch.float8_e4m3fn).double().numpy()
     got = O.e4m3_to_f64(codes.numpy())
     assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(got[~np.isnan(got)], want[~np.isnan(want)])
+
+
+def test_oracle_agrees_with_the_reference_expressions_run_on_a_gpu():
+    """tests/golden/ref_gpu_vectors.npz: the reference's processed_probs / inverse_cdf expressions with the FlashInfer
+    ops it calls, run on a B200 (make_gpu_golden.py).  The oracle must give the same tokens, the same kept sets (ties at
+    a pivot all kept) and the same probabilities to 1e-5 relative."""
+    import _ref_gpu
+    g = _ref_gpu.load()
+    n_rows = 0
+    for name, w, u, lg in _ref_gpu.cases():
+        p = w["params"]
+        V = lg.shape[-1]
+        for b in range(lg.shape[0]):
+            T, k, tp, lmp = float(p["temperature"][b]), int(p["top_k"][b]), float(p["top_p"][b]), float(p["log_min_p"][b])
+            r = O.draw_row(lg[b, 0], T, k, tp, lmp, u[b, 0])
+            assert int(g[name + "_greedy"][b, 0]) == r["greedy"]
+            tok = int(g[name + "_tok"][b, 0])
+            assert tok == r["token"] or min(r["margin"], r["margin_top_p"]) < 1e-6, (name, b, tok, r)
+            if not T > 0:
+                continue
+            pr = O.processed(lg[b, 0], T, k, tp, lmp)
+            kept = pr["w"] > 0
+            if k < V or tp < 1.0:                                  # (without a filter fp32 underflow alone decides the support)
+                assert float(g[name + "_dropped_max_logit"][b, 0]) < float(g[name + "_kept_min_logit"][b, 0])
+                if int(kept.sum()) != int(g[name + "_nkept"][b, 0]):
+                    # the top-p target fell within 1e-6 of a cumulative-mass step: fp32 and float64 sums may cut one token apart
+                    assert pr["margin_top_p"] < 1e-6 and abs(int(kept.sum()) - int(g[name + "_nkept"][b, 0])) <= 2, (name, b)
+                    continue
+                assert float(lg[b, 0][kept].min()) == float(g[name + "_kept_min_logit"][b, 0])
+            ti, tv = g[name + "_top_idx"][b, 0], g[name + "_top_prob"][b, 0].astype(np.float64)
+            assert np.allclose(pr["probs"][ti], tv, rtol=1e-5, atol=1e-30), (name, b)
+            n_rows += 1
+    assert n_rows >= 70
