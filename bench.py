@@ -439,6 +439,9 @@ def main():
     ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs", "rescore"],
                     help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives; "
                          "rescore: draft-head candidate rescoring (256 candidates of a 69,632 x 2560 BF16 lm_head per slot)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the sampled ids are gathered -- peer: one small kernel that stores them into every rank's "
+                         "buffer over NVLink (falls back to nccl when peer memory cannot be mapped); nccl: all_gather")
     ap.add_argument("--cluster", type=int, default=0,
                     help="0: automatic (few rows: cluster-resident kernel, else the streaming kernel); -1: streaming kernel; "
                          "1/2/4/8: the cluster-resident kernel with that cluster size")
@@ -456,7 +459,7 @@ def main():
     import torch
     import torch.distributed as dist
     from colinfer_b200 import _lib, workloads as wl
-    from colinfer_b200.sharding import gather_ids, shard_rows
+    from colinfer_b200.sharding import PeerGather, gather_ids, shard_rows
     from colinfer_b200.spec.accept import draw
 
     lib = _lib.lib()                                       # fail loudly if the CUDA library is missing
@@ -483,10 +486,32 @@ def main():
     pos = w["pos"].to(dev)
     bytes_row = wl.bytes_per_row(V, 4, False, HIST)
 
+    # the id gather: one small kernel over NVLink (peer stores + flags), or the collective call
+    gather_kind, peer_gathers = "none", {}
+    if world > 1:
+        gather_kind = args.gather
+        if gather_kind == "peer":
+            try:
+                peer_gathers[n_rows] = PeerGather(n_rows)
+                ok = torch.ones(1, device=dev)
+            except Exception as e:                         # noqa: BLE001
+                print(f"[bench] rank {rank}: peer gather unavailable ({e!r}); using the collective", file=sys.stderr)
+                ok = torch.zeros(1, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if not float(ok.item()) > 0:
+                gather_kind, peer_gathers = "nccl", {}
+
+    def gather(ids, total):
+        if gather_kind == "peer":
+            if total not in peer_gathers:
+                peer_gathers[total] = PeerGather(total)
+            return peer_gathers[total].gather(ids.reshape(-1)).reshape((total,) + tuple(ids.shape[1:]))
+        return gather_ids(ids, total)
+
     def step():
         ids = draw(logits, sp, pos)
         pos.add_(1)
-        return gather_ids(ids, n_rows) if world > 1 else ids
+        return gather(ids, n_rows) if world > 1 else ids
 
     def barrier():
         if world > 1:
@@ -539,7 +564,7 @@ def main():
         d_hist.copy_(h_hist, non_blocking=True)
         d_pos.copy_(h_pos, non_blocking=True)
         out = draw(d_logits, sp_e, d_pos)
-        out = gather_ids(out, n_rows) if world > 1 else out
+        out = gather(out, n_rows) if world > 1 else out
         h_ids.copy_(out[:B] if world > 1 else out, non_blocking=True)
 
     for _ in range(2):
@@ -575,7 +600,7 @@ def main():
             sps = wl.sampler_params(mine["params"], vv, dev)
             lg, ps = mine["logits"].to(dev), mine["pos"].to(dev)
             mk = mine["mask"].to(dev) if kw_mask else None
-            fn = lambda: gather_ids(draw(lg, sps, ps, mask=mk), total_rows)
+            fn = lambda: gather(draw(lg, sps, ps, mask=mk), total_rows)
             for _ in range(3):
                 fn()
             bl = timed_blocks(fn, args.steps, 0.2)
@@ -607,7 +632,9 @@ def main():
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(h_ids.numel() * 8),
                     "h2d_gbs_per_rank": [round(x, 2) for x in h2d_rates],
                     "gpu_numa_nodes": [numa_node_of(torch, i) for i in range(world)]},
-            "gpu_launches": args.steps * len(blocks),
+            "gpu_launches": args.steps * len(blocks) * (2 if gather_kind == "peer" else 1),
+            "gather": {"none": None, "peer": "k_gather_ids: peer stores + flags over NVLink, one launch", "nccl": "all_gather_into_tensor"}[gather_kind],
+            "gather_timed_out": any(g.timed_out() for g in peer_gathers.values()) if peer_gathers else False,
             "clocks": clk.summary(),
         }
         if strong is not None:

@@ -58,6 +58,8 @@ SIGNATURES = {
     "colinfer_set_cluster_override": (C.c_int, [C.c_int]),
     "colinfer_set_profile_buffer": (C.c_int, [C.c_void_p, C.c_int]),
     "colinfer_max_active_clusters": (C.c_int, [C.c_int, C.c_int]),
+    "colinfer_gather_ids": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
+                                      C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "colinfer_version": (C.c_int, []),
 }
 

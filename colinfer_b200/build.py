@@ -22,7 +22,7 @@ LIB = os.path.join(HERE, "libcolinfer_b200.so")
 STREAM_PARTS = 9
 # (source, object name, extra flags)
 UNITS = [("sample.cu", "sample.o", []), ("ops.cu", "ops.o", []), ("logprobs.cu", "logprobs.o", []),
-         ("rescore.cu", "rescore.o", []), ("stream_host.cu", "stream_host.o", [])] + \
+         ("rescore.cu", "rescore.o", []), ("gather.cu", "gather.o", []), ("stream_host.cu", "stream_host.o", [])] + \
         [("stream_part.cu", f"stream_part_{i}.o", [f"-DCOLINFER_STREAM_PART={i}"]) for i in range(STREAM_PARTS)]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 

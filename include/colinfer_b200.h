@@ -168,6 +168,22 @@ int colinfer_rescore_bf16(const void* x, const void* w, const int64_t* cand, flo
 int colinfer_rescore_nvfp4(const void* x, const void* w, const void* sf, float gs, const int64_t* cand, float* out,
                            int B, int K, int NC, int64_t rows_w, void* stream);
 
+/* The id gather of a row-sharded step over NVLink, in one launch of one CTA (no counterpart in the reference, which runs
+ * on one GPU; it takes the place of an all-gather call behind the sampler).  Every rank calls it with its own ids
+ * `local` [n_local] (the rows [row_offset, row_offset + n_local) of the step): they are stored into every rank's gather
+ * buffer -- peer_bufs[p] is rank p's buffer of 2 * half_elems int64, mapped into this process (device array of n_ranks
+ * pointers); steps alternate between its halves -- then this rank's flag is raised at every rank (peer_flags[p] is rank
+ * p's array of n_ranks int64 flags) and the kernel waits until all n_ranks flags of this rank have reached the step.
+ * step_counter: one int64 of this rank's device memory, zero before the first call; the kernel advances it, so a
+ * captured launch can be replayed.  After the call, on the same stream, the ids of all half_elems rows of the step are
+ * in out_all (this rank's memory).  The wait gives up after limit_cycles clock cycles (<= 0: about a second),
+ * sets COLINFER_GATHER_TIMEOUT in *status (may be NULL) and returns.  Every rank must own its GPU: ranks that share
+ * one would wait on kernels that cannot run. */
+enum { COLINFER_GATHER_TIMEOUT = 1 };
+int colinfer_gather_ids(const int64_t* local, int n_local, int64_t row_offset, int64_t* const* peer_bufs,
+                        long long* const* peer_flags, int n_ranks, int rank, long long* step_counter, int64_t half_elems,
+                        int64_t* out_all, int64_t limit_cycles, int32_t* status, void* stream);
+
 /* Library version (major * 100 + minor). */
 int colinfer_version(void);
 
