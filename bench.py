@@ -463,7 +463,7 @@ def main():
     from colinfer_b200.spec.accept import draw
 
     lib = _lib.lib()                                       # fail loudly if the CUDA library is missing
-    lib.colinfer_set_cluster_override(args.cluster)
+    _lib.default_kernel_flags = _lib.kernel_flags(args.cluster)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

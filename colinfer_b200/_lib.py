@@ -13,6 +13,23 @@ LIB_PATH = os.path.join(_HERE, "libcolinfer_b200.so")
 F32, BF16 = 0, 1
 ROW_DEGENERATE, ROW_TIMEOUT, ROW_HIST_SLOW, ROW_SELECT_SLOW = 1, 2, 4, 8
 FORCE_DISTRIBUTION, TEST_MISS_BAND = 1, 0x4000
+KERNEL_AUTO, KERNEL_STREAM = 0, 0x100
+KERNEL_CLUSTER = {1: 0x200, 2: 0x300, 4: 0x400, 8: 0x500}
+KERNEL_MASK = 0x700
+
+# Kernel-choice bits that draw() adds to calls which do not choose themselves: a knob of this Python module for tests and
+# benchmarks (the C library keeps no settings between calls).
+default_kernel_flags = KERNEL_AUTO
+
+
+def kernel_flags(cluster: int) -> int:
+    """0: automatic, -1: the streaming kernel, 1 / 2 / 4 / 8: the cluster-resident kernel with that cluster size."""
+    if cluster == 0:
+        return KERNEL_AUTO
+    if cluster == -1:
+        return KERNEL_STREAM
+    return KERNEL_CLUSTER[cluster]
+
 
 
 class SamplerParamsC(C.Structure):
@@ -54,9 +71,7 @@ SIGNATURES = {
                                          C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "colinfer_spec_verify_stats_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_spec_verify_ids_bytes": (C.c_int64, [C.c_int, C.c_int]),
-    "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.POINTER(Geometry)]),
-    "colinfer_set_cluster_override": (C.c_int, [C.c_int]),
-    "colinfer_set_profile_buffer": (C.c_int, [C.c_void_p, C.c_int]),
+    "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(Geometry)]),
     "colinfer_max_active_clusters": (C.c_int, [C.c_int, C.c_int]),
     "colinfer_gather_ids": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
                                       C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),

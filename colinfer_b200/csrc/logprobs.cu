@@ -11,6 +11,8 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "../../include/colinfer_b200.h"
 
@@ -342,15 +344,19 @@ extern "C" int colinfer_logprobs(const void* logits, int dtype, const int64_t* t
         (dtype != COLINFER_F32 && dtype != COLINFER_BF16) || (n_top > 0 && (top_ids == nullptr || top_lp == nullptr)))
         return (int)cudaErrorInvalidValue;
     static int sm_count[64] = {};
+    static std::mutex guard;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-    if (sm_count[dev] == 0) {
-        int n = 0;
-        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return (int)e;
-        sm_count[dev] = n > 0 ? n : 1;
+    {
+        std::lock_guard<std::mutex> lock(guard);
+        if (sm_count[dev] == 0) {
+            int n = 0;
+            e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess) return (int)e;
+            sm_count[dev] = n > 0 ? n : 1;
+        }
     }
     lpk::Args a;
     a.logits = logits; a.dtype = dtype;

@@ -1,5 +1,7 @@
 // ops.cu -- the small kernels of the logits -> token path (sm_100a): Philox uniforms, the stand-alone grammar mask, the
 // full-probability writer behind processed_probs, inverse_cdf, and the speculative accept / verify steps.
+#include <mutex>
+
 #include "common.cuh"
 #include "../../include/colinfer_b200.h"
 
@@ -128,6 +130,8 @@ static __device__ __align__(256) colinfer_row_stats g_noalloc_stats[COLINFER_NOA
 // address a kernel may dereference: the address is asked for once per device, with that device current.
 static int noalloc_stats_ptr(colinfer_row_stats** out) {
     static colinfer_row_stats* cached[64] = {};
+    static std::mutex guard;                               // (first calls of two host threads may coincide)
+    std::lock_guard<std::mutex> lock(guard);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;

@@ -24,6 +24,8 @@
 //
 // What the reference does in ~25 torch / FlashInfer launches per slot (engine/spec/accept.py:23-52 after
 // engine/runtime/sampler.py:50-56) is one launch here.
+#include <mutex>
+
 #include "common.cuh"
 #include "../../include/colinfer_b200.h"
 
@@ -1373,21 +1375,23 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
 int colinfer_launch_stream(const void*, int, const int32_t*, int, int, const colinfer_sampler_params*, const void*, int, const float*,
                            int64_t*, colinfer_row_stats*, int32_t*, int, int, int, int, cudaStream_t);
 
-static int g_cluster_override = 0;
-static long long* g_prof = nullptr;
+#ifdef COLINFER_PROFILE
+static long long* g_prof = nullptr;                        // profiling builds only: cycles per phase of later launches
 static int g_prof_slots = 0;
+#endif
 static const int kFixedSmem = 24 * 1024 + (CI_WARPS * CI_WLIST + 8 * CI_PCAP) * (int)sizeof(Cand) + CI_MAX_CHUNKS * 8 +
                               (int)sizeof(Xch) + (int)sizeof(Scratch) + 64;
 
-static int pick_geometry(int V, int dtype, const void* logits, colinfer_geometry* g) {
+// forced: 0 = the smallest cluster that holds the row; 1, 2, 4, 8 = that cluster size
+static int pick_geometry(int V, int dtype, const void* logits, int forced, colinfer_geometry* g) {
     if (V <= 0) return 1;
     const int cap2 = (113 * 1024 - kFixedSmem) / 4;           // slice elements that allow two CTAs per SM
     const int cap1 = (226 * 1024 - kFixedSmem) / 4;           // one CTA per SM
     const int max_slice = CI_CHUNK * CI_MAX_CHUNKS;
     int cs = 0, slice = 0;
     auto slice_for = [&](int c) { return (((V + c - 1) / c) + 127) & ~127; };
-    if (g_cluster_override > 0) {
-        cs = g_cluster_override; slice = slice_for(cs);
+    if (forced > 0) {
+        cs = forced; slice = slice_for(cs);
         if (slice > cap1 || slice > max_slice) return 1;
     } else {
         for (int c = 1; c <= 8 && !cs; c *= 2) if (slice_for(c) <= cap2 && slice_for(c) <= max_slice) { cs = c; slice = slice_for(c); }
@@ -1401,17 +1405,22 @@ static int pick_geometry(int V, int dtype, const void* logits, colinfer_geometry
     return 0;
 }
 
-extern "C" int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geometry* out) {
-    return pick_geometry(V, dtype, logits, out) ? (int)cudaErrorInvalidValue : 0;
+extern "C" int colinfer_sample_geometry(int V, int dtype, const void* logits, int cluster, colinfer_geometry* out) {
+    if (cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
+    return pick_geometry(V, dtype, logits, cluster, out) ? (int)cudaErrorInvalidValue : 0;
 }
 
+#ifdef COLINFER_PROFILE
 void colinfer_profile_buffer(long long** buf, int* slots) { *buf = g_prof; *slots = g_prof_slots; }
-
+// (profiling builds) the first `ctas` CTAs of later launches add their cycles per phase into dev[ctas * 16]
 extern "C" int colinfer_set_profile_buffer(void* dev, int ctas) {
     g_prof = reinterpret_cast<long long*>(dev);
     g_prof_slots = dev ? ctas : 0;
     return 0;
 }
+#else
+void colinfer_profile_buffer(long long** buf, int* slots) { *buf = nullptr; *slots = 0; }
+#endif
 
 static void fill_launch(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, const colinfer_geometry& g, long long clusters, cudaStream_t st) {
     cfg = cudaLaunchConfig_t{};
@@ -1433,6 +1442,8 @@ static int active_clusters(const colinfer_geometry& g) {
     struct Entry { int dev, smem, cs, n; };
     static Entry cache[16];
     static int used = 0;
+    static std::mutex guard;
+    std::lock_guard<std::mutex> lock(guard);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return -1;
     for (int i = 0; i < used; ++i)
@@ -1448,14 +1459,8 @@ static int active_clusters(const colinfer_geometry& g) {
 
 extern "C" int colinfer_max_active_clusters(int V, int dtype) {
     colinfer_geometry g;
-    if (pick_geometry(V, dtype, nullptr, &g)) return -1;
+    if (pick_geometry(V, dtype, nullptr, 0, &g)) return -1;
     return active_clusters(g);
-}
-
-extern "C" int colinfer_set_cluster_override(int cluster) {
-    if (cluster != -1 && cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return (int)cudaErrorInvalidValue;
-    g_cluster_override = cluster;
-    return 0;
 }
 
 extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mask, int mask_rows, int W,
@@ -1470,16 +1475,19 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     if (out_ids && u == nullptr && (pos == nullptr || params->seed == nullptr)) return (int)cudaErrorInvalidValue;
     if (mask && (W < (V + 31) / 32 || mask_rows < R)) return (int)cudaErrorInvalidValue;
     if ((long long)B * R > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-    if (g_cluster_override <= 0) {
-        // Automatic choice (override 0).  Few rows -- at most as many as the device holds clusters at once -- are a
-        // latency problem: one CTA per row would leave most SMs idle, so each row gets a whole 8-CTA cluster of the
-        // cluster-resident kernel (config 3: 8 rows in 43 us against 89 us).  More rows are a throughput problem: the
-        // streaming kernel (one CTA per row, passes over L2).  Override -1 forces the streaming kernel; the
-        // cluster-resident kernel also runs when a row's penalty bitmap does not fit the streaming kernel.
+    // Which kernel: the caller's choice (bits COLINFER_KERNEL_* of flags), else automatic.  Few rows -- at most as many
+    // as the device holds clusters at once -- are a latency problem: one CTA per row would leave most SMs idle, so each
+    // row gets a whole 8-CTA cluster of the cluster-resident kernel.  More rows are a throughput problem: the streaming
+    // kernel (one CTA per row, later passes over L2).  The cluster-resident kernel also runs when a row's tables do not
+    // fit the streaming kernel.
+    const int choice = (flags >> 8) & 7;                   // 0 auto, 1 streaming, 2 .. 5: clusters of 1, 2, 4, 8
+    if (choice > 5) return (int)cudaErrorInvalidValue;
+    const int forced = choice >= 2 ? (1 << (choice - 2)) : 0;
+    if (choice <= 1) {
         bool use_stream = true;
-        if (g_cluster_override == 0) {
+        if (choice == 0) {
             colinfer_geometry g0;
-            if (!pick_geometry(V, dtype, logits, &g0)) {
+            if (!pick_geometry(V, dtype, logits, 0, &g0)) {
                 const int res0 = active_clusters(g0);
                 if (res0 > 0 && (long long)B * R <= res0) use_stream = false;
             }
@@ -1491,7 +1499,7 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
         }
     }
     colinfer_geometry g;
-    if (pick_geometry(V, dtype, logits, &g)) return (int)cudaErrorInvalidValue;
+    if (pick_geometry(V, dtype, logits, forced, &g)) return (int)cudaErrorInvalidValue;
     const int resident = active_clusters(g);
     if (resident <= 0) return (int)cudaErrorInvalidConfiguration;
     const long long clusters = (long long)B * R < resident ? (long long)B * R : resident;
@@ -1503,7 +1511,7 @@ extern "C" int colinfer_sample(const void* logits, int dtype, const int32_t* mas
     a.pos = pos; a.pos_i64 = pos_is_i64; a.u = u;
     a.out = out_ids; a.stats = stats; a.status = status;
     a.B = B; a.R = R; a.V = V; a.slice_elems = g.slice_elems; a.flags = flags;
-    a.prof = g_prof; a.prof_slots = g_prof_slots;
+    colinfer_profile_buffer(&a.prof, &a.prof_slots);
 
     cudaError_t e = cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return (int)e;

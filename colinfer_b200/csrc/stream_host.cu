@@ -1,4 +1,6 @@
 // stream_host.cu -- host side of the streaming kernel: geometry of a launch and the choice of its instantiation.
+#include <mutex>
+
 #include "stream_kernel.cuh"
 
 void colinfer_profile_buffer(long long** buf, int* slots);   // sample.cu: the buffer colinfer_set_profile_buffer registered
@@ -18,11 +20,12 @@ int stream_smem_bytes(int V) {
            (int)sizeof(strm::Sc) + 2 * nw * 4 + strm::PEN_TABLE * 16 + 256;
 }
 
-// Multiprocessors of a device, looked up once (the engine calls from one thread; a second thread that races here
-// repeats an idempotent query).
+// Multiprocessors of a device, looked up once.
 int sm_count_of(int dev, int* out) {
     static int sm_count[64] = {};
+    static std::mutex guard;
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(guard);
     if (sm_count[dev] == 0) {
         int n = 0;
         const cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);

@@ -35,7 +35,7 @@ namespace strm {
 #endif
 
 constexpr int NT = 1024;             // threads per CTA
-constexpr int CTAS_PER_SM = 1;       // (two CTAs of 512 threads per SM were measured: slower -- their rows split unevenly)
+constexpr int CTAS_PER_SM = 1;       // (two CTAs of 512 threads per SM are slower: rows split unevenly over them and each keeps half the loads in flight)
 constexpr int NW = NT / 32;
 constexpr int NWA = 32;              // per-warp exchange arrays are sized (and reduced) for a full warp of warps
 constexpr int NB1 = 8192;            // fine buckets over the distance from the row maximum (or from the sample's)

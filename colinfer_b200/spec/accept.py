@@ -109,7 +109,7 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
     mask [B, R, W] int32: grammar bitmask applied inside the same pass (what apply_mask would do first).
     u [B, R] fp32: explicit uniforms in (0, 1] instead of Philox(seed, pos).
     status / stats: also return the per-row status words int32 [B, R] / the raw row statistics uint8 [B, R, 32].
-    flags: COLINFER_* flag bits of colinfer_sample (test hooks)."""
+    flags: COLINFER_* flag bits of colinfer_sample (kernel choice, test flags)."""
     if logits.dim() != 3:
         raise RuntimeError("logits [B, R, V]")
     check_tensor(logits, None, "logits")
@@ -142,9 +142,12 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
         return out
     st = torch.empty(B, R, dtype=torch.int32, device=logits.device) if status else None
     rs = torch.empty(B, R, _lib.ROW_STATS_BYTES, dtype=torch.uint8, device=logits.device) if stats else None
+    flags = int(flags)
+    if not flags & _lib.KERNEL_MASK:
+        flags |= _lib.default_kernel_flags
     _lib.check(_lib.lib().colinfer_sample(logits.data_ptr(), dt, mask_ptr, mask_rows, W, C.byref(ps), pos_ptr, pos_i64,
                                           u_ptr, out.data_ptr(), rs.data_ptr() if stats else None,
-                                          st.data_ptr() if status else None, B, R, V, int(flags), _stream()), "draw")
+                                          st.data_ptr() if status else None, B, R, V, flags, _stream()), "draw")
     if status or stats:
         return (out,) + ((st,) if status else ()) + ((rs,) if stats else ())
     return out

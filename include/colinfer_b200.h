@@ -55,10 +55,17 @@ enum {
 
 enum { COLINFER_F32 = 0, COLINFER_BF16 = 1 };
 
-/* Flags of colinfer_sample. */
+/* Flags of colinfer_sample (per call: the library keeps no settings between calls). */
 enum {
     COLINFER_FORCE_DISTRIBUTION = 1, /* build the distribution even for temperature <= 0 (processed_probs does) */
-    COLINFER_TEST_MISS_BAND = 0x4000 /* test hook: misplace the estimated top-p band so that the exact retry paths run;
+    /* which kernel runs (tests and benchmarks; results are the same): default automatic -- few rows take the
+       cluster-resident kernel, one 8-CTA cluster per row, more rows the streaming kernel */
+    COLINFER_KERNEL_STREAM   = 0x100, /* the streaming kernel */
+    COLINFER_KERNEL_CLUSTER1 = 0x200, /* the cluster-resident kernel with clusters of 1, */
+    COLINFER_KERNEL_CLUSTER2 = 0x300, /* 2, */
+    COLINFER_KERNEL_CLUSTER4 = 0x400, /* 4, */
+    COLINFER_KERNEL_CLUSTER8 = 0x500, /* 8 CTAs */
+    COLINFER_TEST_MISS_BAND = 0x4000 /* test flag: misplace the estimated top-p band so that the exact retry paths run;
                                         results are unchanged, rows report COLINFER_ROW_SELECT_SLOW */
 };
 
@@ -128,25 +135,16 @@ int colinfer_spec_verify(const void* target_logits, const void* draft_logits, in
 int64_t colinfer_spec_verify_stats_bytes(int B, int k);
 int64_t colinfer_spec_verify_ids_bytes(int B, int k);
 
-/* Geometry the sampler would use for a vocabulary (for tests and benchmarks): CTAs per row (thread-block cluster
- * size), elements per CTA slice, dynamic shared memory per CTA, and whether the bulk-copy (TMA) load path applies. */
+/* Geometry the cluster-resident kernel would use for a vocabulary (for tests and benchmarks): CTAs per row (thread-block
+ * cluster size; cluster = 0 picks the smallest that holds the row, else 1, 2, 4 or 8), elements per CTA slice, dynamic
+ * shared memory per CTA, and whether the bulk-copy (TMA) load path applies. */
 typedef struct colinfer_geometry {
     int32_t cluster;
     int32_t slice_elems;
     int32_t smem_bytes;
     int32_t bulk_copy;
 } colinfer_geometry;
-int colinfer_sample_geometry(int V, int dtype, const void* logits, colinfer_geometry* out);
-
-/* Test hook for later colinfer_sample calls of this process.  0 = automatic (few rows: the cluster-resident kernel, one
- * 8-CTA cluster per row; otherwise the streaming kernel); -1 = always the streaming kernel; 1, 2, 4 or 8 = the
- * cluster-resident kernel with that cluster size. */
-int colinfer_set_cluster_override(int cluster);
-
-/* Profiling hook: when dev is not NULL, the first `ctas` CTAs of later colinfer_sample launches add, into 16 int64
- * each (dev[ctas * 16], zeroed by the caller), the clock cycles spent in each phase summed over the CTA's rows
- * (slots 0-11), the CTA's total cycles (12), %globaltimer at exit (13) and entry (15), and %smid (14).  NULL = off. */
-int colinfer_set_profile_buffer(void* dev, int ctas);
+int colinfer_sample_geometry(int V, int dtype, const void* logits, int cluster, colinfer_geometry* out);
 
 /* How many clusters of the sampler's geometry for this vocabulary the current device holds at once (occupancy query). */
 int colinfer_max_active_clusters(int V, int dtype);

@@ -35,14 +35,14 @@ def test_struct_layouts_match_header(built_lib):
 def test_geometry_of_the_benchmark_vocabularies(built_lib):
     g = _lib.Geometry()
     L = _lib.lib()
-    assert L.colinfer_sample_geometry(151936, _lib.F32, None, C.byref(g)) == 0
+    assert L.colinfer_sample_geometry(151936, _lib.F32, None, 0, C.byref(g)) == 0
     assert g.cluster * g.slice_elems >= 151936 and g.slice_elems % 128 == 0 and g.bulk_copy == 1
     assert g.smem_bytes <= 113 * 1024                          # two CTAs per SM
-    assert L.colinfer_sample_geometry(262144, _lib.BF16, None, C.byref(g)) == 0
+    assert L.colinfer_sample_geometry(262144, _lib.BF16, None, 0, C.byref(g)) == 0
     assert g.cluster * g.slice_elems >= 262144 and g.smem_bytes <= 227 * 1024
-    assert L.colinfer_sample_geometry(50, _lib.F32, None, C.byref(g)) == 0 and g.cluster == 1 and g.bulk_copy == 0
-    assert L.colinfer_sample_geometry(10_000_000, _lib.F32, None, C.byref(g)) == 1   # beyond the resident-row limit
-    assert L.colinfer_set_cluster_override(3) == 1 and L.colinfer_set_cluster_override(-1) == 0 and L.colinfer_set_cluster_override(0) == 0
+    assert L.colinfer_sample_geometry(50, _lib.F32, None, 0, C.byref(g)) == 0 and g.cluster == 1 and g.bulk_copy == 0
+    assert L.colinfer_sample_geometry(10_000_000, _lib.F32, None, 0, C.byref(g)) == 1   # beyond the resident-row limit
+    assert L.colinfer_sample_geometry(151936, _lib.F32, None, 3, C.byref(g)) == 1 and L.colinfer_sample_geometry(151936, _lib.F32, None, 8, C.byref(g)) == 0
 
 
 def test_sampler_params_host_logic(golden):

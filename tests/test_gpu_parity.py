@@ -26,9 +26,10 @@ def _kernel_choice(request):
     """Every test runs twice: with the automatic kernel choice (few rows: cluster-resident kernel, else the streaming
     kernel) and with the streaming kernel forced, so that small cases cover both kernels."""
     assert torch.cuda.is_available(), "the gpu tests need a CUDA device"
-    _lib.lib().colinfer_set_cluster_override(0 if request.param == "auto" else -1)
+    _lib.lib()
+    _lib.default_kernel_flags = _lib.kernel_flags(0 if request.param == "auto" else -1)
     yield request.param
-    _lib.lib().colinfer_set_cluster_override(0)
+    _lib.default_kernel_flags = _lib.KERNEL_AUTO
 
 
 def mods():
@@ -61,7 +62,7 @@ def run_workload(w, V, cluster=None, use_philox=False):
     """draw() on a workload dict vs the oracle.  Returns (#boundary mismatches, tokens)."""
     m = mods()
     if cluster is not None:
-        _lib.lib().colinfer_set_cluster_override(cluster)
+        _lib.default_kernel_flags = _lib.kernel_flags(cluster)
     dev = "cuda"
     logits = w["logits"].to(dev)
     sp = wl.sampler_params(w["params"], V, dev)
@@ -150,7 +151,7 @@ GRID = [(0.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.7, 20, 1.0, 0.0), (1.0, 0, 0.
 @pytest.mark.parametrize("V", [1, 31, 33, 1000, 4099])
 def test_draw_vs_oracle_grid(V, cluster):
     m = mods()
-    _lib.lib().colinfer_set_cluster_override(cluster)
+    _lib.default_kernel_flags = _lib.kernel_flags(cluster)
     g = torch.Generator().manual_seed(100 + V)
     B, R = len(GRID), 2
     logits = torch.randn(B, R, V, generator=g) * 2
@@ -243,7 +244,7 @@ def test_many_distinct_history_ids_use_the_slow_count_path(cluster, rp):
     builds no table for a greedy row whose penalties can only lower a logit (rp >= 1) as long as its lists decide it."""
     m = mods()
     V, H = 8192, 6000
-    _lib.lib().colinfer_set_cluster_override(cluster)
+    _lib.default_kernel_flags = _lib.kernel_flags(cluster)
     g = torch.Generator().manual_seed(9)
     logits = torch.randn(1, 1, V, generator=g) * 2
     hist = torch.randint(0, V, (1, H), generator=g, dtype=torch.int32)
