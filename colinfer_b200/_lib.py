@@ -79,6 +79,25 @@ SIGNATURES = {
 }
 
 _lib = None
+_ext = False            # False: not looked for yet; None: not built
+
+
+def ext():
+    """The thin PyTorch C++ extension over the C ABI (colinfer_b200/_colinfer_torch.so, built by build.build_torch_ext), or
+    None when it has not been built: the Python mirrors then call the library through ctypes (same results)."""
+    global _ext
+    if _ext is False:
+        _ext = None
+        if os.path.exists(os.path.join(_HERE, "_colinfer_torch.so")) and os.environ.get("COLINFER_NO_TORCH_EXT") != "1":
+            try:
+                import importlib
+
+                import torch  # noqa: F401  (its libraries must be loaded first)
+                lib()
+                _ext = importlib.import_module("colinfer_b200._colinfer_torch")
+            except Exception:                              # noqa: BLE001  (an extension built for another torch: fall back to ctypes)
+                _ext = None
+    return _ext
 
 
 def lib():

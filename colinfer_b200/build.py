@@ -28,7 +28,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 
 def _deps():
-    return [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "colinfer_b200.h")]
+    return [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh"))] + \
+           [os.path.join(ROOT, "include", "colinfer_b200.h")]
 
 
 def needs_build() -> bool:
@@ -74,6 +75,32 @@ def build(force: bool = False, verbose: bool = False, only: set[str] | None = No
     return LIB
 
 
+EXT = os.path.join(HERE, "_colinfer_torch.so")
+
+
+def build_torch_ext(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/torch_ext.cpp -- the thin PyTorch C++ extension over the C ABI -- into colinfer_b200/_colinfer_torch.so.
+    It links against libcolinfer_b200.so next to it (rpath $ORIGIN) and needs torch's headers; no GPU is needed."""
+    src = os.path.join(CSRC, "torch_ext.cpp")
+    deps = [src, os.path.join(ROOT, "include", "colinfer_b200.h")]
+    if not force and os.path.exists(EXT) and os.path.getmtime(EXT) >= max(os.path.getmtime(p) for p in deps):
+        return EXT
+    if not os.path.exists(LIB):
+        build()
+    import shutil
+
+    from torch.utils import cpp_extension
+    bdir = os.path.join(HERE, "build", "torch_ext")
+    os.makedirs(bdir, exist_ok=True)
+    cpp_extension.load(name="_colinfer_torch", sources=[src], extra_cflags=["-O2"], with_cuda=True,
+                       extra_ldflags=[f"-L{HERE}", "-lcolinfer_b200", "-Wl,-rpath,'$$ORIGIN'", "-Wl,-rpath,'$$ORIGIN/../..'"], build_directory=bdir,
+                       is_python_module=False, verbose=verbose)
+    shutil.copyfile(os.path.join(bdir, "_colinfer_torch.so"), EXT)
+    return EXT
+
+
 if __name__ == "__main__":
     names = {a.split("=", 1)[1] for a in sys.argv if a.startswith("--only=")}
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, only=names or None))
+    if "--ext" in sys.argv:
+        print(build_torch_ext(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -29,6 +29,9 @@ class _Ops:
     def philox_uniform(seed: torch.Tensor, offset: torch.Tensor, out: torch.Tensor) -> None:
         """out fp32 [B, n] = per-slot seeded uniforms in (0, 1] at counters offset[b] + i (seed, offset: int64 [B]).
         Writes in place; the caller allocates out."""
+        ext = _lib.ext()
+        if ext is not None:
+            return ext.philox_uniform(seed, offset, out)
         check_tensor(seed, torch.int64, "seed")
         check_tensor(offset, torch.int64, "offset")
         check_tensor(out, torch.float32, "out")

@@ -110,6 +110,17 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
     u [B, R] fp32: explicit uniforms in (0, 1] instead of Philox(seed, pos).
     status / stats: also return the per-row status words int32 [B, R] / the raw row statistics uint8 [B, R, 32].
     flags: COLINFER_* flag bits of colinfer_sample (kernel choice, test flags)."""
+    ext = _lib.ext()
+    if ext is not None:
+        # the thin C++ extension: the same checks (TORCH_CHECK), outputs from torch's allocator, torch's current stream
+        flags = int(flags)
+        if not flags & _lib.KERNEL_MASK:
+            flags |= _lib.default_kernel_flags
+        g = lambda name: getattr(p, name, None)  # noqa: E731
+        res = ext.draw(logits, p.temperature, p.top_k, p.top_p, p.log_min_p, g("seed"), g("repetition_penalty"),
+                       g("presence_penalty"), g("frequency_penalty"), g("history"), g("hist_len"), pos if u is None else None,
+                       mask, u, bool(status), bool(stats), flags)
+        return res[0] if len(res) == 1 else tuple(res)
     if logits.dim() != 3:
         raise RuntimeError("logits [B, R, V]")
     check_tensor(logits, None, "logits")

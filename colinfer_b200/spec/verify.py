@@ -18,6 +18,10 @@ def spec_accept(pred: torch.Tensor, tok: torch.Tensor, stop_ids: torch.Tensor | 
     verified inputs (tok[:, 1:] are the drafts); stop_ids [B, S] int64 (-1 unused); active [B] int32.
     Returns (out_tok [B, k+1] int64, n [B] int32): n counts the emitted tokens (accepted drafts + 1; 0 for inactive
     slots), out_tok[:, :n-1] are the accepted drafts and out_tok[:, n-1] is the bonus token."""
+    ext = _lib.ext()
+    if ext is not None:
+        out_tok, n = ext.spec_accept(pred, tok, stop_ids, active)
+        return out_tok, n
     check_tensor(pred, torch.int64, "pred")
     check_tensor(tok, torch.int64, "tok")
     if pred.dim() != 2 or pred.shape != tok.shape:
