@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libcolinfer_b200.so")
 
 F32, BF16 = 0, 1
 ROW_DEGENERATE, ROW_TIMEOUT, ROW_HIST_SLOW, ROW_SELECT_SLOW = 1, 2, 4, 8
-FORCE_DISTRIBUTION, TEST_MISS_BAND = 1, 0x4000
+FORCE_DISTRIBUTION, TEST_MISS_BAND, TEST_DROP_COPY = 1, 0x4000, 0x2000
 KERNEL_AUTO, KERNEL_STREAM = 0, 0x100
 KERNEL_CLUSTER = {1: 0x200, 2: 0x300, 4: 0x400, 8: 0x500}
 KERNEL_MASK = 0x700

@@ -652,6 +652,7 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     auto issue_row = [&](const long long rw) {
         fence_proxy_async();                                   // earlier reads of the buffer precede these writes
         const float* src = reinterpret_cast<const float*>(a.logits) + (size_t)rw * V + slice_lo;
+        if (a.flags & COLINFER_TEST_DROP_COPY) return;        // test flag: nothing is armed, nothing is in flight; the waits run out
         for (int c = 0; c < nchunks; ++c) {
             const int len = min(CI_CHUNK, slice_len - c * CI_CHUNK);
             mbar_expect_tx(&mbar[c], (uint32_t)len * 4u);
@@ -773,8 +774,10 @@ extern "C" __global__ void __launch_bounds__(CI_THREADS, 2) k_sample(const __gri
     for (int j = 0; j < CI_TGROUPS; ++j) tg[j] = CI_NEG_INF;
     // (1) the slice lands: wait for the bulk copies, or load it with plain loads (unaligned fp32 rows, bf16)
     if (a.use_bulk) {
+        const bool drop = (a.flags & COLINFER_TEST_DROP_COPY) != 0;
+        if (drop) for (int i = tid; i < slice_len; i += CI_THREADS) rowbuf[i] = 0.0f;   // (the test reads a defined buffer)
         for (int c = 0; c < nchunks; ++c)
-            if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, CI_WAIT_CYCLES)) sc->fail = 1;
+            if (!mbar_wait_bounded(&mbar[c], (uint32_t)par, drop ? 20000LL : CI_WAIT_CYCLES)) sc->fail = 1;
     } else {
         const size_t g0 = (size_t)row * V + slice_lo;
         if (a.dtype == COLINFER_BF16) {

@@ -65,6 +65,8 @@ enum {
     COLINFER_KERNEL_CLUSTER2 = 0x300, /* 2, */
     COLINFER_KERNEL_CLUSTER4 = 0x400, /* 4, */
     COLINFER_KERNEL_CLUSTER8 = 0x500, /* 8 CTAs */
+    COLINFER_TEST_DROP_COPY = 0x2000, /* test flag (cluster-resident kernel): the bulk copies of a row are never issued, so its
+                                         bounded waits run out: rows report COLINFER_ROW_TIMEOUT and the kernel returns */
     COLINFER_TEST_MISS_BAND = 0x4000 /* test flag: misplace the estimated top-p band so that the exact retry paths run;
                                         results are unchanged, rows report COLINFER_ROW_SELECT_SLOW */
 };

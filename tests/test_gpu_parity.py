@@ -217,6 +217,25 @@ def test_degenerate_rows_report_status_and_never_trap():
                      torch.zeros(0, dtype=torch.int32, device="cuda")).shape == (0, 1)
 
 
+def test_bounded_wait_of_the_cluster_kernel_reports_a_timeout():
+    """The cluster-resident kernel waits for its bulk copies with a limit.  With the test flag the copies are never
+    issued (nothing is armed, nothing is in flight): every wait runs out, the rows report COLINFER_ROW_TIMEOUT, the
+    kernel returns, and the next launch on the same context is clean."""
+    m = mods()
+    V, B = 151936, 4
+    w = wl.config3(B, V=V, H=64)
+    for k in ("history", "hist_len", "repetition_penalty", "presence_penalty", "frequency_penalty"):
+        w["params"].pop(k)
+    sp = wl.sampler_params(w["params"], V, "cuda")
+    logits, pos = w["logits"].cuda(), w["pos"].cuda()
+    good = m["draw"](logits, sp, pos, flags=_lib.KERNEL_CLUSTER[8])
+    out, st = m["draw"](logits, sp, pos, status=True, flags=_lib.KERNEL_CLUSTER[8] | _lib.TEST_DROP_COPY)
+    torch.cuda.synchronize()
+    assert ((st & _lib.ROW_TIMEOUT) != 0).all()
+    again, st2 = m["draw"](logits, sp, pos, status=True, flags=_lib.KERNEL_CLUSTER[8])
+    assert torch.equal(again, good) and int(st2.abs().sum()) == 0
+
+
 def test_neutral_penalties_are_a_bit_exact_no_op():
     m = mods()
     V, B = 4099, 6
