@@ -24,7 +24,9 @@ STREAM_PARTS = 9
 UNITS = [("sample.cu", "sample.o", []), ("ops.cu", "ops.o", []), ("logprobs.cu", "logprobs.o", []),
          ("rescore.cu", "rescore.o", []), ("gather.cu", "gather.o", []), ("stream_host.cu", "stream_host.o", [])] + \
         [("stream_part.cu", f"stream_part_{i}.o", [f"-DCOLINFER_STREAM_PART={i}"]) for i in range(STREAM_PARTS)]
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+# --fmad=false: fp32 expressions on a decision path are never contracted behind the source's back (the reference builds its
+# kernels the same way); the fused multiply-adds the kernels want are written as fmaf().
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false", "-Xcompiler", "-fPIC"]
 
 
 def _deps():
