@@ -265,7 +265,8 @@ extern "C" int colinfer_spec_accept(const int64_t* pred, const int64_t* tok, con
 // ------------------------------------------------------------------------------------------------ spec_verify (rejection)
 // Finish step: per slot, decide the accepted prefix from the row statistics of the target and draft rows, then, at a
 // rejection, stream the two rows of that position once to draw from the residual max(p - q, 0).
-#define VF_THREADS 1024
+#define VF_THREADS 256
+#define VF_NSEG 32                     // segments a slot's rejected position is summed in (one CTA each)
 struct VerifyArgs {
     const void* tl; const void* dl; int dtype;
     const int32_t* mask; int W;
@@ -273,6 +274,10 @@ struct VerifyArgs {
     const int64_t* draft_ids; const float* ua; const float* us;
     const colinfer_row_stats* st_t; const colinfer_row_stats* st_d; const int64_t* samp_t;
     int64_t* out_tok; int32_t* n;
+    int2* slot;                        // [B] (first rejected position j, mode: 0 = token known, 1 = residual draw)
+    u64* seg_sums;                     // [B, VF_NSEG] residual mass per segment of the rejected position
+    int seg;                           // elements per segment (a multiple of 128)
+    int vec;                           // fp32 rows that take 128-bit loads
     int B, k, V;
 };
 
@@ -291,99 +296,159 @@ __device__ double token_prob(const colinfer_row_stats& st, float l, long long to
     return exp((double)d) / ((double)st.mass_q * CI_MASS_INV);
 }
 // residual mass of one token in units of 2^-40 (fp32 arithmetic, integer result: order-independent sums)
-__device__ __forceinline__ u64 residual_q(float lt, float ld, const colinfer_row_stats& st, const colinfer_row_stats& sd,
-                                          float mt, float md, float inv_t, float inv_d) {
-    float p = 0.0f, q = 0.0f;
-    if (lt >= st.lcut && lt > CI_NEG_INF) p = exp2f((scale_logit(lt, st.tc) - mt) * CI_LOG2E) * inv_t;
-    if (ld >= sd.lcut && ld > CI_NEG_INF) q = exp2f((scale_logit(ld, sd.tc) - md) * CI_LOG2E) * inv_d;
-    const float rres = p - q;
-    return rres > 0.0f ? __float2ull_rn(rres * 1099511627776.0f) : 0ull;   // units of 2^-40
-}
+struct Residual {
+    colinfer_row_stats st, sd; float mt, md, inv_t, inv_d;
+    __device__ void init(const colinfer_row_stats& st_, const colinfer_row_stats& sd_) {
+        st = st_; sd = sd_;
+        mt = scale_logit(st.lmax, st.tc); md = scale_logit(sd.lmax, sd.tc);
+        inv_t = (float)(1.0 / ((double)st.mass_q * CI_MASS_INV)); inv_d = (float)(1.0 / ((double)sd.mass_q * CI_MASS_INV));
+    }
+    __device__ __forceinline__ u64 operator()(float lt, float ld) const {
+        float p = 0.0f, q = 0.0f;
+        if (lt >= st.lcut && lt > CI_NEG_INF) p = exp2f((scale_logit(lt, st.tc) - mt) * CI_LOG2E) * inv_t;
+        if (ld >= sd.lcut && ld > CI_NEG_INF) q = exp2f((scale_logit(ld, sd.tc) - md) * CI_LOG2E) * inv_d;
+        const float rres = p - q;
+        return rres > 0.0f ? __float2ull_rn(rres * 1099511627776.0f) : 0ull;   // units of 2^-40
+    }
+};
 
-__global__ void __launch_bounds__(VF_THREADS) k_verify_finish(const __grid_constant__ VerifyArgs a) {
-    __shared__ int s_j;
-    __shared__ int s_mode;                 // 0: token already known, 1: residual draw needed
-    __shared__ long long s_token;
-    __shared__ u64 wtot[VF_THREADS / 32];
-    const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Step 1, one thread per slot: the accepted prefix from the row statistics of the target and draft rows.
+__global__ void k_verify_decide(const __grid_constant__ VerifyArgs a) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= a.B) return;
     const int k = a.k, V = a.V;
     const colinfer_row_stats* st_t = a.st_t + (size_t)b * (k + 1);
     const colinfer_row_stats* st_d = a.st_d + (size_t)b * k;
-    if (threadIdx.x == 0) {
-        const bool greedy = !(a.temperature[b] > 0.0f);
-        int j = 0;
-        for (; j < k; ++j) {
-            const long long d = a.draft_ids[(size_t)b * k + j];
-            bool ok;
-            if (greedy) ok = (d == st_t[j].argmax);
-            else if (d < 0 || d >= V) ok = false;
-            else {
-                const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
-                float lt = load_logit(a.tl, a.dtype, ((size_t)b * (k + 1) + j) * V + d);
-                float ld = load_logit(a.dl, a.dtype, ((size_t)b * k + j) * V + d);
-                if (!mask_allows(mrow, (int)d)) { lt = CI_NEG_INF; ld = CI_NEG_INF; }
-                const double p = token_prob(st_t[j], lt, d), q = token_prob(st_d[j], ld, d);
-                // (a draft token the target gives no probability -- masked, or outside its kept set -- is never accepted,
-                // whatever the draft thought of it: 0 <= 0 must not pass)
-                ok = p > 0.0 && (double)a.ua[(size_t)b * k + j] * q <= p;
-            }
-            if (!ok) break;
+    const bool greedy = !(a.temperature[b] > 0.0f);
+    int j = 0;
+    for (; j < k; ++j) {
+        const long long d = a.draft_ids[(size_t)b * k + j];
+        bool ok;
+        if (greedy) ok = (d == st_t[j].argmax);
+        else if (d < 0 || d >= V) ok = false;
+        else {
+            const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
+            float lt = load_logit(a.tl, a.dtype, ((size_t)b * (k + 1) + j) * V + d);
+            float ld = load_logit(a.dl, a.dtype, ((size_t)b * k + j) * V + d);
+            if (!mask_allows(mrow, (int)d)) { lt = CI_NEG_INF; ld = CI_NEG_INF; }
+            const double p = token_prob(st_t[j], lt, d), q = token_prob(st_d[j], ld, d);
+            // (a draft token the target gives no probability -- masked, or outside its kept set -- is never accepted,
+            // whatever the draft thought of it: 0 <= 0 must not pass)
+            ok = p > 0.0 && (double)a.ua[(size_t)b * k + j] * q <= p;
         }
-        s_j = j;
-        if (greedy) { s_mode = 0; s_token = st_t[j].argmax; }
-        else if (j == k) { s_mode = 0; s_token = a.samp_t[(size_t)b * (k + 1) + k]; }
-        else if ((st_t[j].status | st_d[j].status) & (COLINFER_ROW_DEGENERATE | COLINFER_ROW_TIMEOUT)) {
-            s_mode = 0; s_token = a.samp_t[(size_t)b * (k + 1) + j];
-        } else s_mode = 1;
+        if (!ok) break;
+    }
+    int mode = 1;
+    if (greedy || j == k) mode = 0;
+    else if ((st_t[j].status | st_d[j].status) & (COLINFER_ROW_DEGENERATE | COLINFER_ROW_TIMEOUT)) mode = 0;
+    a.slot[b] = make_int2(j, mode);
+}
+
+// Step 2, VF_NSEG CTAs per slot: the residual mass max(p - q, 0) of one segment of the rejected position's two rows,
+// streamed once with 128-bit loads where the rows allow it.
+__global__ void __launch_bounds__(VF_THREADS) k_verify_residual(const __grid_constant__ VerifyArgs a) {
+    __shared__ u64 wsum[VF_THREADS / 32];
+    const int b = blockIdx.x / VF_NSEG, sgi = blockIdx.x % VF_NSEG;
+    const int2 sl = a.slot[b];
+    if (sl.y != 1) return;
+    const int j = sl.x, k = a.k, V = a.V, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Residual res;
+    res.init(a.st_t[(size_t)b * (k + 1) + j], a.st_d[(size_t)b * k + j]);
+    const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
+    const size_t bt = ((size_t)b * (k + 1) + j) * V, bd = ((size_t)b * k + j) * V;
+    const int lo = min(sgi * a.seg, V), hi = min(lo + a.seg, V);
+    u64 acc = 0;
+    if (a.vec) {
+        const float* pt = reinterpret_cast<const float*>(a.tl) + bt;
+        const float* pd = reinterpret_cast<const float*>(a.dl) + bd;
+        for (int i0 = lo + threadIdx.x * 4; i0 < hi; i0 += 2 * VF_THREADS * 4) {
+            const int i1 = i0 + VF_THREADS * 4;
+            const float4 t0 = __ldcg(reinterpret_cast<const float4*>(pt + i0)), d0 = __ldcg(reinterpret_cast<const float4*>(pd + i0));
+            float4 t1 = make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF), d1 = t1;
+            if (i1 < hi) { t1 = __ldcg(reinterpret_cast<const float4*>(pt + i1)); d1 = __ldcg(reinterpret_cast<const float4*>(pd + i1)); }
+            const float tt[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w}, dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int i = (e < 4 ? i0 : i1 - 4) + e;
+                if (i < hi && mask_allows(mrow, i)) acc += res(tt[e], dd[e]);
+            }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += VF_THREADS)
+            if (mask_allows(mrow, i)) acc += res(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i));
+    }
+    const u64 wt = warp_sum_u64(acc);
+    if (lane == 0) wsum[warp] = wt;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 t = 0;
+        for (int w = 0; w < VF_THREADS / 32; ++w) t += wsum[w];
+        a.seg_sums[(size_t)b * VF_NSEG + sgi] = t;
+    }
+}
+
+// Step 3, one CTA per slot: the segment in which the running residual mass reaches us * total, then the token inside it
+// (threads own consecutive chunks of the segment: token order); and the slot's outputs.
+__global__ void __launch_bounds__(VF_THREADS) k_verify_pick(const __grid_constant__ VerifyArgs a) {
+    __shared__ u64 tsum[VF_THREADS];
+    __shared__ long long s_token;
+    const int b = blockIdx.x, k = a.k, V = a.V, tid = threadIdx.x;
+    const int2 sl = a.slot[b];
+    const int j = sl.x;
+    if (tid == 0) {
+        if (sl.y == 0) {
+            const bool greedy = !(a.temperature[b] > 0.0f);
+            s_token = greedy ? a.st_t[(size_t)b * (k + 1) + j].argmax : a.samp_t[(size_t)b * (k + 1) + j];
+        } else s_token = -1;
     }
     __syncthreads();
-    const int j = s_j;
-    if (s_mode == 1) {
-        const colinfer_row_stats st = st_t[j], sd = st_d[j];
-        const float mt = scale_logit(st.lmax, st.tc), md = scale_logit(sd.lmax, sd.tc);
-        const float inv_t = (float)(1.0 / ((double)st.mass_q * CI_MASS_INV)), inv_d = (float)(1.0 / ((double)sd.mass_q * CI_MASS_INV));
-        const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
-        const size_t bt = ((size_t)b * (k + 1) + j) * V, bd = ((size_t)b * k + j) * V;
-        const int nwarps = VF_THREADS / 32;
-        const int reg = (((V + 31) / 32 + nwarps - 1) / nwarps) * 32;
-        const int lo = min(warp * reg, V), hi = min(lo + reg, V);
-        u64 acc = 0;
-        for (int i = lo + lane; i < hi; i += 32) {
-            if (mask_allows(mrow, i))
-                acc += residual_q(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i), st, sd, mt, md, inv_t, inv_d);
-        }
-        const u64 wt = warp_sum_u64(acc);
-        if (lane == 0) wtot[warp] = wt;
-        if (threadIdx.x == 0) s_token = -1;
-        __syncthreads();
-        u64 total = 0, woff = 0;
-        for (int w = 0; w < nwarps; ++w) { if (w < warp) woff += wtot[w]; total += wtot[w]; }
+    if (sl.y == 1) {
+        u64 total = 0;
+        for (int s = 0; s < VF_NSEG; ++s) total += a.seg_sums[(size_t)b * VF_NSEG + s];
         if (total == 0) {
-            if (threadIdx.x == 0) s_token = a.samp_t[(size_t)b * (k + 1) + j];   // no residual mass: draw from p_j
+            if (tid == 0) s_token = a.samp_t[(size_t)b * (k + 1) + j];   // no residual mass: draw from p_j
         } else {
             double t = ceil((double)a.us[(size_t)b * (k + 1) + j] * (double)total);
             u64 target = t <= 1.0 ? 1ull : (u64)t;
             if (target > total) target = total;
-            if (woff < target && target <= woff + wt) {
-                u64 run = woff;
-                for (int i0 = lo; i0 < hi; i0 += 32) {
-                    const int i = i0 + lane;
-                    u64 v = 0;
-                    if (i < hi && mask_allows(mrow, i))
-                        v = residual_q(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i), st, sd, mt, md, inv_t, inv_d);
-                    const u64 incl = warp_incl_scan_u64(v, lane);
-                    const unsigned hit = __ballot_sync(0xffffffffu, run + incl >= target);
-                    if (hit) {
-                        if (lane == __ffs(hit) - 1) s_token = i;
-                        break;
-                    }
-                    run += __shfl_sync(0xffffffffu, incl, 31);
+            int sx = 0; u64 before = 0;
+            for (; sx < VF_NSEG - 1; ++sx) {
+                const u64 v = a.seg_sums[(size_t)b * VF_NSEG + sx];
+                if (before + v >= target) break;
+                before += v;
+            }
+            Residual res;
+            res.init(a.st_t[(size_t)b * (k + 1) + j], a.st_d[(size_t)b * k + j]);
+            const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
+            const size_t bt = ((size_t)b * (k + 1) + j) * V, bd = ((size_t)b * k + j) * V;
+            const int lo = min(sx * a.seg, V), hi = min(lo + a.seg, V);
+            const int per = (hi - lo + VF_THREADS - 1) / VF_THREADS;
+            const int c_lo = min(lo + tid * per, hi), c_hi = min(c_lo + per, hi);
+            u64 mine = 0;
+            for (int i = c_lo; i < c_hi; ++i)
+                if (mask_allows(mrow, i)) mine += res(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i));
+            tsum[tid] = mine;
+            __syncthreads();
+            if (tid == 0) {
+                u64 run = before;
+                int tx = VF_THREADS - 1;
+                for (int t2 = 0; t2 < VF_THREADS; ++t2) { if (run + tsum[t2] >= target) { tx = t2; break; } run += tsum[t2]; }
+                tsum[0] = run; s_token = -2 - tx;                 // (thread tx walks its chunk from the running sum `run`)
+            }
+            __syncthreads();
+            if (s_token == -2 - tid) {
+                u64 run = tsum[0];
+                long long tok = c_hi > c_lo ? c_hi - 1 : lo;
+                for (int i = c_lo; i < c_hi; ++i) {
+                    if (mask_allows(mrow, i)) run += res(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i));
+                    if (run >= target) { tok = i; break; }
                 }
+                s_token = tok;
             }
         }
         __syncthreads();
     }
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         int64_t* o = a.out_tok + (size_t)b * (k + 1);
         for (int i = 0; i <= k; ++i) o[i] = i < j ? a.draft_ids[(size_t)b * k + i] : -1;
         o[j] = s_token;
@@ -391,7 +456,10 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_finish(const __grid_const
     }
 }
 
-extern "C" int64_t colinfer_spec_verify_stats_bytes(int B, int k) { return (int64_t)B * (2 * k + 1) * (int64_t)sizeof(colinfer_row_stats); }
+// scratch_stats holds, after the 2k + 1 row statistics of every slot, the per-slot decision and the segment sums
+extern "C" int64_t colinfer_spec_verify_stats_bytes(int B, int k) {
+    return (int64_t)B * (2 * k + 1) * (int64_t)sizeof(colinfer_row_stats) + (int64_t)B * 8 + (int64_t)B * VF_NSEG * 8;
+}
 extern "C" int64_t colinfer_spec_verify_ids_bytes(int B, int k) { return (int64_t)B * (k + 1) * 8; }
 
 extern "C" int colinfer_spec_verify(const void* target_logits, const void* draft_logits, int dtype, const int32_t* mask,
@@ -418,7 +486,14 @@ extern "C" int colinfer_spec_verify(const void* target_logits, const void* draft
     a.tl = target_logits; a.dl = draft_logits; a.dtype = dtype; a.mask = mask; a.W = W;
     a.temperature = params->temperature; a.draft_ids = draft_ids; a.ua = ua; a.us = us;
     a.st_t = st_t; a.st_d = st_d; a.samp_t = scratch_ids; a.out_tok = out_tok; a.n = n; a.B = B; a.k = k; a.V = V;
-    k_verify_finish<<<B, VF_THREADS, 0, (cudaStream_t)stream>>>(a);
+    a.slot = reinterpret_cast<int2*>(st_d + (size_t)B * k);
+    a.seg_sums = reinterpret_cast<u64*>(a.slot + B);
+    a.seg = (((V + VF_NSEG - 1) / VF_NSEG + 127) / 128) * 128;
+    a.vec = (dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)target_logits) & 15) == 0 && (((uintptr_t)draft_logits) & 15) == 0) ? 1 : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    k_verify_decide<<<(B + 127) / 128, 128, 0, st>>>(a);
+    k_verify_residual<<<B * VF_NSEG, VF_THREADS, 0, st>>>(a);
+    k_verify_pick<<<B, VF_THREADS, 0, st>>>(a);
     return (int)cudaGetLastError();
 }
 
