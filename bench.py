@@ -349,6 +349,67 @@ def run_rescore(args):
     print(json.dumps(line), flush=True)
 
 
+def run_draft(args):
+    """The greedy draft of the low-rank draft heads in one launch (top-256 of the approximate logits, exact rescoring against
+    the BF16 lm_head, argmax, probability) beside the reference's own expressions for it (engine/spec/mtp4.py:416-423: topk,
+    rescoring op, argmax, gathers, logsumexp, exp, clamp) run with torch and this library's rescoring op on the same GPU.
+    Slots per call: 16 (what one captured cycle drafts at most), and 4 and 256 in `sweep`.  One GPU."""
+    import torch
+    from colinfer_b200 import _lib
+    from colinfer_b200.kernels import ops
+    from colinfer_b200.spec.draft import lowrank_draft
+    _lib.lib()
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU fallback)"
+    dev = torch.device("cuda", 0)
+    Vd, K, NC, rows_w = 69_632, 2560, 256, 151_936
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(rows_w, K, generator=g) * 0.02).bfloat16().to(dev)           # 778 MB: larger than L2
+    vid = torch.randperm(rows_w, generator=g)[:Vd].to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def inputs(N):
+        x = torch.randn(N, K, generator=g).bfloat16().to(dev)
+        ap = (x.float() @ w[vid].float().T + 0.3 * torch.randn(N, Vd, generator=g).to(dev)).contiguous()
+        return x, ap
+
+    def theirs(x, ap):
+        cand = ap.topk(NC, -1).indices
+        ex = ops().rescore_bf16(x, w, vid[cand])
+        best = ex.argmax(-1, keepdim=True)
+        ids = vid[cand.gather(-1, best)].view(-1)
+        return ids, torch.exp(ex.gather(-1, best) - torch.logsumexp(ap, -1, keepdim=True)).clamp_max(1.0).view(-1)
+
+    reps = max(args.steps, 10)
+    sweep, main = [], None
+    with ClockSampler(0) as clk:
+        for N in (16, 4, 256):
+            x, ap = inputs(N)
+            a, b = lowrank_draft(ap, x, w, vid), theirs(x, ap)
+            same = bool(torch.equal(a[0], b[0]))
+            mine_us, mine_best = per_launch_us(torch, lambda: lowrank_draft(ap, x, w, vid), flush, reps, max(args.warmup, 3))
+            ref_us, ref_best = per_launch_us(torch, lambda: theirs(x, ap), flush, reps, max(args.warmup, 3))
+            rec = {"slots": N, "us_per_call": mine_us, "us_best": mine_best, "reference_expressions_us": ref_us,
+                   "reference_expressions_us_best": ref_best, "same_ids": same}
+            if N == 16:
+                main = rec
+            else:
+                sweep.append(rec)
+    peak, kind = measured_peak()
+    N = 16
+    bytes_slot = Vd * 4 + NC * K * 2 + K * 2 + 12
+    ach = bytes_slot * N / (main["us_per_call"] * 1e-6) / 1e9
+    line = {"metric": "drafted slots/s", "value": N / (main["us_per_call"] * 1e-6), "unit": "slots/s", "n_gpus": 1, "steps": reps,
+            "warmup": max(args.warmup, 3), "ms_per_step": main["us_per_call"] * 1e-3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"low-rank draft pick: {N} slots, approximations fp32 [{N}, {Vd}], {NC} candidates rescored "
+                                   f"against a BF16 lm_head [{rows_w}, {K}]; L2 overwritten between calls"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_kind": f"of {kind} copy rate", "bytes_per_slot": bytes_slot, "kernel": "k_draft_pick", "traffic": None},
+            "reference_expressions_us": main["reference_expressions_us"], "same_ids": main["same_ids"], "sweep": sweep,
+            "gpu_launches": reps, "clocks": clk.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def per_launch_us(torch, fn, flush, reps: int, warm: int = 3):
     """Median / best device time of one call of fn (CUDA events on the current stream), the L2 overwritten in between."""
     for _ in range(warm):
@@ -436,9 +497,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the other configurations (and the fixed-batch split)")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="measure blocks of --steps steps for at least this long")
-    ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs", "rescore"],
+    ap.add_argument("--workload", default="sampling", choices=["sampling", "logprobs", "rescore", "draft"],
                     help="sampling: the headline path (config 3); logprobs: logprobs of emitted tokens with 20 alternatives; "
-                         "rescore: draft-head candidate rescoring (256 candidates of a 69,632 x 2560 BF16 lm_head per slot)")
+                         "rescore: draft-head candidate rescoring (256 candidates of a 69,632 x 2560 BF16 lm_head per slot); "
+                         "draft: the whole greedy draft of the low-rank heads (top-256, rescoring, argmax, probability) in one launch")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the sampled ids are gathered -- peer: one small kernel that stores them into every rank's "
                          "buffer over NVLink (falls back to nccl when peer memory cannot be mapped); nccl: all_gather")
@@ -451,6 +513,8 @@ def main():
         return run_logprobs(args)
     if args.workload == "rescore":
         return run_rescore(args)
+    if args.workload == "draft":
+        return run_draft(args)
     if args.impl == "reference":
         return run_reference(args)
     if args.impl == "reference-gpu":

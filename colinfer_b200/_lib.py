@@ -69,6 +69,10 @@ SIGNATURES = {
                                         C.c_int64, C.c_void_p]),
     "colinfer_rescore_nvfp4": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p, C.c_int,
                                          C.c_int, C.c_int, C.c_int64, C.c_void_p]),
+    "colinfer_draft_pick_scratch_bytes": (C.c_int64, [C.c_int]),
+    "colinfer_draft_pick": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int,
+                                      C.c_void_p, C.c_int64, C.c_void_p]),
     "colinfer_spec_verify_stats_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_spec_verify_ids_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "colinfer_sample_geometry": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(Geometry)]),

@@ -22,7 +22,7 @@ LIB = os.path.join(HERE, "libcolinfer_b200.so")
 STREAM_PARTS = 9
 # (source, object name, extra flags)
 UNITS = [("sample.cu", "sample.o", []), ("ops.cu", "ops.o", []), ("logprobs.cu", "logprobs.o", []),
-         ("rescore.cu", "rescore.o", []), ("gather.cu", "gather.o", []), ("stream_host.cu", "stream_host.o", [])] + \
+         ("rescore.cu", "rescore.o", []), ("gather.cu", "gather.o", []), ("draft_pick.cu", "draft_pick.o", []), ("stream_host.cu", "stream_host.o", [])] + \
         [("stream_part.cu", f"stream_part_{i}.o", [f"-DCOLINFER_STREAM_PART={i}"]) for i in range(STREAM_PARTS)]
 # --fmad=false: fp32 expressions on a decision path are never contracted behind the source's back (the reference builds its
 # kernels the same way); the fused multiply-adds the kernels want are written as fmaf().

@@ -1,0 +1,63 @@
+"""The greedy draft of the low-rank draft heads (the step that feeds verify): the `if self.lr_B is not None` block of
+MtpHead.draft (engine/spec/mtp.py:301-309) and Mtp4Head.draft (engine/spec/mtp4.py:416-423) as one launch."""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ..kernels import _stream, check_tensor
+
+LOWRANK_CANDS = 256     # engine/spec/mtp.py:70
+
+
+def lowrank_draft(ap: torch.Tensor, g2: torch.Tensor, w: torch.Tensor, vocab_ids: torch.Tensor | None = None,
+                  sf: torch.Tensor | None = None, gs: float | None = None, n_cands: int = LOWRANK_CANDS,
+                  ctas_per_slot: int = 0, want_index: bool = False):
+    """ap fp32 [N, Vd]: the low-rank head's approximate logits over the draft vocabulary (lr_B(lr_A(g2)) in the reference);
+    g2 bf16 [N, K]: the drafter's outputs; w: the lm_head itself, bf16 [rows, K], or NVFP4 (uint8 [rows, K / 2] with sf
+    [rows, K / 16] E4M3 scales and the global scale gs); vocab_ids int64 [Vd]: draft-vocabulary index -> token id = lm_head
+    row.  Returns (ids int64 [N], p fp32 [N]) as the reference's block does: of the n_cands largest approximations the
+    token with the largest exact logit, and exp(that logit - logsumexp(ap)) clamped to 1.  want_index: also the winning
+    draft-vocabulary index (int32 [N]) and its exact logit (fp32 [N])."""
+    check_tensor(ap, torch.float32, "ap")
+    check_tensor(g2, torch.bfloat16, "g2")
+    if ap.dim() != 2 or g2.dim() != 2 or g2.size(0) != ap.size(0):
+        raise RuntimeError("ap [N, Vd], g2 [N, K]")
+    N, Vd = ap.shape
+    K = g2.size(1)
+    fp4 = sf is not None
+    if fp4:
+        check_tensor(w, torch.uint8, "w")
+        if sf.dtype not in (torch.uint8, torch.float8_e4m3fn):
+            raise RuntimeError("sf must be uint8 or float8_e4m3fn")
+        check_tensor(sf, None, "sf")
+        if gs is None or w.dim() != 2 or w.size(1) * 2 != K or K % 16 or sf.numel() != w.size(0) * (K // 16):
+            raise RuntimeError("w [rows, K / 2], sf [rows, K / 16] with K % 16 == 0, and gs")
+    else:
+        check_tensor(w, torch.bfloat16, "w")
+        if w.dim() != 2 or w.size(1) != K or K % 8:
+            raise RuntimeError("w [rows, K] with K % 8 == 0")
+    if vocab_ids is not None:
+        check_tensor(vocab_ids, torch.int64, "vocab_ids")
+        if vocab_ids.numel() != Vd:
+            raise RuntimeError("vocab_ids [Vd]")
+    if not 1 <= n_cands <= min(Vd, 1024):
+        raise RuntimeError("n_cands must lie in 1 .. min(Vd, 1024)")
+    if g2.data_ptr() % 16 or w.data_ptr() % 16:
+        raise RuntimeError("g2 and w must be 16-byte aligned")
+    dev = ap.device
+    ids = torch.empty(N, dtype=torch.int64, device=dev)
+    p = torch.empty(N, dtype=torch.float32, device=dev)
+    idx = torch.empty(N, dtype=torch.int32, device=dev) if want_index else None
+    ex = torch.empty(N, dtype=torch.float32, device=dev) if want_index else None
+    if N:
+        lib = _lib.lib()
+        nbytes = lib.colinfer_draft_pick_scratch_bytes(N)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        _lib.check(lib.colinfer_draft_pick(ap.data_ptr(), g2.data_ptr(), w.data_ptr(), sf.data_ptr() if fp4 else None,
+                                           float(gs) if fp4 else 1.0, 1 if fp4 else 0,
+                                           vocab_ids.data_ptr() if vocab_ids is not None else None, ids.data_ptr(), p.data_ptr(),
+                                           idx.data_ptr() if want_index else None, ex.data_ptr() if want_index else None,
+                                           N, Vd, K, n_cands, w.size(0), ctas_per_slot, scratch.data_ptr(), nbytes, _stream()),
+                   "draft_pick")
+    return (ids, p, idx, ex) if want_index else (ids, p)

@@ -168,6 +168,24 @@ int colinfer_rescore_bf16(const void* x, const void* w, const int64_t* cand, flo
 int colinfer_rescore_nvfp4(const void* x, const void* w, const void* sf, float gs, const int64_t* cand, float* out,
                            int B, int K, int NC, int64_t rows_w, void* stream);
 
+/* Replaces the greedy draft() of the low-rank draft heads (engine/spec/mtp.py:301-309, engine/spec/mtp4.py:416-423: topk
+ * over the approximate logits, gather of the candidates' lm_head rows, rescoring, argmax, two more gathers, logsumexp,
+ * exp, clamp -- nine launches) with one.  ap fp32 [N, Vd] = the approximate logits over the draft vocabulary; x bf16
+ * [N, K]; w = the lm_head, [rows_w, K] bf16 (w_format COLINFER_W_BF16) or NVFP4 as for colinfer_rescore_nvfp4 (sf, gs;
+ * COLINFER_W_NVFP4); vocab_ids int64 [Vd] maps a draft-vocabulary index to its lm_head row and token id (NULL: identity).
+ * Of the NC (<= 1024, <= Vd) largest entries of ap[n] (equal values: lower index first), the one with the largest exact
+ * logit ex = x[n] . w[row] (accumulated as colinfer_rescore_* does; equal ex: larger ap, then lower index -- what argmax
+ * over topk's sorted list gives) is chosen: out_ids[n] = its token id, out_p[n] = min(1, exp(ex - logsumexp(ap[n]))),
+ * out_idx[n] (optional) = its draft-vocabulary index, out_ex[n] (optional) = ex.  A candidate whose row lies outside
+ * [0, rows_w) is never chosen.  ctas_per_slot: 0 = by N, or 1, 2, 4, 8, 16.  scratch: colinfer_draft_pick_scratch_bytes(N)
+ * bytes, 16-byte aligned, contents irrelevant; nothing in the launch waits for another CTA. */
+enum { COLINFER_W_BF16 = 0, COLINFER_W_NVFP4 = 1 };
+int64_t colinfer_draft_pick_scratch_bytes(int N);
+int colinfer_draft_pick(const float* ap, const void* x, const void* w, const void* sf, float gs, int w_format,
+                        const int64_t* vocab_ids, int64_t* out_ids, float* out_p, int32_t* out_idx, float* out_ex,
+                        int N, int Vd, int K, int NC, int64_t rows_w, int ctas_per_slot, void* scratch, int64_t scratch_bytes,
+                        void* stream);
+
 /* The id gather of a row-sharded step over NVLink, in one launch of one CTA (no counterpart in the reference, which runs
  * on one GPU; it takes the place of an all-gather call behind the sampler).  Every rank calls it with its own ids
  * `local` [n_local] (the rows [row_offset, row_offset + n_local) of the step): they are stored into every rank's gather

@@ -450,3 +450,32 @@ def rescore_nvfp4(x_bits, w_u8, sf_u8, gs, cand):
             acc = np.where(ok[None, :], upd, acc)
         out[b] = (_warp_xor_sum(acc) * np.float32(gs)).astype(np.float32)
     return out
+
+
+def draft_pick(ap, x_bits, vocab_ids, n_cands, w_bits=None, w_u8=None, sf_u8=None, gs=None):
+    """The greedy draft of the low-rank heads (engine/spec/mtp.py:301-309, engine/spec/mtp4.py:416-423): the n_cands largest
+    entries of each row of ap (equal values: lower index first -- the order torch.topk's sorted list has apart from ties),
+    their exact logits in the rescoring kernels' accumulation order, the first maximum of those in that list, and
+    p = min(1, exp(ex - logsumexp(ap))).  ap fp32 [N, Vd]; vocab_ids [Vd] or None.  Returns (token ids [N], p float64 [N],
+    winning draft-vocabulary index [N], its exact logit fp32 [N], margin [N] = gap between the two largest exact logits of
+    different candidates, 0 where they tie)."""
+    ap = np.asarray(ap, dtype=np.float32)
+    N, Vd = ap.shape
+    vid = np.arange(Vd, dtype=np.int64) if vocab_ids is None else np.asarray(vocab_ids, dtype=np.int64)
+    ids, ps, idxs, exs, margins = [], [], [], [], []
+    for n in range(N):
+        order = np.lexsort((np.arange(Vd), -ap[n].astype(np.float64)))[:n_cands]     # value descending, index ascending
+        rows = vid[order][None, :]
+        if w_bits is not None:
+            ex = rescore_bf16(x_bits[n:n + 1], w_bits, rows)[0]
+        else:
+            ex = rescore_nvfp4(x_bits[n:n + 1], w_u8, sf_u8, gs, rows)[0]
+        best = int(np.argmax(ex))                                                   # first maximum in list order
+        m = ap[n].astype(np.float64).max()
+        lse = m + np.log(np.exp(ap[n].astype(np.float64) - m).sum())
+        srt = np.sort(ex.astype(np.float64))
+        ids.append(int(vid[order[best]])); idxs.append(int(order[best])); exs.append(ex[best])
+        ps.append(min(1.0, float(np.exp(np.float64(ex[best]) - lse))))
+        margins.append(float(srt[-1] - srt[-2]) if len(srt) > 1 else np.inf)
+    return (np.array(ids, dtype=np.int64), np.array(ps), np.array(idxs, dtype=np.int64), np.array(exs, dtype=np.float32),
+            np.array(margins))
