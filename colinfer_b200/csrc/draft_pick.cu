@@ -34,6 +34,7 @@ namespace dpk {
 constexpr int NT = 512, NW = NT / 32;
 constexpr int BINS = 4096;            // bins of one level (12 bits; the last level has 256)
 constexpr int LCAP = 4096;            // listed entries (what reaches the floor; or sure ones from the front, the pivot bin's from the back)
+constexpr int WCAP = LCAP / NW;        // a warp's own stretch of the list on the fast route
 constexpr int PCAP = BINS / 2;        // the pivot bin's entries, in the histogram's memory
 constexpr int MAXC = 1024;            // candidates per slot at most
 
@@ -47,8 +48,8 @@ struct Args {
 };
 
 struct Sc {
-    float wf[NW]; float wsum[NW]; int wi[NW]; Partial wbest[NW];
-    int pivot, above, h, n_all, n_sure, n_piv, n_mine, istar;
+    float wf[NW]; float wsum[NW]; int wi[NW]; int wcnt[NW]; Partial wbest[NW];
+    int pivot, above, h, n_sure, n_piv, n_mine, istar;
 };
 
 __device__ __forceinline__ uint32_t fkey(float x) {                  // larger value <=> larger key; NaN above everything
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(NT) k_draft_pick(const Args a) {
         const uint4* xg = reinterpret_cast<const uint4*>(a.x + (size_t)n * a.K);
         for (int c = tid; c < (a.K >> 3); c += NT) xs[c] = __ldg(xg + c);
     }
-    if (tid == 0) { sc->n_all = 0; sc->n_sure = 0; sc->n_piv = 0; sc->n_mine = 0; sc->istar = INT_MAX; sc->pivot = 0; sc->above = 0; sc->h = 0; }
+    if (tid == 0) { sc->n_sure = 0; sc->n_piv = 0; sc->n_mine = 0; sc->istar = INT_MAX; sc->pivot = 0; sc->above = 0; sc->h = 0; }
     for (int i = tid; i < BINS; i += NT) hist[i] = 0;
 
     // ---- a floor under the candidates, from the head of the row (each thread's first batch of loads): with r = ceil(NC / NW),
@@ -191,23 +192,57 @@ __global__ void __launch_bounds__(NT) k_draft_pick(const Args a) {
     }
     const uint32_t floor_k = fkey(floor_v);
 
-    // ---- the one pass over the whole row: a running maximum and sum of exp per thread (the log-sum-exp), and whatever
-    // reaches the floor is listed and counted in the histogram of the top 12 bits of its key
-    float mx, ssum;
-    {
+    // ---- the fast route, one pass over the whole row (rows read with 128-bit loads).  Per batch of U loads: the running
+    // maximum and sum of exp of the thread (the log-sum-exp; no branch: one rescale per batch); and each value that reaches
+    // the floor is listed in the warp's own stretch of the list (a ballot and a count per warp: no atomics)
+    float mx = ninf, ssum = 0.f;
+    bool fast = vec;
+    if (fast) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int n4 = Vd >> 2, wbase = warp * WCAP;
+        const unsigned lt = (1u << lane) - 1u;
+        float* lval = reinterpret_cast<float*>(lkey);                // values first; their keys take their place below
         float m = -3.0e38f, s = 0.f;                                 // finite, so that -inf values add exp(-inf) = 0
-        for_row(row, Vd, vec, [&](float v, int i) {
-            if (v > m) { s = s * ex2_fast((m - v) * L2E) + 1.0f; m = v; }
-            else s += ex2_fast((v - m) * L2E);
-            if (!(v < floor_v)) {
-                const uint32_t k = fkey(v);
-                if (k >= floor_k) {
-                    atomicAdd(&hist[k >> 20], 1u);
-                    const int p = atomicAdd(&sc->n_all, 1);
-                    if (p < LCAP) { lkey[p] = k; lidx[p] = i; }
+        int cnt = 0;                                                 // the same in every lane
+        for (int b0 = 0; b0 < n4; b0 += NT * U) {
+            const int i0 = b0 + tid;
+            const bool full = b0 + NT * U <= n4;                     // the same for the whole CTA
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = __ldg(r4 + (full ? i0 + u * NT : min(i0 + u * NT, n4 - 1)));
+            float bm = ninf;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float q = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
+                bm = (full || i0 + u * NT < n4) ? fmaxf(bm, q) : bm;
+            }
+            const float nm = fmaxf(m, bm);
+            s *= ex2_fast((m - nm) * L2E);
+            m = nm;
+            float t = 0.f;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float q = (ex2_fast((v[u].x - m) * L2E) + ex2_fast((v[u].y - m) * L2E)) +
+                                (ex2_fast((v[u].z - m) * L2E) + ex2_fast((v[u].w - m) * L2E));
+                t += (full || i0 + u * NT < n4) ? q : 0.f;
+            }
+            s += t;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool valid = full || i0 + u * NT < n4;
+                const float c4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const bool pass = valid && !(c4[c] < floor_v);
+                    const unsigned bal = __ballot_sync(0xffffffffu, pass);
+                    if (bal) {
+                        const int pos = cnt + __popc(bal & lt);
+                        if (pass && pos < WCAP) { lval[wbase + pos] = c4[c]; lidx[wbase + pos] = 4 * (i0 + u * NT) + c; }
+                        cnt += __popc(bal);
+                    }
                 }
             }
-        });
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float mo = __shfl_xor_sync(0xffffffffu, m, o), so = __shfl_xor_sync(0xffffffffu, s, o);
@@ -215,27 +250,35 @@ __global__ void __launch_bounds__(NT) k_draft_pick(const Args a) {
             s = s * ex2_fast((m - mm) * L2E) + so * ex2_fast((mo - mm) * L2E);
             m = mm;
         }
-        if (lane == 0) { sc->wf[warp] = m; sc->wsum[warp] = s; }
+        if (lane == 0) { sc->wf[warp] = m; sc->wsum[warp] = s; sc->wcnt[warp] = cnt; }
         __syncthreads();
         mx = sc->wf[0];
         for (int w = 1; w < NW; ++w) mx = fmaxf(mx, sc->wf[w]);
-        ssum = 0.f;
-        for (int w = 0; w < NW; ++w) ssum += sc->wsum[w] * ex2_fast((sc->wf[w] - mx) * L2E);
+        for (int w = 0; w < NW; ++w) { ssum += sc->wsum[w] * ex2_fast((sc->wf[w] - mx) * L2E); fast = fast && sc->wcnt[w] <= WCAP; }
     }
-    find_pivot(hist, BINS, NC, sc);
-    const int n_all = sc->n_all;
-    uint32_t pmask = 0xFFFu << 20, pval = (uint32_t)sc->pivot << 20;
-    int above_total = sc->above, h = sc->h;
-    __syncthreads();                                                 // the histogram is dead: its memory takes the pivot bin's entries
-
-    if (n_all <= LCAP && h <= PCAP) {
-        // ---- everything that can matter is listed: above the pivot bin it is a candidate, inside the bin it is ranked
-        const int need = NC - above_total;
-        for (int e = tid; e < n_all; e += NT) {
-            const uint32_t k = lkey[e]; const int i = lidx[e];
-            if ((k >> 20) > (uint32_t)sc->pivot) { if ((i & gmask) == g) { const int p = atomicAdd(&sc->n_mine, 1); mine[p] = i; mkey[p] = k; } }
-            else if ((k >> 20) == (uint32_t)sc->pivot) { const int p = atomicAdd(&sc->n_piv, 1); pkey[p] = k; pidx[p] = i; }
-        }
+    if (fast) {
+        // the histogram of the top 12 bits of the listed values' keys, and the bin that holds the NC-th largest of them
+        for (int e = tid; e < LCAP; e += NT)
+            if ((e & (WCAP - 1)) < sc->wcnt[e / WCAP]) {
+                const uint32_t k = fkey(__uint_as_float(lkey[e]));
+                lkey[e] = k;
+                atomicAdd(&hist[k >> 20], 1u);
+            }
+        __syncthreads();
+        find_pivot(hist, BINS, NC, sc);
+        fast = sc->h <= PCAP;
+        __syncthreads();                                             // the histogram is dead: its memory takes the pivot bin's entries
+    }
+    if (fast) {
+        // ---- listed values above the pivot bin are candidates; those inside it are ranked among themselves
+        const uint32_t pivot = (uint32_t)sc->pivot;
+        const int need = NC - sc->above;
+        for (int e = tid; e < LCAP; e += NT)
+            if ((e & (WCAP - 1)) < sc->wcnt[e / WCAP]) {
+                const uint32_t k = lkey[e]; const int i = lidx[e];
+                if ((k >> 20) > pivot) { if ((i & gmask) == g) { const int p = atomicAdd(&sc->n_mine, 1); mine[p] = i; mkey[p] = k; } }
+                else if ((k >> 20) == pivot) { const int p = atomicAdd(&sc->n_piv, 1); pkey[p] = k; pidx[p] = i; }
+            }
         __syncthreads();
         const int n_piv = sc->n_piv;
         for (int e = warp; e < n_piv; e += NW) {                     // one warp per entry, the lanes share the count
@@ -250,25 +293,50 @@ __global__ void __launch_bounds__(NT) k_draft_pick(const Args a) {
             if (lane == 0 && r < need) { const int p = atomicAdd(&sc->n_mine, 1); mine[p] = i; mkey[p] = k; }
         }
     } else {
-        // ---- too much reaches the floor (values crowd together, or many are equal): the bin of the NC-th largest key is
-        // narrowed with the next 12 and the last 8 bits, a pass over the row each, until what is left fits the list
-        for (int level = 1; level < 3 && above_total + h > LCAP; ++level) {
-            const int shift = level == 1 ? 8 : 0, nb = level == 2 ? 256 : BINS;
+        // ---- the general route (rows without 128-bit loads; too much reaches the floor: values crowd together, or many
+        // are equal): the bin of the NC-th largest key from histograms of the top 12, the next 12 and the last 8 bits of
+        // the keys, a pass over the row each, until what is left fits the list
+        if (tid == 0) { sc->n_mine = 0; sc->n_piv = 0; sc->n_sure = 0; }
+        uint32_t pmask = 0, pval = 0;
+        int above_total = 0, h = 0;
+        for (int level = 0; level < 3 && (level == 0 || above_total + h > LCAP); ++level) {
+            const int shift = level == 0 ? 20 : level == 1 ? 8 : 0, nb = level == 2 ? 256 : BINS;
+            __syncthreads();
             for (int i = tid; i < nb; i += NT) hist[i] = 0;
             __syncthreads();
             const float edge = key_value(pval > floor_k ? pval : floor_k);
+            float m = -3.0e38f, s = 0.f;
             for_row(row, Vd, vec, [&](float v, int) {
+                if (level == 0) {                                    // the log-sum-exp rides on the first pass
+                    if (v > m) { s = s * ex2_fast((m - v) * L2E) + 1.0f; m = v; }
+                    else s += ex2_fast((v - m) * L2E);
+                }
                 if (!(v < edge)) {
                     const uint32_t k = fkey(v);
                     if (k >= floor_k && (k & pmask) == pval) atomicAdd(&hist[(k >> shift) & (uint32_t)(nb - 1)], 1u);
                 }
             });
+            if (level == 0) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float mo = __shfl_xor_sync(0xffffffffu, m, o), so = __shfl_xor_sync(0xffffffffu, s, o);
+                    const float mm = fmaxf(m, mo);
+                    s = s * ex2_fast((m - mm) * L2E) + so * ex2_fast((mo - mm) * L2E);
+                    m = mm;
+                }
+                if (lane == 0) { sc->wf[warp] = m; sc->wsum[warp] = s; }
+            }
             __syncthreads();
+            if (level == 0) {
+                mx = sc->wf[0]; ssum = 0.f;
+                for (int w = 1; w < NW; ++w) mx = fmaxf(mx, sc->wf[w]);
+                for (int w = 0; w < NW; ++w) ssum += sc->wsum[w] * ex2_fast((sc->wf[w] - mx) * L2E);
+            }
             find_pivot(hist, nb, NC - above_total, sc);
             above_total += sc->above; h = sc->h;
             pval |= (uint32_t)sc->pivot << shift; pmask |= (uint32_t)(nb - 1) << shift;
-            __syncthreads();
         }
+        __syncthreads();
         const int need = NC - above_total;                           // how many of the pivot bin's entries are taken
 
         // more keys equal to the NC-th largest than fit: they are taken in index order, up to sc->istar
