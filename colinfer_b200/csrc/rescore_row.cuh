@@ -28,18 +28,20 @@ __device__ __forceinline__ float dot8_bf16(const uint4& wv, const uint4& xv, flo
     return acc;
 }
 
-// xs: the slot's K bf16 activations in shared memory; w: the matrix [rows, K] bf16; row: which row
+// xs: the slot's K bf16 activations in shared memory; w: the matrix [rows, K] bf16; row: which row.  UN loads of a lane are
+// in flight before the first fma (the order of the fmas does not depend on it).
+template <int UN = UNROLL>
 __device__ __forceinline__ float dot_row_bf16(const uint4* xs, const __nv_bfloat16* w, long long row, int K, int lane) {
     const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)row * K);
     const int chunks = K >> 3;
     float acc = 0.f;
     int c = lane;
-    for (; c + 32 * (UNROLL - 1) < chunks; c += 32 * UNROLL) {
-        uint4 wv[UNROLL];
+    for (; c + 32 * (UN - 1) < chunks; c += 32 * UN) {
+        uint4 wv[UN];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) wv[u] = __ldcs(wr + c + 32 * u);   // streamed: the row is read once by this warp
+        for (int u = 0; u < UN; ++u) wv[u] = __ldcs(wr + c + 32 * u);   // streamed: the row is read once by this warp
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) acc = dot8_bf16(wv[u], xs[c + 32 * u], acc);
+        for (int u = 0; u < UN; ++u) acc = dot8_bf16(wv[u], xs[c + 32 * u], acc);
     }
     for (; c < chunks; c += 32) acc = dot8_bf16(__ldcs(wr + c), xs[c], acc);
 #pragma unroll
@@ -76,18 +78,19 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
     return __half2float(*reinterpret_cast<const __half*>(&sc));
 }
 
+template <int UN = UNROLL>
 __device__ __forceinline__ float dot_row_nvfp4(const uint4* xs, const uint8_t* w, const uint8_t* sf, long long row, int K, int lane) {
     const uint2* wr = reinterpret_cast<const uint2*>(w + (size_t)row * (K / 2));
     const uint8_t* sr = sf + (size_t)row * (K / 16);
     const int blocks = K >> 4;
     float acc = 0.f;
     int blk = lane;
-    for (; blk + 32 * (UNROLL - 1) < blocks; blk += 32 * UNROLL) {
-        uint2 pw[UNROLL]; uint8_t sv[UNROLL];
+    for (; blk + 32 * (UN - 1) < blocks; blk += 32 * UN) {
+        uint2 pw[UN]; uint8_t sv[UN];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) { pw[u] = __ldg(wr + blk + 32 * u); sv[u] = __ldg(sr + blk + 32 * u); }
+        for (int u = 0; u < UN; ++u) { pw[u] = __ldg(wr + blk + 32 * u); sv[u] = __ldg(sr + blk + 32 * u); }
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int u = 0; u < UN; ++u) {
             const int bb = blk + 32 * u;
             acc = fmaf(block16(pw[u], xs[2 * bb], xs[2 * bb + 1]), e4m3_to_float(sv[u]), acc);
         }

@@ -10,6 +10,21 @@ from ..kernels import _stream, check_tensor
 LOWRANK_CANDS = 256     # engine/spec/mtp.py:70
 
 
+_scratch_cache: dict = {}
+
+
+def _scratch(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """The kernel's scratch (each slot's posted results and a counter that every call leaves at zero): zero-filled once
+    and kept per device and stream; a call inside CUDA-graph capture takes a fresh zero-filled one from the graph's pool."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)
+    buf = _scratch_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = _scratch_cache[key] = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=dev)
+    return buf
+
+
 def lowrank_draft(ap: torch.Tensor, g2: torch.Tensor, w: torch.Tensor, vocab_ids: torch.Tensor | None = None,
                   sf: torch.Tensor | None = None, gs: float | None = None, n_cands: int = LOWRANK_CANDS,
                   ctas_per_slot: int = 0, want_index: bool = False):
@@ -53,7 +68,7 @@ def lowrank_draft(ap: torch.Tensor, g2: torch.Tensor, w: torch.Tensor, vocab_ids
     if N:
         lib = _lib.lib()
         nbytes = lib.colinfer_draft_pick_scratch_bytes(N)
-        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        scratch = _scratch(dev, nbytes)
         _lib.check(lib.colinfer_draft_pick(ap.data_ptr(), g2.data_ptr(), w.data_ptr(), sf.data_ptr() if fp4 else None,
                                            float(gs) if fp4 else 1.0, 1 if fp4 else 0,
                                            vocab_ids.data_ptr() if vocab_ids is not None else None, ids.data_ptr(), p.data_ptr(),

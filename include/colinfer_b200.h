@@ -178,7 +178,8 @@ int colinfer_rescore_nvfp4(const void* x, const void* w, const void* sf, float g
  * over topk's sorted list gives) is chosen: out_ids[n] = its token id, out_p[n] = min(1, exp(ex - logsumexp(ap[n]))),
  * out_idx[n] (optional) = its draft-vocabulary index, out_ex[n] (optional) = ex.  A candidate whose row lies outside
  * [0, rows_w) is never chosen.  ctas_per_slot: 0 = by N, or 1, 2, 4, 8, 16.  scratch: colinfer_draft_pick_scratch_bytes(N)
- * bytes, 16-byte aligned, contents irrelevant; nothing in the launch waits for another CTA. */
+ * bytes, 16-byte aligned, zero-filled by the caller once before its first use (every call leaves it ready for the next;
+ * calls that may overlap in time need a scratch each); nothing in the launch waits for another launch or spins. */
 enum { COLINFER_W_BF16 = 0, COLINFER_W_NVFP4 = 1 };
 int64_t colinfer_draft_pick_scratch_bytes(int N);
 int colinfer_draft_pick(const float* ap, const void* x, const void* w, const void* sf, float gs, int w_format,

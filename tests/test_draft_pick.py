@@ -49,7 +49,7 @@ def _check(out, ap, x, vid, n_cands, w=None, wq=None, sf=None, gs=None):
 
 
 @pytest.mark.parametrize("ctas", [0, 1, 2, 4, 8, 16])
-@pytest.mark.parametrize("N,Vd,K", [(1, 69632, 2560), (5, 20000, 264), (3, 4099, 64)])
+@pytest.mark.parametrize("N,Vd,K", [(1, 69632, 2560), (5, 20000, 264), (3, 4099, 64), (20, 147456, 64), (2, 160000, 64)])
 def test_draft_pick_vs_oracle_bf16(ctas, N, Vd, K):
     draft = _draft()
     w, x, vid, ap = _head(Vd + 500, K, Vd, N, seed=Vd + K)
@@ -93,13 +93,13 @@ def test_draft_pick_nvfp4(K):
 
 
 @pytest.mark.parametrize("kind", ["crowded", "crowded_fine", "quantised", "all_equal", "mostly_minus_inf", "few_finite", "two_values"])
-@pytest.mark.parametrize("ctas", [0, 2, 16])
-def test_draft_pick_hard_rows(kind, ctas):
+@pytest.mark.parametrize("ctas,Vd", [(0, 30011), (2, 30011), (16, 30012), (0, 30012), (4, 30012)])
+def test_draft_pick_hard_rows(kind, ctas, Vd):
     """Rows whose values crowd into one histogram bin (the second and third level run), rows with many equal values at the
     NC-th place (index order decides; more of them than the collection holds: the ordered count runs), and rows that are
     mostly -inf."""
     draft = _draft()
-    N, Vd, K, NC = 3, 30011, 128, 256
+    N, K, NC = 3, 128, 256                                      # Vd divisible by 4: the CTAs of a slot may share the row as a cluster
     w, x, vid, ap = _head(Vd + 100, K, Vd, N, seed=len(kind))
     g = torch.Generator().manual_seed(7)
     if kind == "crowded":
