@@ -262,6 +262,62 @@ extern "C" int colinfer_spec_accept(const int64_t* pred, const int64_t* tok, con
     return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------ spec_advance
+// The bookkeeping the reference's scheduler does on the host after every cycle (engine/runtime/scheduler.py:635-641:
+// n and out_tok read back with .tolist(), `tokens.append(y); tokens += o[:-1]; y = o[-1]`), kept on the device: the
+// slot's pending token and the cycle's accepted drafts are appended to its token history (the one the penalties count
+// in), the bonus token becomes the pending token, the position moves on by n.  One CTA per slot.  A history that
+// would overflow keeps its most recent H ids.
+#define ADV_THREADS 256
+__global__ void __launch_bounds__(ADV_THREADS) k_spec_advance(const int64_t* __restrict__ out_tok, const int32_t* __restrict__ n_in,
+                                                              int64_t* __restrict__ y, int32_t* __restrict__ history,
+                                                              int32_t* __restrict__ hist_len, int64_t* __restrict__ pos, int k1, int H) {
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int n = n_in[b];
+    if (n <= 0) return;                                              // an inactive slot keeps its state
+    const int64_t* o = out_tok + (size_t)b * k1;
+    const int nn = n < k1 ? n : k1;
+    int32_t* h = history ? history + (size_t)b * H : nullptr;
+    if (h != nullptr && H > 0) {
+        int len = hist_len[b];
+        len = len < 0 ? 0 : len > H ? H : len;
+        const int add = nn < H ? nn : H;                             // the last `add` of [y, o[0 .. nn-2]]
+        const int keep = len + add > H ? H - add : len;              // the most recent `keep` of the old ids stay
+        const int drop = len - keep;
+        if (drop > 0) {                                              // move left: every id is read before any is written
+            int32_t buf[8];
+            for (int base = 0; base < keep; base += ADV_THREADS * 8) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { const int i = base + u * ADV_THREADS + tid; buf[u] = i < keep ? h[i + drop] : 0; }
+                __syncthreads();
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { const int i = base + u * ADV_THREADS + tid; if (i < keep) h[i] = buf[u]; }
+                __syncthreads();
+            }
+        }
+        for (int i = tid; i < add; i += ADV_THREADS) {
+            const int src = nn - add + i;                            // index into [y, o[0], ..., o[nn-2]]
+            h[keep + i] = (int32_t)(src == 0 ? y[b] : o[src - 1]);
+        }
+        __syncthreads();
+        if (tid == 0) hist_len[b] = keep + add;
+    } else {
+        __syncthreads();
+    }
+    if (tid == 0) {
+        y[b] = o[nn - 1];
+        if (pos != nullptr) pos[b] += nn;
+    }
+}
+
+extern "C" int colinfer_spec_advance(const int64_t* out_tok, const int32_t* n, int64_t* y, int32_t* history, int32_t* hist_len,
+                                     int64_t* pos, int B, int k1, int H, void* stream) {
+    if (!out_tok || !n || !y || B < 0 || k1 < 1 || H < 0 || (history && !hist_len)) return (int)cudaErrorInvalidValue;
+    if (B == 0) return 0;
+    k_spec_advance<<<B, ADV_THREADS, 0, (cudaStream_t)stream>>>(out_tok, n, y, H > 0 ? history : nullptr, hist_len, pos, k1, H);
+    return (int)cudaGetLastError();
+}
+
 // ------------------------------------------------------------------------------------------------ spec_verify (rejection)
 // Finish step: per slot, decide the accepted prefix from the row statistics of the target and draft rows, then, at a
 // rejection, stream the two rows of that position once to draw from the residual max(p - q, 0).

@@ -88,7 +88,8 @@ std::vector<at::Tensor> draw(const at::Tensor& logits, const at::Tensor& tempera
     colinfer_sampler_params p = params_of(B, temperature, top_k, top_p, log_min_p, seed, rep, pres, freq, history, hist_len);
     const int32_t* mask_ptr = nullptr; int mask_rows = 0, W = 0;
     if (mask) {
-        check(*mask, at::kInt, "mask");
+        if (mask->is_cuda() || !mask->is_pinned()) check(*mask, at::kInt, "mask");   // pinned host rows are read in place (mapped memory)
+        else TORCH_CHECK(mask->is_contiguous() && mask->scalar_type() == at::kInt, "mask must be contiguous int32");
         TORCH_CHECK(mask->dim() == 3 && mask->size(0) == B && mask->size(1) >= R && mask->size(2) >= (V + 31) / 32,
                     "mask [B, R, W] int32 with W >= ceil(V / 32)");
         mask_ptr = mask->data_ptr<int32_t>(); mask_rows = (int)mask->size(1); W = (int)mask->size(2);

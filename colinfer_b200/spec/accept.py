@@ -106,7 +106,8 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
     p: SamplerParams for the B slots.  Returns the sampled tokens [B, R] int64 (argmax for slots with temperature 0).
     (engine/spec/accept.py:43-52)
 
-    mask [B, R, W] int32: grammar bitmask applied inside the same pass (what apply_mask would do first).
+    mask [B, R, W] int32: grammar bitmask applied inside the same pass (what apply_mask would do first).  Besides a CUDA
+    tensor, a pinned host tensor is taken as it is (RowMasks(zero_copy=True)): the kernel reads it over PCIe.
     u [B, R] fp32: explicit uniforms in (0, 1] instead of Philox(seed, pos).
     status / stats: also return the per-row status words int32 [B, R] / the raw row statistics uint8 [B, R, 32].
     flags: COLINFER_* flag bits of colinfer_sample (kernel choice, test flags)."""
@@ -129,7 +130,9 @@ def draw(logits: torch.Tensor, p, pos: torch.Tensor, *, mask: torch.Tensor | Non
     ps = _params_struct(p, B)
     mask_ptr, mask_rows, W = None, 0, 0
     if mask is not None:
-        check_tensor(mask, torch.int32, "mask")
+        if not (isinstance(mask, torch.Tensor) and not mask.is_cuda and mask.is_pinned() and mask.is_contiguous()
+                and mask.dtype == torch.int32):
+            check_tensor(mask, torch.int32, "mask")
         if mask.dim() != 3 or mask.size(0) != B or mask.size(1) < R or mask.size(2) < (V + 31) // 32:
             raise RuntimeError("mask [B, R, W] int32 with W >= ceil(V / 32)")
         mask_ptr, mask_rows, W = mask.data_ptr(), mask.size(1), mask.size(2)

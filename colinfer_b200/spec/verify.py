@@ -46,6 +46,36 @@ def spec_accept(pred: torch.Tensor, tok: torch.Tensor, stop_ids: torch.Tensor | 
     return out_tok, n
 
 
+def spec_advance(out_tok: torch.Tensor, n: torch.Tensor, y: torch.Tensor, history: torch.Tensor | None = None,
+                 hist_len: torch.Tensor | None = None, pos: torch.Tensor | None = None) -> None:
+    """The scheduler's bookkeeping after a cycle (engine/runtime/scheduler.py:635-641: `tokens.append(y); tokens += o[:-1];
+    y = o[-1]`) without reading n back: in place, for every slot with n > 0, y int64 [B] and the accepted drafts are
+    appended to history int32 [B, H] / hist_len int32 [B] (the most recent H ids are kept), y becomes the bonus token,
+    pos int64 [B] moves on by n."""
+    check_tensor(out_tok, torch.int64, "out_tok")
+    check_tensor(n, torch.int32, "n")
+    check_tensor(y, torch.int64, "y")
+    if out_tok.dim() != 2 or n.numel() != out_tok.size(0) or y.numel() != out_tok.size(0):
+        raise RuntimeError("out_tok [B, k+1], n [B], y [B]")
+    B, k1 = out_tok.shape
+    H = 0
+    if history is not None:
+        check_tensor(history, torch.int32, "history")
+        if hist_len is None:
+            raise RuntimeError("hist_len is required with history")
+        check_tensor(hist_len, torch.int32, "hist_len")
+        if history.dim() != 2 or history.size(0) != B or hist_len.numel() != B:
+            raise RuntimeError("history [B, H], hist_len [B]")
+        H = history.size(1)
+    if pos is not None:
+        check_tensor(pos, torch.int64, "pos")
+        if pos.numel() != B:
+            raise RuntimeError("pos [B]")
+    _lib.check(_lib.lib().colinfer_spec_advance(out_tok.data_ptr(), n.data_ptr(), y.data_ptr(),
+                                                history.data_ptr() if H else None, hist_len.data_ptr() if H else None,
+                                                pos.data_ptr() if pos is not None else None, B, k1, H, _stream()), "spec_advance")
+
+
 def spec_verify(target_logits: torch.Tensor, draft_logits: torch.Tensor, draft_ids: torch.Tensor, p,
                 ua: torch.Tensor, us: torch.Tensor, mask: torch.Tensor | None = None):
     """Rejection verify.  target_logits [B, k+1, V], draft_logits [B, k, V] (fp32 or bf16), draft_ids [B, k] int64,

@@ -122,6 +122,15 @@ int colinfer_inverse_cdf(const float* P, const float* u, int64_t* out, int R, in
 int colinfer_spec_accept(const int64_t* pred, const int64_t* tok, const int64_t* stop_ids, const int32_t* active,
                          int64_t* out_tok, int32_t* n, int B, int k1, int S, void* stream);
 
+/* Keeps on the device what the reference's scheduler does on the host after every cycle (engine/runtime/scheduler.py:
+ * 635-641: n and out_tok read back, `tokens.append(y); tokens += o[:-1]; y = o[-1]`).  For each slot with n[b] > 0: the
+ * pending token y[b] and the accepted drafts out_tok[b, 0 .. n-2] are appended to history[b, :hist_len[b]] (int32 [B, H],
+ * the history the penalties count in; NULL: no history; on overflow the most recent H ids are kept), y[b] becomes the
+ * bonus token out_tok[b, n-1], hist_len[b] and pos[b] (int64, NULL: none) move on by n.  Slots with n[b] <= 0 keep
+ * their state.  out_tok [B, k1] int64 and n [B] int32 as colinfer_spec_accept / colinfer_spec_verify write them. */
+int colinfer_spec_advance(const int64_t* out_tok, const int32_t* n, int64_t* y, int32_t* history, int32_t* hist_len,
+                          int64_t* pos, int B, int k1, int H, void* stream);
+
 /* Rejection verify with the (p - q)+ residual resample (no counterpart in the reference, which accepts by exact match;
  * semantics: accept draft i iff p_i(d_i) > 0 and ua[i] * q_i(d_i) <= p_i(d_i); at the first rejection j emit a draw from
  * normalize(max(p_j - q_j, 0)) with us[j]; if none is rejected emit a draw from p_k with us[k]; temperature <= 0 uses

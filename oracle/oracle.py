@@ -479,3 +479,23 @@ def draft_pick(ap, x_bits, vocab_ids, n_cands, w_bits=None, w_u8=None, sf_u8=Non
         margins.append(float(srt[-1] - srt[-2]) if len(srt) > 1 else np.inf)
     return (np.array(ids, dtype=np.int64), np.array(ps), np.array(idxs, dtype=np.int64), np.array(exs, dtype=np.float32),
             np.array(margins))
+
+
+def spec_advance(out_tok, n, y, history, hist_len, pos):
+    """The scheduler's bookkeeping after a cycle (engine/runtime/scheduler.py:635-641) on arrays: for each slot with n > 0,
+    tokens += [y] + out_tok[:n-1], y = out_tok[n-1], pos += n; the history keeps its most recent H ids.  Returns new
+    (y, history, hist_len, pos); the inputs are not modified."""
+    y, history, hist_len, pos = np.array(y), np.array(history), np.array(hist_len), np.array(pos)
+    B, H = history.shape
+    for b in range(B):
+        nb = int(n[b])
+        if nb <= 0:
+            continue
+        o = [int(t) for t in out_tok[b][:nb]]
+        toks = [int(t) for t in history[b, :hist_len[b]]] + [int(y[b])] + o[:-1]
+        toks = toks[-H:] if H else []
+        history[b, :len(toks)] = toks
+        hist_len[b] = len(toks)
+        y[b] = o[-1]
+        pos[b] += nb
+    return y, history, hist_len, pos
