@@ -27,6 +27,14 @@ __device__ __forceinline__ float key2f(uint32_t k) {
 #define CI_KEY_NEG_INF 0x007FFFFFu  // f2key(-inf)
 
 // z = l / tc exactly as the reference computes it (one IEEE division); tc == 1 needs no division.
+// Repetition / presence / frequency penalties of one logit whose token occurs cnt > 0 times in the slot's history (not in
+// the reference; this project's definition): l > 0 ? l / rp : l * rp, then - fp * cnt, then - pp, each rounded to fp32.
+__device__ __forceinline__ float apply_penalty(float l, int cnt, float rp, float pp, float fp) {
+    l = l > 0.0f ? __fdiv_rn(l, rp) : __fmul_rn(l, rp);
+    l = __fsub_rn(l, __fmul_rn(fp, (float)cnt));
+    return __fsub_rn(l, pp);
+}
+
 __device__ __forceinline__ float scale_logit(float l, float tc) { return __fdiv_rn(l, tc); }
 
 // Smallest float c with c / tc >= zt (division rounded to nearest, monotone in c).  `start` must be within a few

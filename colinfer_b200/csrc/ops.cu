@@ -335,6 +335,51 @@ struct VerifyArgs {
     int seg;                           // elements per segment (a multiple of 128)
     int vec;                           // fp32 rows that take 128-bit loads
     int B, k, V;
+    const int32_t* history; const int32_t* hist_len; int hist_stride;   // the slots' penalties (NULL: none)
+    const float* rp; const float* pp; const float* fp;
+};
+
+// A slot's penalties as the verify's kernels see them: every row of the slot, target and draft, is penalised with the
+// slot's history before mask and temperature, as the two sampler launches did when they took the rows' statistics.
+#define VF_BM_WORDS 512                // bitmap of one segment's tokens that occur in the history (segments up to 16,384 logits)
+struct PenSlot {
+    const int32_t* h; int len; float rp, pp, fp; bool on;
+    __device__ void init(const VerifyArgs& a, int b) {
+        h = a.history ? a.history + (size_t)b * a.hist_stride : nullptr;
+        len = h ? (a.hist_len ? min(max(a.hist_len[b], 0), a.hist_stride) : a.hist_stride) : 0;
+        rp = a.rp ? a.rp[b] : 1.0f; pp = a.pp ? a.pp[b] : 0.0f; fp = a.fp ? a.fp[b] : 0.0f;
+        on = len > 0 && !(rp == 1.0f && pp == 0.0f && fp == 0.0f);
+    }
+    __device__ int count(int tok) const {                            // one thread scans the history
+        int c = 0;
+        for (int i = 0; i < len; ++i) c += (__ldg(h + i) == tok) ? 1 : 0;
+        return c;
+    }
+    __device__ int count_warp(int tok, int lane) const {             // a warp shares the scan
+        int c = 0;
+        for (int i = lane; i < len; i += 32) c += (__ldg(h + i) == tok) ? 1 : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        return c;
+    }
+    // marks in bm (zeroed here) the tokens of [lo, hi) that occur in the history; all threads of the CTA call it
+    __device__ void mark(uint32_t* bm, int lo, int hi) const {
+        for (int i = threadIdx.x; i < VF_BM_WORDS; i += blockDim.x) bm[i] = 0;
+        __syncthreads();
+        if (on)
+            for (int i = threadIdx.x; i < len; i += blockDim.x) {
+                const int v = __ldg(h + i);
+                if (v >= lo && v < hi) atomicOr(&bm[(v - lo) >> 5], 1u << ((v - lo) & 31));
+            }
+        __syncthreads();
+    }
+    // the two logits of token i as the distributions see them
+    __device__ __forceinline__ void fix(const uint32_t* bm, int lo, int i, float& lt, float& ld) const {
+        if (on && ((bm[(i - lo) >> 5] >> ((i - lo) & 31)) & 1u)) {
+            const int c = count(i);
+            lt = apply_penalty(lt, c, rp, pp, fp); ld = apply_penalty(ld, c, rp, pp, fp);
+        }
+    }
 };
 
 __device__ __forceinline__ float load_logit(const void* base, int dtype, size_t idx) {
@@ -368,14 +413,17 @@ struct Residual {
     }
 };
 
-// Step 1, one thread per slot: the accepted prefix from the row statistics of the target and draft rows.
+// Step 1, one warp per slot: the accepted prefix from the row statistics of the target and draft rows (the lanes share
+// the count of a draft token in the slot's history; everything else every lane does alike).
 __global__ void k_verify_decide(const __grid_constant__ VerifyArgs a) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (b >= a.B) return;
     const int k = a.k, V = a.V;
     const colinfer_row_stats* st_t = a.st_t + (size_t)b * (k + 1);
     const colinfer_row_stats* st_d = a.st_d + (size_t)b * k;
     const bool greedy = !(a.temperature[b] > 0.0f);
+    PenSlot pen;
+    pen.init(a, b);
     int j = 0;
     for (; j < k; ++j) {
         const long long d = a.draft_ids[(size_t)b * k + j];
@@ -386,6 +434,10 @@ __global__ void k_verify_decide(const __grid_constant__ VerifyArgs a) {
             const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
             float lt = load_logit(a.tl, a.dtype, ((size_t)b * (k + 1) + j) * V + d);
             float ld = load_logit(a.dl, a.dtype, ((size_t)b * k + j) * V + d);
+            if (pen.on) {
+                const int c = pen.count_warp((int)d, lane);
+                if (c > 0) { lt = apply_penalty(lt, c, pen.rp, pen.pp, pen.fp); ld = apply_penalty(ld, c, pen.rp, pen.pp, pen.fp); }
+            }
             if (!mask_allows(mrow, (int)d)) { lt = CI_NEG_INF; ld = CI_NEG_INF; }
             const double p = token_prob(st_t[j], lt, d), q = token_prob(st_d[j], ld, d);
             // (a draft token the target gives no probability -- masked, or outside its kept set -- is never accepted,
@@ -397,13 +449,14 @@ __global__ void k_verify_decide(const __grid_constant__ VerifyArgs a) {
     int mode = 1;
     if (greedy || j == k) mode = 0;
     else if ((st_t[j].status | st_d[j].status) & (COLINFER_ROW_DEGENERATE | COLINFER_ROW_TIMEOUT)) mode = 0;
-    a.slot[b] = make_int2(j, mode);
+    if (lane == 0) a.slot[b] = make_int2(j, mode);
 }
 
 // Step 2, VF_NSEG CTAs per slot: the residual mass max(p - q, 0) of one segment of the rejected position's two rows,
 // streamed once with 128-bit loads where the rows allow it.
 __global__ void __launch_bounds__(VF_THREADS) k_verify_residual(const __grid_constant__ VerifyArgs a) {
     __shared__ u64 wsum[VF_THREADS / 32];
+    __shared__ uint32_t bm[VF_BM_WORDS];
     const int b = blockIdx.x / VF_NSEG, sgi = blockIdx.x % VF_NSEG;
     const int2 sl = a.slot[b];
     if (sl.y != 1) return;
@@ -413,6 +466,9 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_residual(const __grid_con
     const int32_t* mrow = a.mask ? a.mask + ((size_t)b * (k + 1) + j) * a.W : nullptr;
     const size_t bt = ((size_t)b * (k + 1) + j) * V, bd = ((size_t)b * k + j) * V;
     const int lo = min(sgi * a.seg, V), hi = min(lo + a.seg, V);
+    PenSlot pen;
+    pen.init(a, b);
+    if (pen.on) pen.mark(bm, lo, hi);                                // (the same for every thread of the CTA)
     u64 acc = 0;
     if (a.vec) {
         const float* pt = reinterpret_cast<const float*>(a.tl) + bt;
@@ -426,12 +482,16 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_residual(const __grid_con
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int i = (e < 4 ? i0 : i1 - 4) + e;
-                if (i < hi && mask_allows(mrow, i)) acc += res(tt[e], dd[e]);
+                if (i < hi && mask_allows(mrow, i)) { float lt = tt[e], ld = dd[e]; pen.fix(bm, lo, i, lt, ld); acc += res(lt, ld); }
             }
         }
     } else {
         for (int i = lo + threadIdx.x; i < hi; i += VF_THREADS)
-            if (mask_allows(mrow, i)) acc += res(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i));
+            if (mask_allows(mrow, i)) {
+                float lt = load_logit(a.tl, a.dtype, bt + i), ld = load_logit(a.dl, a.dtype, bd + i);
+                pen.fix(bm, lo, i, lt, ld);
+                acc += res(lt, ld);
+            }
     }
     const u64 wt = warp_sum_u64(acc);
     if (lane == 0) wsum[warp] = wt;
@@ -447,6 +507,7 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_residual(const __grid_con
 // (threads own consecutive chunks of the segment: token order); and the slot's outputs.
 __global__ void __launch_bounds__(VF_THREADS) k_verify_pick(const __grid_constant__ VerifyArgs a) {
     __shared__ u64 tsum[VF_THREADS];
+    __shared__ uint32_t bm[VF_BM_WORDS];
     __shared__ long long s_token;
     const int b = blockIdx.x, k = a.k, V = a.V, tid = threadIdx.x;
     const int2 sl = a.slot[b];
@@ -480,9 +541,16 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_pick(const __grid_constan
             const int lo = min(sx * a.seg, V), hi = min(lo + a.seg, V);
             const int per = (hi - lo + VF_THREADS - 1) / VF_THREADS;
             const int c_lo = min(lo + tid * per, hi), c_hi = min(c_lo + per, hi);
+            PenSlot pen;
+            pen.init(a, b);
+            if (pen.on) pen.mark(bm, lo, hi);                        // (sx, and so this branch, is the same for every thread)
             u64 mine = 0;
             for (int i = c_lo; i < c_hi; ++i)
-                if (mask_allows(mrow, i)) mine += res(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i));
+                if (mask_allows(mrow, i)) {
+                    float lt = load_logit(a.tl, a.dtype, bt + i), ld = load_logit(a.dl, a.dtype, bd + i);
+                    pen.fix(bm, lo, i, lt, ld);
+                    mine += res(lt, ld);
+                }
             tsum[tid] = mine;
             __syncthreads();
             if (tid == 0) {
@@ -496,7 +564,11 @@ __global__ void __launch_bounds__(VF_THREADS) k_verify_pick(const __grid_constan
                 u64 run = tsum[0];
                 long long tok = c_hi > c_lo ? c_hi - 1 : lo;
                 for (int i = c_lo; i < c_hi; ++i) {
-                    if (mask_allows(mrow, i)) run += res(load_logit(a.tl, a.dtype, bt + i), load_logit(a.dl, a.dtype, bd + i));
+                    if (mask_allows(mrow, i)) {
+                        float lt = load_logit(a.tl, a.dtype, bt + i), ld = load_logit(a.dl, a.dtype, bd + i);
+                        pen.fix(bm, lo, i, lt, ld);
+                        run += res(lt, ld);
+                    }
                     if (run >= target) { tok = i; break; }
                 }
                 s_token = tok;
@@ -526,8 +598,8 @@ extern "C" int colinfer_spec_verify(const void* target_logits, const void* draft
     if (!target_logits || !draft_logits || !params || !draft_ids || !ua || !us || !out_tok || !n || !scratch_stats ||
         !scratch_ids || B < 0 || k < 1 || V <= 0)
         return (int)cudaErrorInvalidValue;
-    if (params->history != nullptr) return (int)cudaErrorInvalidValue;   // penalties are not part of the verify step
     if (B == 0) return 0;
+    if ((((V + VF_NSEG - 1) / VF_NSEG + 127) / 128) * 128 > VF_BM_WORDS * 32) return (int)cudaErrorInvalidValue;
     colinfer_row_stats* st_t = scratch_stats;
     colinfer_row_stats* st_d = scratch_stats + (size_t)B * (k + 1);
     // target rows: statistics and the plain draw of every row with its sampling uniform
@@ -545,9 +617,11 @@ extern "C" int colinfer_spec_verify(const void* target_logits, const void* draft
     a.slot = reinterpret_cast<int2*>(st_d + (size_t)B * k);
     a.seg_sums = reinterpret_cast<u64*>(a.slot + B);
     a.seg = (((V + VF_NSEG - 1) / VF_NSEG + 127) / 128) * 128;
+    a.history = params->history; a.hist_len = params->hist_len; a.hist_stride = params->history ? params->hist_stride : 0;
+    a.rp = params->repetition_penalty; a.pp = params->presence_penalty; a.fp = params->frequency_penalty;
     a.vec = (dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)target_logits) & 15) == 0 && (((uintptr_t)draft_logits) & 15) == 0) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
-    k_verify_decide<<<(B + 127) / 128, 128, 0, st>>>(a);
+    k_verify_decide<<<(B + 3) / 4, 128, 0, st>>>(a);
     k_verify_residual<<<B * VF_NSEG, VF_THREADS, 0, st>>>(a);
     k_verify_pick<<<B, VF_THREADS, 0, st>>>(a);
     return (int)cudaGetLastError();

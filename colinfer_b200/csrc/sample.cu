@@ -148,11 +148,6 @@ __device__ u64 block_sum_u64(u64 v, Scratch* s) {
     return t;
 }
 
-__device__ __forceinline__ float apply_penalty(float l, int cnt, float rp, float pp, float fp) {
-    l = l > 0.0f ? __fdiv_rn(l, rp) : __fmul_rn(l, rp);
-    l = __fsub_rn(l, __fmul_rn(fp, (float)cnt));
-    return __fsub_rn(l, pp);
-}
 
 // Estimated mass (units of 2^-30) of one element in distance bucket b: exp(-(b + 0.5) * CI_RANGE / CI_NB1).
 __device__ __forceinline__ u64 bucket_mass_est(int b) {

@@ -272,11 +272,6 @@ __device__ bool lean_select(GL getl, W wt, int n, float base, float scale, u64 t
     return sc->sel_ok != 0;
 }
 
-__device__ __forceinline__ float apply_penalty(float l, int cnt, float rp, float pp, float fp) {
-    l = l > 0.0f ? __fdiv_rn(l, rp) : __fmul_rn(l, rp);
-    l = __fsub_rn(l, __fmul_rn(fp, (float)cnt));
-    return __fsub_rn(l, pp);
-}
 
 // One row as the passes see it: effective logits (penalties, then mask), four at a time.
 struct Row {

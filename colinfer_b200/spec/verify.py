@@ -79,8 +79,8 @@ def spec_advance(out_tok: torch.Tensor, n: torch.Tensor, y: torch.Tensor, histor
 def spec_verify(target_logits: torch.Tensor, draft_logits: torch.Tensor, draft_ids: torch.Tensor, p,
                 ua: torch.Tensor, us: torch.Tensor, mask: torch.Tensor | None = None):
     """Rejection verify.  target_logits [B, k+1, V], draft_logits [B, k, V] (fp32 or bf16), draft_ids [B, k] int64,
-    p: SamplerParams (penalties unsupported here), ua [B, k] accept uniforms, us [B, k+1] sampling uniforms,
-    mask [B, k+1, W] int32 applied to both models' rows.  Accept draft i iff ua_i * q_i(d_i) <= p_i(d_i); at the first
+    p: SamplerParams (its penalties, if any, apply to every row of both models with the slot's history), ua [B, k] accept
+    uniforms, us [B, k+1] sampling uniforms, mask [B, k+1, W] int32 applied to both models' rows.  Accept draft i iff ua_i * q_i(d_i) <= p_i(d_i); at the first
     rejection emit a draw from normalize(max(p - q, 0)); with no rejection emit a draw from p_k.  temperature <= 0:
     accept while the draft equals the target's argmax.  Returns (out_tok [B, k+1] int64 padded with -1, n [B] int32)."""
     check_tensor(target_logits, None, "target_logits")
@@ -97,8 +97,6 @@ def spec_verify(target_logits: torch.Tensor, draft_logits: torch.Tensor, draft_i
     check_tensor(us, torch.float32, "us")
     if draft_ids.numel() != B * k or ua.numel() != B * k or us.numel() != B * k1:
         raise RuntimeError("draft_ids, ua [B, k]; us [B, k+1]")
-    if getattr(p, "history", None) is not None:
-        raise RuntimeError("spec_verify does not take penalties (apply them before the verify)")
     ps = _params_struct(p, B)
     mask_ptr, W = None, 0
     if mask is not None:

@@ -135,7 +135,8 @@ int colinfer_spec_advance(const int64_t* out_tok, const int32_t* n, int64_t* y, 
  * semantics: accept draft i iff p_i(d_i) > 0 and ua[i] * q_i(d_i) <= p_i(d_i); at the first rejection j emit a draw from
  * normalize(max(p_j - q_j, 0)) with us[j]; if none is rejected emit a draw from p_k with us[k]; temperature <= 0 uses
  * the argmax rule).  target_logits [B, k+1, V], draft_logits [B, k, V] (dtype), mask [B, k+1, W] or NULL (applies to
- * both), draft_ids [B, k] int64, ua [B, k], us [B, k+1].  scratch: B * (2k + 1) colinfer_row_stats and B * (k + 1)
+ * both), draft_ids [B, k] int64, ua [B, k], us [B, k+1].  Penalties in params (history, hist_len, the three factors)
+ * apply to every row of both models with the slot's history, before mask and temperature; V <= 524,288.  scratch: B * (2k + 1) colinfer_row_stats and B * (k + 1)
  * int64 (device).  out_tok [B, k+1] int64 (accepted drafts, then the emitted token, then -1), n [B] int32 = accepted + 1. */
 int colinfer_spec_verify(const void* target_logits, const void* draft_logits, int dtype, const int32_t* mask, int W,
                          const colinfer_sampler_params* params, const int64_t* draft_ids, const float* ua,

@@ -303,10 +303,11 @@ def spec_accept(pred, tok, stop_ids, active):
 
 
 def spec_verify_reject(target_logits, draft_logits, draft_ids, temperature, top_k, top_p, log_min_p, ua, us,
-                       target_mask=None):
+                       target_mask=None, history=None, rep=1.0, pres=0.0, freq=0.0):
     """Rejection verify with the (p - q)+ residual (not in the reference; this project's definition) for one slot.
     target_logits [k+1, V], draft_logits [k, V], draft_ids [k], ua [k] accept uniforms, us [k+1] sampling uniforms.
-    p_i, q_i = processed() of target / draft row i (the same parameters; the mask, if any, applies to both).
+    p_i, q_i = processed() of target / draft row i (the same parameters; the slot's penalties, then the mask, if any,
+    apply to every row of both).
     temperature <= 0: accept while draft == argmax(target row), emit the argmax of the first mismatching row.
     Else accept draft i iff p_i(d_i) > 0 and ua_i * q_i(d_i) <= p_i(d_i); at the first rejection j emit inverse_cdf(max(p_j - q_j, 0),
     us_j) (from p_j if that residual has no mass); if none is rejected emit inverse_cdf(p_k, us_k).
@@ -314,6 +315,9 @@ def spec_verify_reject(target_logits, draft_logits, draft_ids, temperature, top_
     tl = np.asarray(target_logits, dtype=F32)
     dl = np.asarray(draft_logits, dtype=F32)
     k = dl.shape[0]
+    if history is not None:
+        tl = np.stack([penalties(tl[i], history, rep, pres, freq) for i in range(k + 1)])
+        dl = np.stack([penalties(dl[i], history, rep, pres, freq) for i in range(k)])
     if target_mask is not None:
         tl = np.stack([apply_mask(tl[i], target_mask[i]) for i in range(k + 1)])
         dl = np.stack([apply_mask(dl[i], target_mask[i]) for i in range(k)])

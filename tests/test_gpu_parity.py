@@ -794,6 +794,58 @@ def test_spec_verify_never_accepts_a_token_the_target_excludes():
         assert tok == r["token"] or r["margin"] < 1e-5
 
 
+def test_spec_verify_with_penalties_vs_oracle():
+    """The slot's penalties apply to every target and draft row of the verify (this project's definition).  Histories hold
+    the targets' most likely tokens and the drafts themselves, so that acceptance and the residual both depend on them;
+    neutral factors leave the result of the penalty-free call."""
+    m = mods()
+    for (B, k, V, H) in [(24, 3, 5000, 64), (3, 4, wl.V_QWEN, 2048)]:
+        g = torch.Generator().manual_seed(B + V)
+        target = torch.randn(B, k + 1, V, generator=g) * 2.5
+        draft = (target[:, :k] + torch.randn(B, k, V, generator=g) * 0.6).contiguous()
+        params = wl._params(B, V, torch.where(torch.arange(B) % 6 == 0, 0.0, 0.8), 50, 0.95, 0.0)
+        hist = torch.randint(0, V, (B, H), generator=g, dtype=torch.int64)
+        top = target[:, :k].topk(8, -1).indices.reshape(B, -1)          # the most likely tokens of every target row
+        hist[:, :top.size(1)] = top
+        hist[:, top.size(1):2 * top.size(1)] = top                      # twice: counts of 2
+        hist[:, -3:] = torch.tensor([-1, V, V + 7])                     # ids outside the vocabulary are skipped
+        hl = torch.randint(2 * top.size(1), H + 1, (B,), generator=g, dtype=torch.int64)
+        rep = torch.where(torch.arange(B) % 4 == 3, 1.0, 1.3)
+        pres = torch.where(torch.arange(B) % 4 == 3, 0.0, 0.5)
+        freq = torch.where(torch.arange(B) % 4 == 3, 0.0, 0.25)
+        sp = wl.sampler_params(params, V, "cuda")
+        for b in range(B):
+            sp.set_penalties(b, float(rep[b]), float(pres[b]), float(freq[b]))
+        sp.set_history(hist.int().cuda(), hl.int().cuda())
+        ud, ua, us = wl.open_unit(g, B, k), wl.open_unit(g, B, k), wl.open_unit(g, B, k + 1)
+        d_ids = m["draw"](draft.cuda(), sp, None, u=ud.cuda())           # drafts drawn from the penalised q
+        out, n = m["spec_verify"](target.cuda(), draft.cuda(), d_ids, sp, ua.cuda(), us.cuda())
+        out, n, d_np = out.cpu().numpy(), n.cpu().numpy(), d_ids.cpu().numpy()
+        pr = np_params(params)
+        boundary, lens = 0, set()
+        for b in range(B):
+            r = O.spec_verify_reject(target[b].numpy(), draft[b].numpy(), d_np[b], pr["temperature"][b], pr["top_k"][b], pr["top_p"][b],
+                                     pr["log_min_p"][b], ua[b].numpy(), us[b].numpy(), history=hist[b, :int(hl[b])].numpy(),
+                                     rep=float(rep[b]), pres=float(pres[b]), freq=float(freq[b]))
+            ok = (n[b] == r["n_accept"] + 1 and out[b, r["n_accept"]] == r["token"]
+                  and list(out[b, :r["n_accept"]]) == list(d_np[b, :r["n_accept"]]))
+            lens.add(int(n[b]))
+            if not ok:
+                assert min(r["margin"], r["accept_margin"]) < 1e-5, (b, n[b], out[b], r)
+                boundary += 1
+        assert boundary <= 1 and len(lens) >= 2
+        # neutral factors: the penalty-free call, bit for bit
+        sp0 = wl.sampler_params(params, V, "cuda")
+        base = m["spec_verify"](target.cuda(), draft.cuda(), d_ids, sp0, ua.cuda(), us.cuda())
+        for b in range(B):
+            sp0.set_penalties(b, 1.0, 0.0, 0.0)
+        sp0.set_history(hist.int().cuda(), hl.int().cuda())
+        neutral = m["spec_verify"](target.cuda(), draft.cuda(), d_ids, sp0, ua.cuda(), us.cuda())
+        assert torch.equal(base[0], neutral[0]) and torch.equal(base[1], neutral[1])
+        # and the penalties do change decisions on these inputs
+        assert not (torch.equal(base[0].cpu(), torch.from_numpy(out)) and torch.equal(base[1].cpu(), torch.from_numpy(n)))
+
+
 def test_spec_verify_preserves_the_target_distribution():
     """The first emitted token of a rejection verify follows p_0 whatever the draft distribution is."""
     m = mods()
