@@ -273,9 +273,24 @@ __device__ bool lean_select(GL getl, W wt, int n, float base, float scale, u64 t
 }
 
 
+// How long a row's lines should stay in L2: rows that are read twice (the wide ones: a pass for the histogram, a pass for
+// the exact masses) ask to be evicted last on their first pass and first on their second; rows read once ask to be evicted
+// first, so that the 126 MB keep the ~ 50 wide rows in flight (30 MB) instead of the last 90 MB streamed.
+__device__ __forceinline__ unsigned long long l2_policy_keep() {
+    unsigned long long p;
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long l2_policy_stream() {
+    unsigned long long p;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
 // One row as the passes see it: effective logits (penalties, then mask), four at a time.
 struct Row {
     const float* p32; const __nv_bfloat16* p16; int V; bool vec, vec16;   // 128-bit fp32 loads / 64-bit bf16 loads of four logits
+    unsigned long long pol;            // L2 eviction policy of the row's loads (l2_policy_keep / l2_policy_stream)
     const int32_t* mrow;
     bool has_pen; const uint32_t* pen_bits; const uint32_t* pen_prefix; const float* pen_val;
     bool pen_inline;                   // the passes apply the penalties element by element (else: raw logits, lists patched afterwards)
@@ -295,10 +310,13 @@ struct Row {
     __device__ __forceinline__ float4 raw4(int i) const {
         float4 v;
         if (vec) {
-            v = i < V ? __ldcg(reinterpret_cast<const float4*>(p32 + i)) : make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
+            if (i < V) asm("ld.global.cg.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+                           : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p32 + i), "l"(pol));
+            else v = make_float4(CI_NEG_INF, CI_NEG_INF, CI_NEG_INF, CI_NEG_INF);
         } else if (vec16) {
             if (i < V) {
-                const uint2 u = __ldcg(reinterpret_cast<const uint2*>(p16 + i));    // four bf16: a float's upper halves
+                uint2 u;                                                            // four bf16: a float's upper halves
+                asm("ld.global.cg.L2::cache_hint.v2.u32 {%0, %1}, [%2], %3;" : "=r"(u.x), "=r"(u.y) : "l"(p16 + i), "l"(pol));
                 v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u),
                                 __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
             } else {
@@ -888,6 +906,7 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
         rw.pen_bits = pen_bits; rw.pen_prefix = pen_prefix; rw.pen_val = pen_val; rw.hist_slow = &sc->hist_slow;
         if (tid == 0) sc->hist_slow = 0;
         const bool fastk = sampled && kk > 0 && kk <= FASTK && kk < V;
+        rw.pol = (sampled && !fastk) ? l2_policy_keep() : l2_policy_stream();
         // Rows that are finished from their candidate lists alone -- greedy and small-top-k rows -- need the penalties of
         // the listed tokens only.  When the penalties can only lower a logit (the usual setting) such a row builds no
         // tables: after the pass every history entry looks itself up in the lists (they are ordered by token) and the
@@ -1467,6 +1486,7 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
                             }
                         }
                     };
+                    rw.pol = l2_policy_stream();                 // the row's last full read
                     if (PEN && rw.pen_inline) { if (band) mass_pass(BoolTag<PEN>{}, BoolTag<true>{}); else mass_pass(BoolTag<PEN>{}, BoolTag<false>{}); }
                     else { if (band) mass_pass(BoolTag<false>{}, BoolTag<true>{}); else mass_pass(BoolTag<false>{}, BoolTag<false>{}); }
                     ST_PROF(11);
