@@ -19,6 +19,7 @@ roofline  algorithmic bytes per row (one read of every input + outputs) x rows /
         capture recorded under profiles/ (with the commit it was taken at), scaled by rows -- not measured in this run.
 sweep   (one GPU) the other configurations, each timed per launch with the L2 flushed in between: the batched sweep at
         8 / 64 / 256 rows, the bf16 large-vocabulary stress [512, 262144], the speculative verify (verifies/s).
+next_rows  (one GPU) the whole lines of --workload logprobs / rescore / draft: the kernels of the rows next to the path.
 strong  (N > 1) fixed batches split over the ranks with sharding.shard_rows: 1024 rows of the sweep, 512 of the stress.
 cpu_baseline  the reference's torch path restated for the CPU (oracle/torch_cpu_path.py), timed on this box's host
         cores on a bounded sample of the same batch.  --impl reference times only that, on the whole batch.
@@ -728,6 +729,16 @@ def main():
                 line["sweep"]["reference_gpu_path"] = {k: rec[k] for k in ("value", "unit", "ms_per_step", "note", "unavailable") if k in rec}
             except Exception as e:                         # noqa: BLE001
                 line["sweep"]["reference_gpu_path"] = {"unavailable": f"{e!r}"[:160]}
+            # the kernels of the rows next to the path (logprobs of emitted tokens, draft-head rescoring, the one-launch
+            # low-rank draft): their own workloads, each in a child process, their lines kept whole
+            line["next_rows"] = {}
+            for wk in ("logprobs", "rescore", "draft"):
+                try:
+                    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", wk, "--steps", "20", "--warmup", "5"],
+                                       capture_output=True, text=True, timeout=300)
+                    line["next_rows"][wk] = json.loads(r.stdout.strip().splitlines()[-1])
+                except Exception as e:                     # noqa: BLE001
+                    line["next_rows"][wk] = {"unavailable": f"{e!r}"[:160]}
         if world == 1 and not args.no_cpu_baseline:
             n, times, threads = cpu_rows_per_s(w, CPU_SAMPLE_ROWS, reps=3, warm=1)
             line["cpu_baseline"] = {"value": n / statistics.median(times), "unit": "rows/s", "cores": threads, "kind": "port",
