@@ -2,8 +2,9 @@
 // alternatives -- what engine/runtime/scheduler.py:714-722 computes with log_softmax + gather + topk (three full-vocabulary
 // passes and a [r, V] temporary) -- in ONE pass over the row.
 //
-// One 1024-thread CTA per SM walks over rows (persistent).  Warp w owns a contiguous region of the row; lanes read
-// 128-bit groups, four in flight per thread.  Each thread keeps an online (maximum, sum of exp) pair; the first batch
+// Two 512-thread CTAs per SM walk over rows (persistent): every row costs the same, so the SM's rows split evenly, and
+// while one CTA is in its short block-wide steps (the sample's bound, the selection of the alternatives) the other one
+// streams.  Warp w owns a contiguous region of the row; lanes read 128-bit groups, four in flight per thread.  Each thread keeps an online (maximum, sum of exp) pair; the first batch
 // of every warp (a tenth of the row at 151,936 logits) bounds the n_top-th largest logit from below, and the pass lists
 // what reaches the bound (a few hundred logits), from which one warp takes the exact top n_top in descending order
 // (equal logits: lower token first).  A row whose lists overflow (long runs of equal logits) takes n_top extra passes.
@@ -18,10 +19,11 @@
 
 namespace lpk {
 
-constexpr int NT = 1024, NW = NT / 32;
+constexpr int NT = 512, NW = NT / 32;
+constexpr int CTAS_PER_SM = 2;
 constexpr int BINS = 512;            // bins of the sample histogram and of the candidate selection
 constexpr float SAMPLE_SCALE = 32.0f;
-constexpr int WLIST = 64;            // list entries per warp
+constexpr int WLIST = 128;           // list entries per warp
 constexpr int FCAP = 128;            // candidates of the one-warp selection
 constexpr int MAX_TOP = 32;          // n_top <= MAX_TOP
 #define LP_FLT_MAX 3.402823466e38f
@@ -103,7 +105,7 @@ struct Args {
 // LOADER: 1 = fp32 rows that take 128-bit loads, 2 = bf16 rows that take 64-bit loads of four logits, 0 = the general
 // loader (unaligned rows, vocabularies that are not a multiple of 4).
 template <int LOADER>
-__global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args a) {
+__global__ void __launch_bounds__(NT, CTAS_PER_SM) k_logprobs(const __grid_constant__ Args a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int V = a.V, n_top = a.n_top;
     __shared__ __align__(16) uint32_t hist[BINS];
@@ -112,6 +114,9 @@ __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args
     const int reg = (((V + 127) / 128 + NW - 1) / NW) * 128;
     const int r_lo = min(warp * reg, V), r_hi = min(r_lo + reg, V);
     Cand* mylist = ownlist + warp * WLIST;
+    if (tid >= NW && tid < 32) {                                    // neutral entries for the warps this CTA does not have
+        sc.wm[tid] = CI_NEG_INF; sc.ws[tid] = 0.0f; sc.wf[tid] = CI_NEG_INF; sc.wcount[tid] = -1;
+    }
 
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
         __syncthreads();
@@ -262,22 +267,23 @@ __global__ void __launch_bounds__(NT, 1) k_logprobs(const __grid_constant__ Args
                 }
                 __syncthreads();
                 {
-                    // rank of every candidate among the candidates (value descending, then token ascending): 8 threads
-                    // per candidate compare it with 16 others each; a candidate of rank < n_top is that alternative
-                    static_assert(NT == FCAP * 8, "eight threads per candidate");
-                    const int c = tid >> 3, part = tid & 7;
+                    // rank of every candidate among the candidates (value descending, then token ascending): a few threads
+                    // per candidate compare it with a share of the others each; a candidate of rank < n_top is that alternative
+                    constexpr int TPC = NT / FCAP;                  // threads per candidate
+                    static_assert(TPC == 4 || TPC == 8, "four or eight threads per candidate");
+                    const int c = tid / TPC, part = tid % TPC;
                     int rank = 0;
                     if (c < (int)nc) {
                         const float lc = sc.fc_l[c]; const uint32_t ic = sc.fc_idx[c];
 #pragma unroll
-                        for (int t = 0; t < FCAP / 8; ++t) {
-                            const int o = part * (FCAP / 8) + t;
+                        for (int t = 0; t < FCAP / TPC; ++t) {
+                            const int o = part * (FCAP / TPC) + t;
                             if (o < (int)nc && before(sc.fc_l[o], sc.fc_idx[o], lc, ic)) ++rank;
                         }
                     }
                     rank += __shfl_xor_sync(0xffffffffu, rank, 1);
                     rank += __shfl_xor_sync(0xffffffffu, rank, 2);
-                    rank += __shfl_xor_sync(0xffffffffu, rank, 4);
+                    if (TPC == 8) rank += __shfl_xor_sync(0xffffffffu, rank, 4);
                     if (part == 0 && c < (int)nc && rank < n_top) {
                         a.top_ids[(size_t)row * n_top + rank] = (long long)sc.fc_idx[c];
                         a.top_lp[(size_t)row * n_top + rank] = sc.fc_l[c] - lse;
@@ -363,7 +369,8 @@ extern "C" int colinfer_logprobs(const void* logits, int dtype, const int64_t* t
     a.vec = (dtype == COLINFER_F32 && (V % 4) == 0 && (((uintptr_t)logits) & 15) == 0) ? 1 : 0;
     a.toks = toks; a.n_top = n_top; a.chosen = chosen; a.top_ids = top_ids; a.top_lp = top_lp;
     a.rows = rows; a.V = V;
-    const int grid = rows < sm_count[dev] ? rows : sm_count[dev];
+    const int slots = sm_count[dev] * lpk::CTAS_PER_SM;
+    const int grid = rows < slots ? rows : slots;
     const bool vec16 = dtype == COLINFER_BF16 && (V % 4) == 0 && (((uintptr_t)logits) & 7) == 0;
     if (a.vec) lpk::k_logprobs<1><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
     else if (vec16) lpk::k_logprobs<2><<<grid, lpk::NT, 0, (cudaStream_t)stream>>>(a);
