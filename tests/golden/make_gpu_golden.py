@@ -7,7 +7,7 @@ itself, in the reference's order, and runs them with the FlashInfer installed on
 the output; the reference pins flashinfer-python 0.7.0.post1).  The vectors pin what the oracle and the kernels are
 compared with: kept sets (ties at a pivot all kept), renormalised probabilities and drawn tokens.
 
-    python tests/golden/make_gpu_golden.py gpurun_out/ref_gpu_vectors.npz      (on a box with a GPU and FlashInfer)
+    python tests/golden/make_gpu_golden.py [out.npz]      (on a box with a GPU and FlashInfer; default: next to this script)
 
 Inputs are the seeded workloads of colinfer_b200/workloads.py (the tests regenerate them); penalties and the grammar
 mask -- which the reference applies before this step or not at all -- are applied with the numpy oracle first.
@@ -105,7 +105,7 @@ def tie_case(V=wl.V_QWEN):
 
 def main():
     import flashinfer
-    dst = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "ref_gpu_vectors.npz")
+    dst = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "tests", "golden", "ref_gpu_vectors.npz")
     out = {"flashinfer_version": np.array(flashinfer.__version__), "torch_version": np.array(torch.__version__),
            "topn": np.array(TOPN)}
     w = wl.config0()
