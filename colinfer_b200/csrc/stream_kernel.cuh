@@ -83,6 +83,7 @@ struct Sc {
     uint32_t cand_kmin, cand_kmax; // ordered keys: extremes of the pivot bin's entries (a crowded bin of equal logits)
     int hist_slow, overflow;
     int wcount[NWA], woffs[NWA + 1];
+    u64 g_all[NWA], g_keep[NWA], g_tot_all, g_tot_keep;   // sums that ride on gather_lists
     float bc_f; int bc_i;
     float wtw[NWA], wmin[NWA];     // running top-k: each warp's threshold and smallest list entry
     int fin_ok;
@@ -430,11 +431,15 @@ __device__ __forceinline__ int warp_drop_penalised(Cand* mylist, int wn, const u
 }
 
 // Concatenates the warps' lists (token order) into glist with masses; returns n, or -1 on overflow.  All threads call.
-static __device__ int gather_lists(const Cand* ownlist, int wn, Entry* glist, const MassFn& mass, Sc* sc) {
+// wall / wkeep (one value per warp; s1 / s_above: their sums over the warps) ride on the same two barriers when given.
+static __device__ int gather_lists(const Cand* ownlist, int wn, Entry* glist, const MassFn& mass, Sc* sc, u64 wall = 0, u64 wkeep = 0,
+                                   u64* s1 = nullptr, u64* s_above = nullptr) {
     const int lane = lane_id(), warp = warp_id();
-    if (lane == 0) sc->wcount[warp] = wn;
+    if (lane == 0) { sc->wcount[warp] = wn; sc->g_all[warp] = wall; sc->g_keep[warp] = wkeep; }
     __syncthreads();
     if (warp == 0) {
+        const u64 ta = warp_sum_u64(lane < NW ? sc->g_all[lane] : 0ull), tk = warp_sum_u64(lane < NW ? sc->g_keep[lane] : 0ull);
+        if (lane == 0) { sc->g_tot_all = ta; sc->g_tot_keep = tk; }
         const int c = sc->wcount[lane];
         int incl = c;
 #pragma unroll
@@ -445,6 +450,8 @@ static __device__ int gather_lists(const Cand* ownlist, int wn, Entry* glist, co
         if (lane == 0) sc->overflow = over != 0u;
     }
     __syncthreads();
+    if (s1) *s1 = sc->g_tot_all;
+    if (s_above) *s_above = sc->g_tot_keep;
     const int n = sc->woffs[NWA];
     if (sc->overflow || n > GLIST) return -1;
     const int off = sc->woffs[warp];
@@ -1507,9 +1514,7 @@ __global__ void __launch_bounds__(NT, CTAS_PER_SM) k_sample_stream(const __grid_
                     if (band) {
                         const u64 wall = warp_sum_u64(acc_all) + wall_corr;
                         u64 s1, s_above;
-                        block_excl_scan(lane == 0 ? wall : 0ull, sc, s1);
-                        block_excl_scan(lane == 0 ? wkeep : 0ull, sc, s_above);
-                        int n = gather_lists(ownlist, wn, glist, mass, sc);
+                        int n = gather_lists(ownlist, wn, glist, mass, sc, wall, wkeep, &s1, &s_above);
                         if (corr && n >= 0) {
                             if (tid == 0) sc->glist_n = n;
                             __syncthreads();
