@@ -95,7 +95,10 @@ def build_torch_ext(force: bool = False, verbose: bool = False) -> str:
     bdir = os.path.join(HERE, "build", "torch_ext")
     os.makedirs(bdir, exist_ok=True)
     cpp_extension.load(name="_colinfer_torch", sources=[src], extra_cflags=["-O2"], with_cuda=True,
-                       extra_ldflags=[f"-L{HERE}", "-lcolinfer_b200", "-Wl,-rpath,'$$ORIGIN'", "-Wl,-rpath,'$$ORIGIN/../..'"], build_directory=bdir,
+                       # -l:libstdc++.so.6 first: a compiler driver whose own libstdc++.so link dangles would otherwise link
+                       # the static libstdc++ into the extension, whose streams are then not the process's (and crash)
+                       extra_ldflags=["-l:libstdc++.so.6", f"-L{HERE}", "-lcolinfer_b200", "-Wl,-rpath,'$$ORIGIN'", "-Wl,-rpath,'$$ORIGIN/../..'"],
+                       build_directory=bdir,
                        is_python_module=False, verbose=verbose)
     shutil.copyfile(os.path.join(bdir, "_colinfer_torch.so"), EXT)
     return EXT

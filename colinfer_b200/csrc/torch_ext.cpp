@@ -136,6 +136,66 @@ std::vector<at::Tensor> spec_accept(const at::Tensor& pred, const at::Tensor& to
     return {out_tok, n};
 }
 
+// spec_advance(out_tok, n, y, history?, hist_len?, pos?): the scheduler's bookkeeping after a cycle, in place on the device
+// (engine/runtime/scheduler.py:635-641)
+void spec_advance(const at::Tensor& out_tok, const at::Tensor& n, at::Tensor y, const Opt& history, const Opt& hist_len, const Opt& pos) {
+    check(out_tok, at::kLong, "out_tok"); check(n, at::kInt, "n"); check(y, at::kLong, "y");
+    TORCH_CHECK(out_tok.dim() == 2 && n.numel() == out_tok.size(0) && y.numel() == out_tok.size(0), "out_tok [B, k+1], n [B], y [B]");
+    const int64_t B = out_tok.size(0), k1 = out_tok.size(1);
+    int64_t H = 0;
+    if (history) {
+        check(*history, at::kInt, "history");
+        TORCH_CHECK(hist_len.has_value(), "hist_len is required with history");
+        check(*hist_len, at::kInt, "hist_len");
+        TORCH_CHECK(history->dim() == 2 && history->size(0) == B && hist_len->numel() == B, "history [B, H], hist_len [B]");
+        H = history->size(1);
+    }
+    if (pos) { check(*pos, at::kLong, "pos"); TORCH_CHECK(pos->numel() == B, "pos [B]"); }
+    c10::cuda::CUDAGuard guard(out_tok.device());
+    cuda_ok(colinfer_spec_advance(out_tok.data_ptr<int64_t>(), n.data_ptr<int32_t>(), y.data_ptr<int64_t>(),
+                                  H ? history->data_ptr<int32_t>() : nullptr, H ? hist_len->data_ptr<int32_t>() : nullptr,
+                                  pos ? pos->data_ptr<int64_t>() : nullptr, (int)B, (int)k1, (int)H, stream()), "spec_advance");
+}
+
+// lowrank_draft(ap, g2, w, vocab_ids?, sf?, gs, n_cands, ctas_per_slot, scratch, want_index) -> ids, p (+ idx, ex): the greedy
+// draft of the low-rank heads in one launch (engine/spec/mtp.py:301-309, engine/spec/mtp4.py:416-423).  scratch: a uint8
+// tensor of colinfer_draft_pick_scratch_bytes(N) bytes that is zero-filled before its first use (the mirror keeps it).
+std::vector<at::Tensor> lowrank_draft(const at::Tensor& ap, const at::Tensor& g2, const at::Tensor& w, const Opt& vocab_ids, const Opt& sf,
+                                      double gs, int64_t n_cands, int64_t ctas_per_slot, at::Tensor scratch, bool want_index) {
+    check(ap, at::kFloat, "ap"); check(g2, at::kBFloat16, "g2");
+    TORCH_CHECK(ap.dim() == 2 && g2.dim() == 2 && g2.size(0) == ap.size(0), "ap [N, Vd], g2 [N, K]");
+    const int64_t N = ap.size(0), Vd = ap.size(1), K = g2.size(1);
+    const bool fp4 = sf.has_value();
+    if (fp4) {
+        check(w, at::kByte, "w");
+        TORCH_CHECK(sf->is_cuda() && sf->is_contiguous() && (sf->scalar_type() == at::kByte || sf->scalar_type() == at::kFloat8_e4m3fn),
+                    "sf must be a contiguous CUDA tensor of uint8 or float8_e4m3fn");
+        TORCH_CHECK(w.dim() == 2 && w.size(1) * 2 == K && K % 16 == 0 && sf->numel() == w.size(0) * (K / 16),
+                    "w [rows, K / 2], sf [rows, K / 16] with K % 16 == 0");
+    } else {
+        check(w, at::kBFloat16, "w");
+        TORCH_CHECK(w.dim() == 2 && w.size(1) == K && K % 8 == 0, "w [rows, K] with K % 8 == 0");
+    }
+    if (vocab_ids) { check(*vocab_ids, at::kLong, "vocab_ids"); TORCH_CHECK(vocab_ids->numel() == Vd, "vocab_ids [Vd]"); }
+    TORCH_CHECK(n_cands >= 1 && n_cands <= std::min<int64_t>(Vd, 1024), "n_cands must lie in 1 .. min(Vd, 1024)");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(g2.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0,
+                "g2 and w must be 16-byte aligned");
+    check(scratch, at::kByte, "scratch");
+    TORCH_CHECK(scratch.numel() >= colinfer_draft_pick_scratch_bytes((int)N), "scratch is too small");
+    c10::cuda::CUDAGuard guard(ap.device());
+    at::Tensor ids = at::empty({N}, ap.options().dtype(at::kLong)), p = at::empty({N}, ap.options());
+    std::vector<at::Tensor> res{ids, p};
+    at::Tensor idx, ex;
+    if (want_index) { idx = at::empty({N}, ap.options().dtype(at::kInt)); ex = at::empty({N}, ap.options()); res.push_back(idx); res.push_back(ex); }
+    if (N == 0) return res;
+    cuda_ok(colinfer_draft_pick(ap.data_ptr<float>(), g2.data_ptr(), w.data_ptr(), fp4 ? sf->data_ptr() : nullptr, fp4 ? (float)gs : 1.0f,
+                                fp4 ? COLINFER_W_NVFP4 : COLINFER_W_BF16, vocab_ids ? vocab_ids->data_ptr<int64_t>() : nullptr,
+                                ids.data_ptr<int64_t>(), p.data_ptr<float>(), want_index ? idx.data_ptr<int32_t>() : nullptr,
+                                want_index ? ex.data_ptr<float>() : nullptr, (int)N, (int)Vd, (int)K, (int)n_cands, w.size(0),
+                                (int)ctas_per_slot, scratch.data_ptr(), scratch.numel(), stream()), "draft_pick");
+    return res;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -144,4 +204,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("apply_mask", &apply_mask, "logits with every token whose mask bit is clear set to -inf (a new tensor)");
     m.def("draw", &draw, "fused penalties + mask + temperature + min-p / top-k / top-p + argmax or seeded draw: one launch");
     m.def("spec_accept", &spec_accept, "exact-match accept, bonus token and stop cut of the speculative cycle");
+    m.def("spec_advance", &spec_advance, "the bookkeeping after a cycle, in place on the device");
+    m.def("lowrank_draft", &lowrank_draft, "the greedy draft of the low-rank heads: top candidates, exact rescoring, argmax, probability: one launch");
 }

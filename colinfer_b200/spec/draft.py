@@ -34,6 +34,12 @@ def lowrank_draft(ap: torch.Tensor, g2: torch.Tensor, w: torch.Tensor, vocab_ids
     row.  Returns (ids int64 [N], p fp32 [N]) as the reference's block does: of the n_cands largest approximations the
     token with the largest exact logit, and exp(that logit - logsumexp(ap)) clamped to 1.  want_index: also the winning
     draft-vocabulary index (int32 [N]) and its exact logit (fp32 [N])."""
+    ext = _lib.ext()
+    if ext is not None and hasattr(ext, "lowrank_draft") and isinstance(ap, torch.Tensor) and ap.is_cuda and ap.dim() == 2:
+        nbytes = _lib.lib().colinfer_draft_pick_scratch_bytes(ap.size(0))
+        res = ext.lowrank_draft(ap, g2, w, vocab_ids, sf, float(gs) if gs is not None else 1.0, int(n_cands), int(ctas_per_slot),
+                                _scratch(ap.device, max(int(nbytes), 1)), bool(want_index))
+        return tuple(res)
     check_tensor(ap, torch.float32, "ap")
     check_tensor(g2, torch.bfloat16, "g2")
     if ap.dim() != 2 or g2.dim() != 2 or g2.size(0) != ap.size(0):

@@ -52,6 +52,10 @@ def spec_advance(out_tok: torch.Tensor, n: torch.Tensor, y: torch.Tensor, histor
     y = o[-1]`) without reading n back: in place, for every slot with n > 0, y int64 [B] and the accepted drafts are
     appended to history int32 [B, H] / hist_len int32 [B] (the most recent H ids are kept), y becomes the bonus token,
     pos int64 [B] moves on by n."""
+    ext = _lib.ext()
+    if ext is not None and hasattr(ext, "spec_advance"):
+        ext.spec_advance(out_tok, n, y, history, hist_len, pos)
+        return
     check_tensor(out_tok, torch.int64, "out_tok")
     check_tensor(n, torch.int32, "n")
     check_tensor(y, torch.int64, "y")

@@ -794,6 +794,23 @@ def test_spec_verify_never_accepts_a_token_the_target_excludes():
         assert tok == r["token"] or r["margin"] < 1e-5
 
 
+def test_error_paths_raise_and_do_not_crash():
+    """Errors found behind the tensor checks -- a vocabulary beyond the kernels' limit, a slot count that does not match --
+    come back as RuntimeError with the numbers in the message (formatting them once crashed an extension that had been
+    linked against a second copy of the C++ runtime)."""
+    m = mods()
+    V = 600000                                                     # beyond the streaming kernel's penalty bitmap and the clusters' slices
+    logits = torch.zeros(1, 1, V, device="cuda")
+    sp = m["SamplerParams"](1, V, "cuda")
+    sp.set(0, temperature=1.0, top_k=5, top_p=0.9, seed=1)
+    pos = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with pytest.raises(RuntimeError):
+        m["draw"](logits, sp, pos, flags=_lib.kernel_flags(8))
+    sp2 = m["SamplerParams"](2, 1000, "cuda")
+    with pytest.raises(RuntimeError, match="slot"):
+        m["draw"](torch.zeros(1, 1, 1000, device="cuda"), sp2, pos)
+
+
 def test_spec_verify_with_penalties_vs_oracle():
     """The slot's penalties apply to every target and draft row of the verify (this project's definition).  Histories hold
     the targets' most likely tokens and the drafts themselves, so that acceptance and the residual both depend on them;
