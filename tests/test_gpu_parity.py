@@ -811,6 +811,31 @@ def test_error_paths_raise_and_do_not_crash():
         m["draw"](torch.zeros(1, 1, 1000, device="cuda"), sp2, pos)
 
 
+def test_spec_verify_and_the_mass_horizon():
+    """A draft token the kernels give no mass (more than ~21.5 temperatures below the target row's maximum; p ~ 1e-11 in
+    float64) counts as excluded by the target and is rejected, whatever the draft thought of it; one well above the
+    horizon follows the oracle's accept test.  Found by a randomised sweep with drafts that were not drawn from q."""
+    m = mods()
+    V, k, T = 2000, 1, 0.5
+    g = torch.Generator().manual_seed(4)
+    target = torch.randn(2, k + 1, V, generator=g)
+    target[:, 0, 7] = 20.0                                         # the maximum of the first row
+    target[0, 0, 11] = 20.0 - 25.0 * T                             # slot 0's draft: 25 temperatures below it
+    target[1, 0, 11] = 20.0 - 10.0 * T                             # slot 1's draft: 10 temperatures below it
+    draft = target[:, :k].clone()
+    draft[:, 0, 11] -= 5.0                                         # the drafter likes it even less: q < p, the test would accept
+    d_ids = torch.full((2, k), 11, dtype=torch.int64)
+    params = wl._params(2, V, T, 0, 1.0, 0.0)
+    sp = wl.sampler_params(params, V, "cuda")
+    ua, us = torch.full((2, k), 0.5), torch.full((2, k + 1), 0.4)
+    out, n = m["spec_verify"](target.cuda(), draft.cuda(), d_ids.cuda(), sp, ua.cuda(), us.cuda())
+    r0 = O.spec_verify_reject(target[0].numpy(), draft[0].numpy(), d_ids[0].numpy(), T, V, 1.0, -np.inf, ua[0].numpy(), us[0].numpy())
+    r1 = O.spec_verify_reject(target[1].numpy(), draft[1].numpy(), d_ids[1].numpy(), T, V, 1.0, -np.inf, ua[1].numpy(), us[1].numpy())
+    assert r0["n_accept"] == 1 and r1["n_accept"] == 1             # in float64 both drafts pass p > 0 and ua * q <= p
+    assert int(n[0]) == 1 and int(out[0, 0]) != 11                 # below the horizon: rejected, another token emitted
+    assert int(n[1]) == 2 and int(out[1, 0]) == 11 and int(out[1, 1]) == r1["token"]
+
+
 def test_spec_verify_with_penalties_vs_oracle():
     """The slot's penalties apply to every target and draft row of the verify (this project's definition).  Histories hold
     the targets' most likely tokens and the drafts themselves, so that acceptance and the residual both depend on them;
