@@ -147,3 +147,67 @@ def test_spec_verify_random_sweep(seed):
                 boundary += 1
     print(f"[parity] random sweep of the verify, seed {seed}: {slots} slots, {boundary} inside the margin, {horizon} drafts below the mass horizon")
     assert boundary <= max(2, slots // 500)
+
+
+def test_draft_pick_and_logprobs_random_sweep():
+    from colinfer_b200.runtime.logprobs import logprobs_tensors
+    from colinfer_b200.spec.draft import lowrank_draft
+    _lib.lib()
+    bits = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+    for case in range(40):
+        rng = np.random.default_rng(3100000 + case)
+        g = torch.Generator().manual_seed(3100000 + case)
+        # ---- the one-launch draft of the low-rank heads
+        Vd = int(rng.choice([256, 300, 1000, 4096, 8190, 20000]))
+        K, N = int(rng.choice([8, 64, 264])), int(rng.choice([1, 2, 9, 12, 40, 80]))
+        NC, rows_w = int(min(Vd, rng.choice([1, 16, 256, 1000]))), Vd + int(rng.integers(0, 50))
+        w = (torch.randn(rows_w, K, generator=g) * 0.05).bfloat16().cuda()
+        x = torch.randn(N, K, generator=g).bfloat16().cuda()
+        vid = torch.randperm(rows_w, generator=g)[:Vd].cuda() if rng.random() < 0.8 else None
+        kind = rng.choice(["track", "normal", "ties", "crowded", "neg_inf"])
+        if kind == "track":
+            ap = x.float() @ w[vid if vid is not None else slice(0, Vd)].float().T + 0.3 * torch.randn(N, Vd, generator=g).cuda()
+        elif kind == "normal":
+            ap = torch.randn(N, Vd, generator=g).cuda() * 3
+        elif kind == "ties":
+            ap = (torch.randn(N, Vd, generator=g) * 2).round().cuda()
+        elif kind == "crowded":
+            ap = (5.0 + 1e-4 * torch.randn(N, Vd, generator=g)).cuda()
+        else:
+            ap = torch.randn(N, Vd, generator=g)
+            ap[torch.rand(N, Vd, generator=g) < 0.9] = -float("inf")
+            ap = ap.cuda()
+        ap = ap.contiguous()
+        ctas = int(rng.choice([0, 0, 1, 2, 4, 8, 16]))
+        ids, p, idx, ex = lowrank_draft(ap, x, w, vid, n_cands=NC, ctas_per_slot=ctas, want_index=True)
+        want = O.draft_pick(ap.cpu().numpy(), bits(x), None if vid is None else vid.cpu().numpy(), NC, w_bits=bits(w))
+        what = (case, N, Vd, K, NC, ctas, kind)
+        assert np.array_equal(idx.cpu().numpy(), want[2]) and np.array_equal(ids.cpu().numpy(), want[0]), what
+        assert np.array_equal(ex.cpu().numpy().view(np.uint32), want[3].view(np.uint32)), what
+        fin = np.isfinite(want[1])
+        np.testing.assert_allclose(p.cpu().numpy()[fin], want[1][fin], rtol=2e-5, atol=1e-30)
+        # ---- logprobs of emitted tokens
+        V, r = int(rng.choice([1, 5, 33, 128, 1000, 4099, 20000])), int(rng.choice([1, 3, 17, 200]))
+        n_top = int(min(V, rng.choice([0, 1, 5, 20, 32])))
+        dtype = torch.bfloat16 if rng.random() < 0.3 else torch.float32
+        rows = torch.randn(r, V, generator=g) * float(rng.choice([1.0, 4.0]))
+        kind = rng.choice(["normal", "ties", "peaked", "neg_inf"])
+        if kind == "ties":
+            rows = (rows * 2).round() * 0.5
+        elif kind == "peaked":
+            rows[:, int(rng.integers(0, V))] += 30.0
+        elif kind == "neg_inf":
+            rows[torch.rand(r, V, generator=g) < 0.7] = -float("inf")
+            rows[:, 0] = 0.0
+        rows = rows.to(dtype)
+        toks = torch.tensor(rng.integers(0, V, size=r))
+        c, ti, tl = (t.cpu().numpy() for t in logprobs_tensors(rows.cuda(), toks.cuda(), n_top))
+        wc, wi, wl_ = O.logprobs(rows.float().numpy(), toks.numpy(), n_top)
+        fin = np.isfinite(wc)
+        np.testing.assert_allclose(c[fin], wc[fin], atol=3e-5, rtol=0)
+        if n_top:
+            fin = np.isfinite(wl_)
+            np.testing.assert_allclose(tl[fin], wl_[fin], atol=3e-5, rtol=0)
+            xv = rows.float().numpy()
+            for i in range(r):                                      # equal logits may swap places: the values must agree
+                assert np.array_equal(xv[i][ti[i]], xv[i][wi[i]]), (case, i)
