@@ -69,7 +69,9 @@ def config_of(B: int, world: int) -> dict:
     """The `config` object of the headline line: identical for both arms of a run."""
     return {"workload": f"config3 batched sampling sweep: fp32 logits [{B}, {V}] per GPU, history {HIST}, "
                         "penalties, T~U[0.5,1.2], top_k in {0,20,100}, top_p~U[0.8,1.0]",
-            "rows_per_gpu": B, "vocab": V, "l2": "inputs (630 MB per GPU) larger than L2, no flush needed",
+            "rows_per_gpu": B, "vocab": V,
+            "l2": (f"inputs ({B * V * 4 / 1e6:.0f} MB per GPU) larger than L2, no flush needed" if B * V * 4 > 126e6
+                   else f"inputs ({B * V * 4 / 1e6:.0f} MB per GPU) fit in L2: steps after the first are served from it"),
             "sharding": f"rows x{world}, ids gathered" if world > 1 else "single GPU"}
 
 
